@@ -1,0 +1,248 @@
+"""Python face of the CUDA kernels: checks tensors, passes raw pointers through ctypes.
+
+Every function launches on torch's current CUDA stream and raises
+:class:`KernelError` when a kernel refuses its arguments or the launch fails.  There is
+no fallback: without a CUDA device and the built libraries these functions raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional
+
+import torch
+
+from . import build as _build
+
+CJ_F32, CJ_BF16 = 0, 1
+_REFUSALS = {-2: "dtype combination not built into this kernel", -3: "a size this kernel does not take",
+             -4: "pointer or stride alignment this kernel needs", -5: "null pointer or bad count"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_libs: Dict[str, ctypes.CDLL] = {}
+
+
+def library(name: str) -> ctypes.CDLL:
+    """The loaded kernel library ``name`` (built first when it has to be)."""
+    lib = _libs.get(name)
+    if lib is None:
+        path = _build.build(name)
+        lib = ctypes.CDLL(path)
+        _libs[name] = lib
+    return lib
+
+
+def loaded_libraries() -> Dict[str, str]:
+    return {n: l._name for n, l in _libs.items()}
+
+
+def _code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return CJ_F32
+    if t.dtype == torch.bfloat16:
+        return CJ_BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, found {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    if t is None:
+        return ctypes.c_void_p(0)
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status in _REFUSALS:
+        raise KernelError(f"{what}: refused: {_REFUSALS[status]}")
+    raise KernelError(f"{what}: CUDA error {status} at launch")
+
+
+def _need(t: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor; this engine has no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, found {t.dtype}")
+
+
+_i = ctypes.c_int
+_ll = ctypes.c_longlong
+_f = ctypes.c_float
+
+
+def embed_gather(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+    """out[t, :] = table[ids[t], :] widened to float32.  out: [T, H] float32."""
+    _need(out, "out", torch.float32), _need(table, "table"), _need(ids, "ids", torch.int32)
+    T, H = out.shape
+    V = table.shape[0]
+    st = library("rowwise").cj_embed_gather(_ptr(out), _ptr(table), _i(_code(table)), _ptr(ids), _i(T), _i(H), _i(V), _stream())
+    _check(st, "embed_gather")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            out_f32: Optional[torch.Tensor] = None, row_index: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rmsnorm(x[row_index[r] or r]) * weight; x, weight float32; out float32 or
+    bfloat16; out_f32 an optional float32 copy of the result."""
+    _need(x, "x", torch.float32), _need(weight, "weight", torch.float32), _need(out, "out")
+    rows, H = out.shape
+    if x.shape[-1] != H or weight.numel() != H:
+        raise KernelError(f"rmsnorm: width mismatch x {tuple(x.shape)} weight {tuple(weight.shape)} out {tuple(out.shape)}")
+    if out_f32 is not None:
+        _need(out_f32, "out_f32", torch.float32)
+    if row_index is not None:
+        _need(row_index, "row_index", torch.int32)
+    st = library("rowwise").cj_rmsnorm(_ptr(x), _ptr(weight), _f(eps), _i(rows), _i(H), _ptr(out), _i(_code(out)),
+                                       _ptr(out_f32), _ptr(row_index), _stream())
+    _check(st, "rmsnorm")
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+         accumulate: bool = False, w_up: Optional[torch.Tensor] = None, group_offsets: Optional[torch.Tensor] = None,
+         a_row_index: Optional[torch.Tensor] = None, rows: Optional[int] = None) -> None:
+    """out[M, N] (+)= a[M, K] . w[N, K]^T (+ bias) on the float32 FMA pipe.
+
+    ``w_up`` selects the SwiGLU form silu(a.w^T) * (a.w_up^T).  With ``group_offsets``
+    ([G + 1] int32) ``w`` is [G, N, K], output row s belongs to the group whose range
+    holds s, and ``a_row_index[s]`` names the row of ``a`` that feeds it.
+    """
+    _need(a, "a"), _need(w, "w"), _need(out, "out")
+    grouped = group_offsets is not None
+    N, K = w.shape[-2], w.shape[-1]
+    M = rows if rows is not None else out.shape[0]
+    if a.shape[-1] != K or out.shape[-1] != N:
+        raise KernelError(f"gemm: shapes a {tuple(a.shape)} w {tuple(w.shape)} out {tuple(out.shape)} do not agree")
+    if w_up is not None:
+        _need(w_up, "w_up")
+        if w_up.shape != w.shape or w_up.dtype != w.dtype:
+            raise KernelError("gemm: w_up must match w")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    G = 0
+    if grouped:
+        _need(group_offsets, "group_offsets", torch.int32)
+        G = w.shape[0]
+        if group_offsets.numel() != G + 1:
+            raise KernelError("gemm: group_offsets must hold one more entry than w has groups")
+    if a_row_index is not None:
+        _need(a_row_index, "a_row_index", torch.int32)
+    st = library("gemm_simt").cj_gemm_simt(
+        _ptr(a), _ll(a.stride(0)), _i(_code(a)), _ptr(w), _ptr(w_up), _ll(K), _i(_code(w)), _ptr(bias),
+        _ptr(out), _ll(out.stride(0)), _i(_code(out)), _i(M), _i(N), _i(K), _i(1 if accumulate else 0),
+        _ptr(group_offsets), _i(G), _ll(N * K), _ptr(a_row_index), _stream())
+    _check(st, "gemm")
+
+
+def rope_kv_write(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor,
+                  k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], positions: torch.Tensor,
+                  row_req: Optional[torch.Tensor], table: Optional[torch.Tensor], page_tokens: int, n_heads: int,
+                  n_kv: int, head_dim: int, rotary_dim: int, inv_freq: Optional[torch.Tensor], write_kv: bool) -> None:
+    """Rotate q and k at each row's position; write q to q_out, rotated k and raw v into
+    the cache pages of the row's request.  qkv: float32 [T, ld]."""
+    _need(qkv, "qkv", torch.float32), _need(q_out, "q_out"), _need(positions, "positions", torch.int32)
+    T = qkv.shape[0]
+    cache_dtype = _code(q_out)
+    if write_kv:
+        _need(k_plane, "k_plane"), _need(v_plane, "v_plane"), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
+        cache_dtype = _code(k_plane)
+    st = library("rowwise").cj_rope_kv_write(
+        _ptr(qkv), _i(qkv.stride(0)), _i(q_off), _i(k_off), _i(v_off), _ptr(q_out), _i(_code(q_out)),
+        _ptr(k_plane), _ptr(v_plane), _i(cache_dtype), _ptr(positions), _ptr(row_req), _ptr(table),
+        _i(table.stride(0) if table is not None else 0), _i(page_tokens), _i(T), _i(n_heads), _i(n_kv), _i(head_dim),
+        _i(rotary_dim), _ptr(inv_freq), _i(1 if write_kv else 0), _stream())
+    _check(st, "rope_kv_write")
+
+
+def paged_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+                    positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int,
+                    n_heads: int, n_kv: int, head_dim: int, window: int, scale: float) -> None:
+    """Attention of every row over its request's cached keys [from, position]."""
+    _need(q, "q"), _need(out, "out"), _need(k_plane, "k_plane"), _need(v_plane, "v_plane")
+    _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
+    T = q.shape[0]
+    if head_dim > 256:
+        raise KernelError(f"paged_attention: head_dim {head_dim} is larger than 256")
+    st = library("attention_paged").cj_paged_attention(
+        _ptr(q), _ptr(out), _i(_code(q)), _ptr(k_plane), _ptr(v_plane), _i(_code(k_plane)), _ptr(positions),
+        _ptr(row_req), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(T), _i(n_heads), _i(n_kv), _i(head_dim),
+        _i(window), _f(scale), _stream())
+    _check(st, "paged_attention")
+
+
+def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[torch.Tensor], top_k: int,
+                norm_topk: bool, sel: torch.Tensor, weights: torch.Tensor, shared_scale: Optional[torch.Tensor]) -> None:
+    """Router logits, softmax over all experts, top-k and the shared expert's sigmoid gate."""
+    _need(x, "x", torch.float32), _need(router_w, "router_w", torch.float32)
+    _need(sel, "sel", torch.int32), _need(weights, "weights", torch.float32)
+    T, H = x.shape
+    E = router_w.shape[0]
+    if E > 1024:
+        raise KernelError(f"router_topk: {E} experts; this kernel takes at most 1024")
+    if shared_gate is not None:
+        _need(shared_gate, "shared_gate", torch.float32), _need(shared_scale, "shared_scale", torch.float32)
+    st = library("moe_route").cj_router_topk(_ptr(x), _ptr(router_w), _ptr(shared_gate), _i(T), _i(H), _i(E), _i(top_k),
+                                             _i(1 if norm_topk else 0), _ptr(sel), _ptr(weights), _ptr(shared_scale), _stream())
+    _check(st, "router_topk")
+
+
+def moe_group(sel: torch.Tensor, top_k: int, num_experts: int, offsets: torch.Tensor, slot_token: torch.Tensor,
+              slot_of_pick: torch.Tensor) -> None:
+    """Counting sort of the picks by expert: offsets [E + 1], slot_token, slot_of_pick."""
+    for n, t in (("sel", sel), ("offsets", offsets), ("slot_token", slot_token), ("slot_of_pick", slot_of_pick)):
+        _need(t, n, torch.int32)
+    st = library("moe_route").cj_moe_group(_ptr(sel), _i(sel.numel()), _i(top_k), _i(num_experts), _ptr(offsets),
+                                           _ptr(slot_token), _ptr(slot_of_pick), _stream())
+    _check(st, "moe_group")
+
+
+def moe_combine(hs: torch.Tensor, y: Optional[torch.Tensor], slot_of_pick: Optional[torch.Tensor],
+                weights: Optional[torch.Tensor], top_k: int, shared: Optional[torch.Tensor],
+                shared_scale: Optional[torch.Tensor]) -> None:
+    """hs[t] += sum_j weights[t, j] * y[slot_of_pick[t, j]] (+ shared_scale[t] * shared[t])."""
+    _need(hs, "hs", torch.float32)
+    T, H = hs.shape
+    for n, t in (("y", y), ("weights", weights), ("shared", shared), ("shared_scale", shared_scale)):
+        if t is not None:
+            _need(t, n, torch.float32)
+    if slot_of_pick is not None:
+        _need(slot_of_pick, "slot_of_pick", torch.int32)
+    st = library("rowwise").cj_moe_combine(_ptr(hs), _ptr(y), _ptr(slot_of_pick), _ptr(weights), _i(top_k), _ptr(shared),
+                                           _ptr(shared_scale), _i(T), _i(H), _stream())
+    _check(st, "moe_combine")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """First-occurrence argmax of each row of float32 logits into int32 out."""
+    _need(logits, "logits", torch.float32), _need(out, "out", torch.int32)
+    rows, V = logits.shape
+    st = library("sampling").cj_argmax(_ptr(logits), _i(rows), _i(V), _ptr(out), _stream())
+    _check(st, "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, scratch: torch.Tensor,
+           out: torch.Tensor, top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
+           repeat_penalty: Optional[torch.Tensor] = None, history: Optional[torch.Tensor] = None,
+           history_offsets: Optional[torch.Tensor] = None) -> None:
+    """One token per row by the reference's sampler order; scratch is [rows, V] float32."""
+    _need(logits, "logits", torch.float32), _need(temperature, "temperature", torch.float32)
+    _need(uniform, "uniform", torch.float32), _need(scratch, "scratch", torch.float32), _need(out, "out", torch.int32)
+    rows, V = logits.shape
+    if scratch.numel() < rows * V:
+        raise KernelError("sample: scratch is smaller than the logits")
+    for n, t, d in (("top_k", top_k, torch.int32), ("top_p", top_p, torch.float32),
+                    ("repeat_penalty", repeat_penalty, torch.float32), ("history", history, torch.int32),
+                    ("history_offsets", history_offsets, torch.int32)):
+        if t is not None:
+            _need(t, n, d)
+    st = library("sampling").cj_sample(_ptr(logits), _i(rows), _i(V), _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                                       _ptr(repeat_penalty), _ptr(uniform), _ptr(history), _ptr(history_offsets),
+                                       _ptr(scratch), _ptr(out), _stream())
+    _check(st, "sample")

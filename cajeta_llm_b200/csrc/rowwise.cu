@@ -1,0 +1,214 @@
+// Row-wise kernels: embedding gather, RMSNorm, rotary encoding fused with the write
+// of keys and values into cache pages, and the weighted combine of expert outputs.
+// All statistics, angles and sums are float32; storage is float32 or bfloat16.
+#include "common.cuh"
+
+using namespace cj;
+
+// ---------------------------------------------------------------------------------
+// embedding: hs[t, :] = table[id_t, :] widened to float32 (the residual stream)
+// reference: model/Embedding.cajeta:73-81, gather kernel io/QuantKernel.cajeta:40720
+// ---------------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_gather_kernel(float* __restrict__ out, const TW* __restrict__ table,
+                                    const int* __restrict__ ids, int H, int V) {
+    int t = blockIdx.x;
+    int id = ids[t];
+    bool ok = id >= 0 && id < V;   // the host checks ids; an id out of range reads nothing
+    const TW* src = table + (size_t)(ok ? id : 0) * H;
+    float* dst = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ok ? to_f32(src[i]) : 0.0f;
+}
+
+CJ_EXPORT int cj_embed_gather(float* out, const void* table, int table_dtype, const int* ids,
+                              int T, int H, int V, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (!out || !table || !ids || H <= 0 || V <= 0) return CJ_ERR_ARG;
+    int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == CJ_F32)
+        embed_gather_kernel<float><<<T, threads, 0, stream>>>(out, (const float*)table, ids, H, V);
+    else if (table_dtype == CJ_BF16)
+        embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, H, V);
+    else
+        return CJ_ERR_DTYPE;
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+// RMSNorm: ss = sum x^2; scale = 1/sqrt(ss/dim + eps); y = x * scale * w
+// reference: model/Prim.cajeta:120-151.  One block per output row; the input row may
+// be picked through row_index (the rows whose logits are wanted).  Writes the result
+// in the activation dtype and, when asked, a float32 copy (the router's input).
+// ---------------------------------------------------------------------------------
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int H,
+                               TO* __restrict__ out, float* __restrict__ out_f32,
+                               const int* __restrict__ row_index) {
+    __shared__ float partial[32];
+    __shared__ float scale_s;
+    int r = blockIdx.x;
+    const float* src = x + (size_t)(row_index ? row_index[r] : r) * H;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = src[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    if (lane == 0) partial[warp] = ss;
+    __syncthreads();
+    if (warp == 0) {
+        float v = lane < nwarps ? partial[lane] : 0.0f;
+        v = warp_sum(v);
+        if (lane == 0) scale_s = 1.0f / sqrtf(v / (float)H + eps);
+    }
+    __syncthreads();
+    float scale = scale_s;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float y = src[i] * scale * w[i];
+        out[(size_t)r * H + i] = from_f32<TO>(y);
+        if (out_f32) out_f32[(size_t)r * H + i] = y;
+    }
+}
+
+CJ_EXPORT int cj_rmsnorm(const float* x, const float* w, float eps, int rows, int H, void* out, int out_dtype,
+                         float* out_f32, const int* row_index, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (!x || !w || !out || H <= 0) return CJ_ERR_ARG;
+    int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (out_dtype == CJ_F32)
+        rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(x, w, eps, H, (float*)out, out_f32, row_index);
+    else if (out_dtype == CJ_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(x, w, eps, H, (__nv_bfloat16*)out, out_f32, row_index);
+    else
+        return CJ_ERR_DTYPE;
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+// Rotary encoding of q and k at each row's absolute position, fused with the write of
+// the rotated k and the raw v into the cache pages of the row's request.
+// Half-split pairs (d, d + rot/2): ang = float(p) * inv[d]; a' = a cos - b sin;
+// b' = a sin + b cos (model/Prim.cajeta:1917-1940); dims >= rotary_dim pass through.
+// reference kernels: model/AttnKernel.cajeta:128 (qkPrep), :554 (ropeAppendRows).
+//
+// qkv is float32 [T, ld] with q at column q_off (n_heads*hd wide), k at k_off and v at
+// v_off (n_kv*hd wide each).  q_out is [T, n_heads, hd] in the activation dtype.  A
+// cache plane is [pages, n_kv, page_tokens, hd]; position p of request r lies in page
+// table[r * table_stride + p / page_tokens] at slot p % page_tokens.
+// ---------------------------------------------------------------------------------
+template <typename TQ, typename TC>
+__global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, int v_off,
+                                     TQ* __restrict__ q_out, TC* __restrict__ kplane, TC* __restrict__ vplane,
+                                     const int* __restrict__ positions, const int* __restrict__ row_req,
+                                     const int* __restrict__ table, int table_stride, int page_tokens,
+                                     int n_heads, int n_kv, int hd, int rot, const float* __restrict__ inv_freq,
+                                     int write_kv) {
+    int t = blockIdx.x;
+    int slot = blockIdx.y;                 // [0, n_heads): q head; then k heads; then v heads
+    int pos = positions[t];
+    const float* row = qkv + (size_t)t * ld;
+    int half = rot >> 1;
+    if (slot < n_heads) {
+        const float* src = row + q_off + slot * hd;
+        TQ* dst = q_out + ((size_t)t * n_heads + slot) * hd;
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+            float v;
+            if (d < rot) {
+                int dd = d < half ? d : d - half;
+                float ang = (float)pos * inv_freq[dd];
+                float c = cosf(ang), s = sinf(ang);
+                float a = src[dd], b = src[dd + half];
+                v = d < half ? a * c - b * s : a * s + b * c;
+            } else {
+                v = src[d];
+            }
+            dst[d] = from_f32<TQ>(v);
+        }
+        return;
+    }
+    if (!write_kv) return;
+    int page = table[(size_t)row_req[t] * table_stride + pos / page_tokens];
+    if (page < 0) return;                  // no page: the host never schedules this
+    int in_page = pos % page_tokens;
+    if (slot < n_heads + n_kv) {
+        int kh = slot - n_heads;
+        const float* src = row + k_off + kh * hd;
+        TC* dst = kplane + (((size_t)page * n_kv + kh) * page_tokens + in_page) * hd;
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+            float v;
+            if (d < rot) {
+                int dd = d < half ? d : d - half;
+                float ang = (float)pos * inv_freq[dd];
+                float c = cosf(ang), s = sinf(ang);
+                float a = src[dd], b = src[dd + half];
+                v = d < half ? a * c - b * s : a * s + b * c;
+            } else {
+                v = src[d];
+            }
+            dst[d] = from_f32<TC>(v);
+        }
+    } else {
+        int kh = slot - n_heads - n_kv;
+        const float* src = row + v_off + kh * hd;
+        TC* dst = vplane + (((size_t)page * n_kv + kh) * page_tokens + in_page) * hd;
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = from_f32<TC>(src[d]);
+    }
+}
+
+CJ_EXPORT int cj_rope_kv_write(const float* qkv, int ld, int q_off, int k_off, int v_off, void* q_out, int q_dtype,
+                               void* kplane, void* vplane, int cache_dtype, const int* positions,
+                               const int* row_req, const int* table, int table_stride, int page_tokens, int T,
+                               int n_heads, int n_kv, int hd, int rotary_dim, const float* inv_freq, int write_kv,
+                               cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (!qkv || !q_out || !positions || n_heads <= 0 || hd <= 0) return CJ_ERR_ARG;
+    if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return CJ_ERR_SIZE;
+    if (rotary_dim > 0 && !inv_freq) return CJ_ERR_ARG;
+    if (write_kv && (!kplane || !vplane || !row_req || !table || page_tokens <= 0 || n_kv <= 0)) return CJ_ERR_ARG;
+    dim3 grid(T, n_heads + (write_kv ? 2 * n_kv : 0));
+    int threads = hd <= 32 ? 32 : (hd <= 64 ? 64 : 128);
+#define LAUNCH(TQ, TC)                                                                                          \
+    rope_kv_write_kernel<TQ, TC><<<grid, threads, 0, stream>>>(qkv, ld, q_off, k_off, v_off, (TQ*)q_out,        \
+        (TC*)kplane, (TC*)vplane, positions, row_req, table, table_stride, page_tokens, n_heads, n_kv, hd,      \
+        rotary_dim, inv_freq, write_kv)
+    if (q_dtype == CJ_F32 && cache_dtype == CJ_F32) LAUNCH(float, float);
+    else if (q_dtype == CJ_BF16 && cache_dtype == CJ_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else return CJ_ERR_DTYPE;
+#undef LAUNCH
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+// Combine of the mixture's outputs into the residual stream, per token and in a fixed
+// order: acc = sum_j w[t,j] * y[slot(t,j)] for j = 0..k-1 (selection order), then
+// acc += gate[t] * shared[t]; hs[t] += acc.  No atomics: one thread owns an element.
+// reference: model/MoeFfn.cajeta:1849-1916 (row form), combine kernel
+// io/QuantKernel.cajeta:40747; shared expert model/Prim.cajeta:1652-1664.
+// ---------------------------------------------------------------------------------
+__global__ void moe_combine_kernel(float* __restrict__ hs, const float* __restrict__ y, const int* __restrict__ slot_of_pick,
+                                   const float* __restrict__ w, int k, const float* __restrict__ shared,
+                                   const float* __restrict__ shared_scale, int H) {
+    int t = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < k; ++j) {
+            int s = slot_of_pick[t * k + j];
+            acc += w[t * k + j] * y[(size_t)s * H + i];
+        }
+        if (shared) {
+            float g = shared_scale ? shared_scale[t] : 1.0f;
+            acc += g * shared[(size_t)t * H + i];
+        }
+        hs[(size_t)t * H + i] += acc;
+    }
+}
+
+CJ_EXPORT int cj_moe_combine(float* hs, const float* y, const int* slot_of_pick, const float* w, int k,
+                             const float* shared, const float* shared_scale, int T, int H, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (!hs || H <= 0 || k < 0 || (k > 0 && (!y || !slot_of_pick || !w))) return CJ_ERR_ARG;
+    int threads = H >= 1024 ? 256 : 128;
+    moe_combine_kernel<<<T, threads, 0, stream>>>(hs, y, slot_of_pick, w, k, shared, shared_scale, H);
+    return launch_status();
+}

@@ -1,0 +1,193 @@
+"""The step function: one mixed batch of (request, its next tokens) through the model.
+
+A step holds, for each request in it, the next tokens of that request: a portion of a
+prompt of any length, or a single decoded token; portions and single tokens sit side
+by side and a prompt may be cut anywhere.  The step runs only these tokens, as one
+batch of rows, against what earlier steps left in the cache, and returns the float32
+logits at the wanted places.
+
+The reference has three entry points instead (one sequence ``stepSeq``, several prompt
+chunks ``stepPrefillBatch``, up to eight decode rows ``stepDecodeBatch``:
+model/CausalLM.cajeta:801-878,955-1066,4445-4512) and never mixes chunks with decode
+rows in one pass (sched/Scheduler.cajeta:572-573); here one call serves all of them.
+
+Rows are laid out request after request; each row carries its request's index in the
+step (``row_req``) and its absolute position, each request its first row, row count and
+the length it had before the step.  All of this plus the block-table rows of the
+step's requests goes to the device in one pinned buffer and one copy.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from .model import Model
+
+
+class OutOfPages(RuntimeError):
+    """The cache has too few free pages for this step; nothing was changed."""
+
+
+class StepError(ValueError):
+    """A step that cannot run: unknown slot, token id out of range, bad ``want``."""
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request and the places among them whose logits are wanted."""
+
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class EntryContext:
+    """What one schedule entry sees of the cache during a step."""
+
+    index: int
+    writes_cache: bool
+    k_plane: Optional[torch.Tensor]
+    v_plane: Optional[torch.Tensor]
+    block_table: Optional[torch.Tensor]      # int32 [requests, width] of the entry's group
+    page_tokens: int
+    state: Optional[torch.Tensor]            # [max_seqs, ...] per-request state of this entry
+
+
+@dataclass
+class StepContext:
+    """Metadata of one step, on the device and (``h_`` fields) on the host."""
+
+    n_rows: int
+    n_requests: int
+    token_ids: torch.Tensor        # int32 [rows]
+    positions: torch.Tensor        # int32 [rows] absolute position of each row
+    row_req: torch.Tensor          # int32 [rows] index of the row's request within the step
+    req_start: torch.Tensor        # int32 [requests + 1] first row of each request
+    req_prior: torch.Tensor        # int32 [requests] tokens cached before this step
+    req_slot: torch.Tensor         # int32 [requests] cache slot of each request
+    want_rows: torch.Tensor        # int32 [wanted] rows whose logits are returned
+    tables: List[torch.Tensor]     # per cache group: int32 [requests, width]
+    h_req_start: List[int] = field(default_factory=list)
+    h_req_prior: List[int] = field(default_factory=list)
+    h_req_slot: List[int] = field(default_factory=list)
+    max_rows_per_request: int = 0
+    max_context: int = 0           # longest prior + new over the step's requests
+    all_single: bool = False       # every request brings exactly one token
+
+
+class ModelRunner:
+    """Owns a model and its cache; ``step`` is the only way tokens reach the model."""
+
+    def __init__(self, model: Model, page_tokens: int = 16, max_seqs: int = 4, max_tokens_per_seq: int = 4096,
+                 num_pages: Optional[int] = None):
+        self.model = model
+        self.runtime = model.runtime
+        if num_pages is None:
+            num_pages = max_seqs * (-(-max_tokens_per_seq // page_tokens))
+        self.cache = CacheManager(model.kv_needs(), model.state_needs(), model.cache_from(), page_tokens, max_seqs,
+                                  max_tokens_per_seq, num_pages, self.runtime.cache_dtype, self.runtime.device)
+        self.page_tokens = page_tokens
+        self.steps_run = 0
+
+    # -- requests --------------------------------------------------------------------
+    def admit(self) -> Optional[int]:
+        return self.cache.admit()
+
+    def release(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    # -- the step --------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run one batch; returns float32 logits ``[wanted, vocab]`` in the order of the
+        entries and of each entry's ``want``.  Raises :class:`OutOfPages` (cache
+        unchanged) when the pages for the new tokens are not there."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.runtime.device)
+        ctx = self._prepare(entries)
+        hs = self.model.embed(ctx.token_ids)
+        for i, e in enumerate(self.model.plan.schedule):
+            k_plane, v_plane, group = self.cache.plane(i)
+            ectx = EntryContext(index=i, writes_cache=e.cache_from is None, k_plane=k_plane, v_plane=v_plane,
+                                block_table=ctx.tables[group] if group is not None else None,
+                                page_tokens=self.page_tokens, state=self.cache.state.get(i))
+            self.model.blocks[e.layer].forward(hs, ctx, ectx)
+        for e in entries:
+            self.cache.commit(e.slot, len(e.tokens))
+        self.steps_run += 1
+        if ctx.want_rows.numel() == 0:
+            return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.runtime.device)
+        return self.model.logits(hs, ctx.want_rows)
+
+    def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        cache = self.cache
+        vocab = self.model.vocab
+        slots = [e.slot for e in entries]
+        if len(set(slots)) != len(slots):
+            raise StepError("a request appears twice in one step")
+        # every check comes before the first change of the books
+        needs = []
+        for e in entries:
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            if toks.min() < 0 or toks.max() >= vocab:
+                bad = int(toks[(toks < 0) | (toks >= vocab)][0])
+                raise StepError(f"token id {bad} is outside the vocabulary [0, {vocab})")
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise StepError(f"want index {w} is outside the {len(e.tokens)} tokens of the entry")
+            needs.append(cache.pages_needed(e.slot, len(e.tokens)))
+        if not cache.books.fits(needs):
+            raise OutOfPages(f"step needs {[sum(n[g] for n in needs) for g in range(cache.num_groups)]} new pages per group; "
+                             f"free: {cache.free_pages()}")
+        for e in entries:
+            ok = cache.reserve(e.slot, len(e.tokens))
+            assert ok
+
+        R = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        n_want = sum(len(e.want) for e in entries)
+        width = cache.table_width(slots)
+        G = cache.num_groups
+        # one pinned int32 buffer: tokens | positions | row_req | req_start | req_prior | req_slot | want | tables
+        sizes = [T, T, T, R + 1, R, R, n_want] + [R * width] * G
+        offs = np.concatenate([[0], np.cumsum(sizes)])
+        host = torch.empty((int(offs[-1]),), dtype=torch.int32, pin_memory=True)
+        h = host.numpy()
+        req_start, req_prior = [0], []
+        row = 0
+        wi = 0
+        for r, e in enumerate(entries):
+            n = len(e.tokens)
+            prior = cache.length(e.slot)
+            h[offs[0] + row: offs[0] + row + n] = np.asarray(e.tokens, dtype=np.int32)
+            h[offs[1] + row: offs[1] + row + n] = np.arange(prior, prior + n, dtype=np.int32)
+            h[offs[2] + row: offs[2] + row + n] = r
+            for w in e.want:
+                h[offs[6] + wi] = row + w
+                wi += 1
+            req_prior.append(prior)
+            row += n
+            req_start.append(row)
+        h[offs[3]: offs[3] + R + 1] = req_start
+        h[offs[4]: offs[4] + R] = req_prior
+        h[offs[5]: offs[5] + R] = slots
+        for g in range(G):
+            h[offs[7 + g]: offs[7 + g] + R * width] = cache.table_rows(g, slots, width).reshape(-1)
+        dev = host.to(self.runtime.device, non_blocking=True)
+
+        def view(i: int) -> torch.Tensor:
+            return dev[int(offs[i]): int(offs[i + 1])]
+
+        return StepContext(
+            n_rows=T, n_requests=R, token_ids=view(0), positions=view(1), row_req=view(2), req_start=view(3),
+            req_prior=view(4), req_slot=view(5), want_rows=view(6),
+            tables=[view(7 + g).view(R, width) for g in range(G)],
+            h_req_start=req_start, h_req_prior=req_prior, h_req_slot=slots,
+            max_rows_per_request=max(len(e.tokens) for e in entries),
+            max_context=max(p + len(e.tokens) for p, e in zip(req_prior, entries)),
+            all_single=all(len(e.tokens) == 1 for e in entries))

@@ -1,0 +1,146 @@
+"""Feed-forward parts: the dense SwiGLU MLP and the sparse mixture of experts.
+
+``dense_swiglu``: ``W_d (silu(W_g x) * (W_u x))``, ``silu(x) = x / (1 + exp(-x))``
+(model/Prim.cajeta:1822-1847, model/CausalLM.cajeta:1556-1566).  Parameters:
+``hidden_size``, ``intermediate_size``.
+
+``sparse_moe``: router logits ``l_e = Wr[e] . x`` in float32, softmax over all experts,
+top-k by repeated strict-``>`` argmax (ties to the lower index), weights = the picked
+probabilities, optionally renormalised with the divisor clamped at 2^-14
+(model/MoeFfn.cajeta:908-988); each picked expert is a SwiGLU MLP of
+``expert_intermediate_size``, summed per token in selection order
+(model/MoeFfn.cajeta:1849-1916); an optional shared expert of
+``shared_intermediate_size`` is added, scaled by ``sigma(g . x)`` when it has a gate
+(model/MoeFfn.cajeta:1925-1964).  Tokens are grouped by expert with a counting sort and
+each expert multiplies its own rows (model/MoeFfn.cajeta:2064-2099,2644-2777).
+Parameters: ``hidden_size``, ``num_experts``, ``top_k``, ``expert_intermediate_size``,
+``shared_intermediate_size`` (0 = none), ``shared_gate``, ``norm_topk_prob``.
+
+The file stores one tensor per expert and projection
+(``experts.{e}.gate_proj.weight`` ...); they are stacked into ``[E, I, H]`` and
+``[E, H, I]`` slabs at load, as the reference binds merged slabs
+(model/ExpertBank.cajeta:243-308).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..csrc import kernels as K
+from .base import Part, register_part
+from .plan import ParamSpec
+
+
+@register_part("feed_forward", "dense_swiglu")
+class DenseSwiGLU(Part):
+    needs_f32_input = False
+
+    def __init__(self, spec, prefix, runtime):
+        super().__init__(spec, prefix, runtime)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.w_gate = self.w_up = self.w_down = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        return {
+            self.name("gate_proj.weight"): ParamSpec((self.inter, self.hidden)),
+            self.name("up_proj.weight"): ParamSpec((self.inter, self.hidden)),
+            self.name("down_proj.weight"): ParamSpec((self.hidden, self.inter)),
+        }
+
+    def load(self, source) -> None:
+        self.w_gate = self.fetch(source, self.name("gate_proj.weight"))
+        self.w_up = self.fetch(source, self.name("up_proj.weight"))
+        self.w_down = self.fetch(source, self.name("down_proj.weight"))
+
+    def forward(self, x: torch.Tensor, x_f32: Optional[torch.Tensor], residual: torch.Tensor, ctx) -> None:
+        T = x.shape[0]
+        act = torch.empty((T, self.inter), dtype=self.runtime.act_dtype, device=x.device)
+        K.gemm(x, self.w_gate, act, w_up=self.w_up)
+        K.gemm(act, self.w_down, residual, accumulate=True)
+
+
+@register_part("feed_forward", "sparse_moe")
+class SparseMoE(Part):
+    needs_f32_input = True      # the router reads the normed row in float32
+
+    def __init__(self, spec, prefix, runtime):
+        super().__init__(spec, prefix, runtime)
+        self.hidden = int(spec["hidden_size"])
+        self.num_experts = int(spec["num_experts"])
+        self.top_k = int(spec["top_k"])
+        self.inter = int(spec["expert_intermediate_size"])
+        self.shared_inter = int(spec.get("shared_intermediate_size", 0) or 0)
+        self.shared_gate = bool(spec.get("shared_gate", False)) and self.shared_inter > 0
+        self.norm_topk = bool(spec.get("norm_topk_prob", False))
+        if not 1 <= self.top_k <= self.num_experts:
+            raise ValueError(f"top_k must be between 1 and num_experts ({self.num_experts}), found {self.top_k}")
+        if self.num_experts > 1024:
+            raise ValueError(f"num_experts {self.num_experts} is more than the router kernel takes (1024)")
+        self.router = None
+        self.w_gate = self.w_up = self.w_down = None
+        self.ws_gate = self.ws_up = self.ws_down = None
+        self.shared_gate_w = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        p = {self.name("gate.weight"): ParamSpec((self.num_experts, self.hidden), role="vector")}
+        for e in range(self.num_experts):
+            p[self.name(f"experts.{e}.gate_proj.weight")] = ParamSpec((self.inter, self.hidden))
+            p[self.name(f"experts.{e}.up_proj.weight")] = ParamSpec((self.inter, self.hidden))
+            p[self.name(f"experts.{e}.down_proj.weight")] = ParamSpec((self.hidden, self.inter))
+        if self.shared_inter > 0:
+            p[self.name("shared_expert.gate_proj.weight")] = ParamSpec((self.shared_inter, self.hidden))
+            p[self.name("shared_expert.up_proj.weight")] = ParamSpec((self.shared_inter, self.hidden))
+            p[self.name("shared_expert.down_proj.weight")] = ParamSpec((self.hidden, self.shared_inter))
+            if self.shared_gate:
+                p[self.name("shared_expert_gate.weight")] = ParamSpec((1, self.hidden), role="vector")
+        return p
+
+    def load(self, source) -> None:
+        rt = self.runtime
+        self.router = self.fetch(source, self.name("gate.weight"))
+
+        def slab(proj: str, rows: int, cols: int) -> torch.Tensor:
+            out = torch.empty((self.num_experts, rows, cols), dtype=rt.matrix_dtype, device=rt.device)
+            for e in range(self.num_experts):
+                out[e].copy_(self.fetch(source, self.name(f"experts.{e}.{proj}.weight")))
+            return out
+
+        self.w_gate = slab("gate_proj", self.inter, self.hidden)
+        self.w_up = slab("up_proj", self.inter, self.hidden)
+        self.w_down = slab("down_proj", self.hidden, self.inter)
+        if self.shared_inter > 0:
+            self.ws_gate = self.fetch(source, self.name("shared_expert.gate_proj.weight"))
+            self.ws_up = self.fetch(source, self.name("shared_expert.up_proj.weight"))
+            self.ws_down = self.fetch(source, self.name("shared_expert.down_proj.weight"))
+            if self.shared_gate:
+                self.shared_gate_w = self.fetch(source, self.name("shared_expert_gate.weight")).reshape(-1).contiguous()
+
+    def forward(self, x: torch.Tensor, x_f32: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+        rt = self.runtime
+        dev = x.device
+        T = x.shape[0]
+        k, E = self.top_k, self.num_experts
+        sel = torch.empty((T, k), dtype=torch.int32, device=dev)
+        wts = torch.empty((T, k), dtype=torch.float32, device=dev)
+        shared_scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.shared_gate else None
+        K.router_topk(x_f32, self.router, self.shared_gate_w, k, self.norm_topk, sel, wts, shared_scale)
+
+        offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+        slot_token = torch.empty((T * k,), dtype=torch.int32, device=dev)
+        slot_of_pick = torch.empty((T * k,), dtype=torch.int32, device=dev)
+        K.moe_group(sel, k, E, offsets, slot_token, slot_of_pick)
+
+        act = torch.empty((T * k, self.inter), dtype=rt.act_dtype, device=dev)
+        K.gemm(x, self.w_gate, act, w_up=self.w_up, group_offsets=offsets, a_row_index=slot_token)
+        y = torch.empty((T * k, self.hidden), dtype=torch.float32, device=dev)
+        K.gemm(act, self.w_down, y, group_offsets=offsets)
+
+        shared = None
+        if self.shared_inter > 0:
+            sact = torch.empty((T, self.shared_inter), dtype=rt.act_dtype, device=dev)
+            K.gemm(x, self.ws_gate, sact, w_up=self.ws_up)
+            shared = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
+            K.gemm(sact, self.ws_down, shared)
+        K.moe_combine(residual, y, slot_of_pick, wts, k, shared, shared_scale)
