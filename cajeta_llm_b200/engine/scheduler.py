@@ -1,0 +1,316 @@
+"""Continuous batching above the step function.
+
+Policy, after the reference's scheduler (sched/Scheduler.cajeta:414-605):
+
+* states WAITING -> RUNNING -> DONE and RUNNING <-> PREEMPTED; finish reasons
+  NONE / BUDGET / EOS / STOP / CANCEL (sched/Request.cajeta:11-23);
+* admission at the start and at the end of every iteration: preempted requests first
+  (oldest preemption first), then waiters in submission order; a request needs a free
+  slot and pages for its whole uncached suffix plus one page of decode headroom per
+  cache group, counted against the free pages that running requests have not yet
+  claimed for their own prompts; admission stops at the first request that does not
+  fit, nothing is skipped (sched/Scheduler.cajeta:1068-1151);
+* every iteration is ONE mixed step under a token budget: the single decode tokens of
+  all running requests first, then prompt portions in admission order until the budget
+  is used; ``chunk`` > 0 also caps a portion (the reference gives each running request
+  one item of at most ``chunk`` tokens per iteration and runs them as separate model
+  calls, sched/Scheduler.cajeta:472-560);
+* when the pages for an item are not there, the YOUNGEST running request (latest
+  admission) is preempted: its pages are given back, it forgets what it had cached
+  and is later re-admitted ahead of new work and recomputed from its tokens (prompt
+  plus generated) through the same chunked path; if the youngest is the request
+  itself, it yields; if nothing can be preempted the request can never fit and the
+  scheduler raises (sched/Scheduler.cajeta:495-509,1263-1315);
+* a request finishes on a stop token (by default the engine's end-of-generation set)
+  -> EOS, or when it has generated ``max_new_tokens`` -> BUDGET; its slot and pages are
+  free for a request admitted in the same iteration (sched/Scheduler.cajeta:732-757,575).
+"""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Xorshift64
+from .step import StepEntry
+
+
+class RequestState(enum.Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    PREEMPTED = "preempted"
+    DONE = "done"
+
+
+class FinishReason(enum.Enum):
+    NONE = "none"
+    BUDGET = "budget"
+    EOS = "eos"
+    STOP = "stop"
+    CANCEL = "cancel"
+
+
+class SchedulerError(RuntimeError):
+    pass
+
+
+@dataclass
+class Request:
+    id: int
+    prompt: List[int]
+    params: SamplingParams
+    stop_tokens: Tuple[int, ...]
+    generated: List[int] = field(default_factory=list)
+    state: RequestState = RequestState.WAITING
+    finish_reason: FinishReason = FinishReason.NONE
+    slot: Optional[int] = None
+    cached_len: int = 0
+    admit_stamp: int = -1
+    preempt_stamp: int = -1
+    rng: Optional[Xorshift64] = None
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.prompt + self.generated
+
+    @property
+    def total_len(self) -> int:
+        return len(self.prompt) + len(self.generated)
+
+    @property
+    def is_done(self) -> bool:
+        return self.state == RequestState.DONE
+
+    def generated_count(self) -> int:
+        return len(self.generated)
+
+
+@dataclass
+class Counters:
+    admitted: int = 0
+    preempted: int = 0
+    resumed: int = 0
+    steps: int = 0
+    recomputed_tokens: int = 0
+    prefill_rows: int = 0
+    decode_rows: int = 0
+
+
+class Scheduler:
+    def __init__(self, runner, sampler, max_batch_tokens: int = 2048, chunk: int = 0,
+                 eog_token_ids: Sequence[int] = ()):
+        """``runner`` offers admit / release / step and a ``cache`` with pages_needed,
+        free_pages and length; ``sampler.sample(logits, params, rngs, histories)`` returns
+        one token per row."""
+        if max_batch_tokens < 1:
+            raise SchedulerError(f"max_batch_tokens must be >= 1, found {max_batch_tokens}")
+        self.runner = runner
+        self.sampler = sampler
+        self.max_batch_tokens = max_batch_tokens
+        self.chunk = chunk
+        self.eog_token_ids = tuple(eog_token_ids)
+        self.requests: Dict[int, Request] = {}
+        self.waiting: List[Request] = []
+        self.preempted: List[Request] = []
+        self.running: List[Request] = []
+        self.counters = Counters()
+        self.sink: Optional[Callable[[int, int], None]] = None
+        self._next_id = 0
+        self._stamp = 0
+
+    # -- submission ------------------------------------------------------------------
+    def submit(self, prompt: Sequence[int], params: SamplingParams) -> int:
+        if len(prompt) == 0:
+            raise SchedulerError("a request needs at least one prompt token")
+        stops = params.stop_token_ids if params.stop_token_ids is not None else self.eog_token_ids
+        r = Request(id=self._next_id, prompt=[int(t) for t in prompt], params=params, stop_tokens=tuple(stops),
+                    rng=Xorshift64(params.seed))
+        self._next_id += 1
+        self.requests[r.id] = r
+        self.waiting.append(r)
+        return r.id
+
+    def request(self, request_id: int) -> Request:
+        return self.requests[request_id]
+
+    def cancel(self, request_id: int) -> bool:
+        """Between steps; False when the request is done or unknown (sched/Scheduler.cajeta:293-313)."""
+        r = self.requests.get(request_id)
+        if r is None or r.state == RequestState.DONE:
+            return False
+        if r.state == RequestState.RUNNING:
+            self.runner.release(r.slot)
+            self.running.remove(r)
+        elif r.state == RequestState.WAITING:
+            self.waiting.remove(r)
+        else:
+            self.preempted.remove(r)
+        self._finish(r, FinishReason.CANCEL, release=False)
+        return True
+
+    @property
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.preempted or self.running)
+
+    # -- admission -------------------------------------------------------------------
+    def _claimed(self) -> List[int]:
+        """Pages per group that running requests still need for their known tokens."""
+        cache = self.runner.cache
+        total = [0] * len(cache.free_pages())
+        for r in self.running:
+            need = cache.pages_needed(r.slot, r.total_len - r.cached_len)
+            total = [a + b for a, b in zip(total, need)]
+        return total
+
+    def _admit_phase(self) -> None:
+        cache = self.runner.cache
+        while True:
+            queue = self.preempted if self.preempted else self.waiting
+            if not queue:
+                return
+            r = queue[0]
+            slot = self.runner.admit()
+            if slot is None:
+                return
+            need = cache.pages_needed(slot, r.total_len)
+            free = cache.free_pages()
+            claimed = self._claimed()
+            fits = all(n + 1 + c <= f for n, c, f in zip(need, claimed, free))
+            if not fits:
+                self.runner.release(slot)
+                if not self.running:
+                    # nothing runs, so every page is free: the request can never fit
+                    queue.pop(0)
+                    self._finish(r, FinishReason.CANCEL, release=False)
+                    raise SchedulerError(
+                        f"request {r.id} holds {r.total_len} tokens and can never fit the cache pool "
+                        f"({cache.free_pages()} free pages per group with nothing else running)")
+                return
+            queue.pop(0)
+            r.slot = slot
+            r.cached_len = 0
+            r.admit_stamp = self._stamp
+            self._stamp += 1
+            if r.state == RequestState.PREEMPTED:
+                self.counters.resumed += 1
+            self.counters.admitted += 1
+            r.state = RequestState.RUNNING
+            self.running.append(r)
+
+    # -- one iteration ---------------------------------------------------------------
+    def plan_step(self) -> List[Tuple[Request, int]]:
+        """(request, number of its next tokens) for this iteration: decode tokens first,
+        then prompt portions in admission order under the token budget; preempts the
+        youngest running request while the plan's pages are not there."""
+        cache = self.runner.cache
+        order = sorted(self.running, key=lambda r: r.admit_stamp)
+        decodes = [r for r in order if r.total_len - r.cached_len == 1]
+        prompts = [r for r in order if r.total_len - r.cached_len > 1]
+        plan: List[Tuple[Request, int]] = []
+        budget = self.max_batch_tokens
+        for r in decodes:
+            if budget < 1:
+                break
+            plan.append((r, 1))
+            budget -= 1
+        for r in prompts:
+            if budget < 1:
+                break
+            n = min(r.total_len - r.cached_len, budget)
+            if self.chunk > 0:
+                n = min(n, self.chunk)
+            plan.append((r, n))
+            budget -= n
+        # pages: walk the plan in order; when the pages run out preempt the youngest
+        while True:
+            free = cache.free_pages()
+            used = [0] * len(free)
+            short_at = None
+            for i, (r, n) in enumerate(plan):
+                need = cache.pages_needed(r.slot, n)
+                used = [a + b for a, b in zip(used, need)]
+                if any(u > f for u, f in zip(used, free)):
+                    short_at = i
+                    break
+            if short_at is None:
+                return plan
+            victim = max(self.running, key=lambda r: r.admit_stamp)
+            blocked = plan[short_at][0]
+            if victim is blocked and len(self.running) == 1:
+                raise SchedulerError(
+                    f"request {blocked.id} needs more pages than the pool holds even alone "
+                    f"({cache.pages_needed(blocked.slot, plan[short_at][1])} new, {free} free)")
+            self._preempt(victim)
+            plan = [(r, n) for r, n in plan if r is not victim]
+
+    def _preempt(self, r: Request) -> None:
+        self.runner.release(r.slot)
+        self.running.remove(r)
+        self.counters.preempted += 1
+        self.counters.recomputed_tokens += r.cached_len
+        r.slot = None
+        r.cached_len = 0
+        r.state = RequestState.PREEMPTED
+        r.preempt_stamp = self._stamp
+        self._stamp += 1
+        self.preempted.append(r)
+        self.preempted.sort(key=lambda q: q.preempt_stamp)
+
+    def step_once(self) -> int:
+        """One iteration; returns the number of tokens it ran."""
+        self._admit_phase()
+        if not self.running:
+            if self.has_work:
+                raise SchedulerError("requests are waiting but none can be admitted")
+            return 0
+        plan = self.plan_step()
+        if not plan:
+            return 0
+        entries, finishing = [], []
+        for r, n in plan:
+            toks = r.tokens[r.cached_len: r.cached_len + n]
+            completes = r.cached_len + n == r.total_len
+            entries.append(StepEntry(slot=r.slot, tokens=toks, want=[n - 1] if completes else []))
+            if completes:
+                finishing.append(r)
+            if n == 1 and completes and r.generated:
+                self.counters.decode_rows += 1
+            else:
+                self.counters.prefill_rows += n
+        logits = self.runner.step(entries)
+        for r, n in plan:
+            r.cached_len += n
+        self.counters.steps += 1
+        if finishing:
+            tokens = self.sampler.sample(logits, [r.params for r in finishing], [r.rng for r in finishing],
+                                         [r.generated for r in finishing])
+            for r, tok in zip(finishing, tokens):
+                self._consume(r, int(tok))
+        self._admit_phase()
+        return sum(n for _, n in plan)
+
+    def _consume(self, r: Request, token: int) -> None:
+        r.generated.append(token)
+        if self.sink is not None:
+            self.sink(r.id, token)
+        if token in r.stop_tokens:
+            self._finish(r, FinishReason.EOS)
+        elif len(r.generated) >= r.params.max_new_tokens:
+            self._finish(r, FinishReason.BUDGET)
+
+    def _finish(self, r: Request, reason: FinishReason, release: bool = True) -> None:
+        if release and r.slot is not None:
+            self.runner.release(r.slot)
+            self.running.remove(r)
+        r.slot = None
+        r.state = RequestState.DONE
+        r.finish_reason = reason
+
+    def run_all(self, max_steps: int = 0) -> int:
+        """Iterate until nothing is left (or ``max_steps`` iterations, 0 = no limit)."""
+        steps = 0
+        while self.has_work and (max_steps <= 0 or steps < max_steps):
+            self.step_once()
+            steps += 1
+        return steps

@@ -1,0 +1,160 @@
+"""Shared by the tests: the tiny configurations, model folders, the plain reference."""
+import functools
+import json
+import os
+import subprocess
+import sys
+from typing import Dict, List, Sequence
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# Two tiny configurations that differ in every size and option, and a third whose
+# explicit head_dim is not hidden / heads.
+TINY_A = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "vocab_size": 256,
+    "max_position_embeddings": 4096, "rms_norm_eps": 1e-6, "rope_theta": 10000.0,
+    "num_experts": 4, "num_experts_per_tok": 2, "moe_intermediate_size": 32,
+    "shared_expert_intermediate_size": 64, "norm_topk_prob": True,
+    "decoder_sparse_step": 1, "mlp_only_layers": [], "tie_word_embeddings": False,
+    "use_sliding_window": False, "sliding_window": 4096, "max_window_layers": 2, "eos_token_id": 255,
+}
+TINY_B = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "hidden_size": 96, "intermediate_size": 160, "num_hidden_layers": 3,
+    "num_attention_heads": 4, "num_key_value_heads": 1, "head_dim": 24, "vocab_size": 320,
+    "max_position_embeddings": 4096, "rms_norm_eps": 1e-5, "rope_theta": 1000000.0,
+    "num_experts": 6, "num_experts_per_tok": 3, "moe_intermediate_size": 48,
+    "shared_expert_intermediate_size": 80, "norm_topk_prob": False,
+    "decoder_sparse_step": 2, "mlp_only_layers": [0], "tie_word_embeddings": True,
+    "use_sliding_window": True, "sliding_window": 8, "max_window_layers": 1, "eos_token_id": [318, 319],
+}
+TINY_C = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "hidden_size": 80, "intermediate_size": 112, "num_hidden_layers": 2,
+    "num_attention_heads": 6, "num_key_value_heads": 3, "head_dim": 32, "vocab_size": 200,
+    "max_position_embeddings": 4096, "rms_norm_eps": 1e-6, "rope_theta": 50000.0,
+    "num_experts": 5, "num_experts_per_tok": 1, "moe_intermediate_size": 40,
+    "shared_expert_intermediate_size": 0, "norm_topk_prob": True,
+    "decoder_sparse_step": 1, "mlp_only_layers": [1], "tie_word_embeddings": False,
+    "use_sliding_window": True, "sliding_window": 20, "max_window_layers": 0,
+}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+SEEDS = {"A": 11, "B": 23, "C": 37}
+
+
+def write_model(model_dir: str, raw_config: dict, seed: int, store_dtype=torch.bfloat16) -> None:
+    """A model folder through the engine's random-weights mode."""
+    import cajeta_llm_b200  # noqa: F401
+    from cajeta_llm_b200.config import parse_config_dict
+    from cajeta_llm_b200.engine.model import build_model
+    from cajeta_llm_b200.parts.base import Runtime
+    from cajeta_llm_b200.weights.sources import write_model_folder
+
+    cfg = parse_config_dict(raw_config)
+    schema = build_model(cfg, Runtime("float32", device="cpu")).params()
+    write_model_folder(model_dir, cfg, schema, seed, store_dtype)
+
+
+def random_tokens(vocab: int, n: int, seed: int) -> List[int]:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+_plain_cache: Dict = {}
+
+
+def plain_logits(model_dir: str, tokens: Sequence[int]) -> torch.Tensor:
+    """Logits [T, vocab] of the plain implementation (float64 arithmetic), cached."""
+    import plain_qwen2moe as P
+
+    key = (model_dir, tuple(tokens))
+    if key not in _plain_cache:
+        if model_dir not in _plain_cache:
+            _plain_cache[model_dir] = P.read_model(model_dir)
+        config, weights = _plain_cache[model_dir]
+        _plain_cache[key] = P.forward(config, weights, list(tokens)).to(torch.float32)
+    return _plain_cache[key]
+
+
+# Tolerances.  float32: the engine differs from the float64 plain implementation by the
+# rounding of float32 sums (measured ~3e-7 on logits of size ~1).  bfloat16: activations
+# between kernels and the cache are rounded to 8 bits of mantissa; on these models the
+# logits differ by ~1e-2 at most (measured), against logits of size ~1.
+TOL = {"float32": dict(atol=2e-5, rtol=1e-4), "bfloat16": dict(atol=4e-2, rtol=4e-2)}
+
+
+def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = "") -> None:
+    tol = TOL[dtype]
+    diff = (got.double() - want.double()).abs()
+    bound = tol["atol"] + tol["rtol"] * want.double().abs()
+    if bool((diff > bound).any()):
+        i = int(torch.argmax(diff - bound))
+        r, c = divmod(i, got.shape[-1])
+        raise AssertionError(f"{what}: {int((diff > bound).sum())} of {got.numel()} logits differ; worst at row {r} "
+                             f"col {c}: got {got.reshape(-1)[i]:.6f} want {want.reshape(-1)[i]:.6f}; "
+                             f"first bad row {int(torch.nonzero((diff > bound).any(dim=-1))[0])}")
+
+
+def run_trace(model_dir: str, dtype: str, steps: List[dict], out_dir: str, max_tokens: int, extra: Sequence[str] = ()) -> Dict[int, np.ndarray]:
+    """Replay ``steps`` through ``bin/trace_run`` as a child process, one step at a time
+    (the next step is written only after ``done <step>`` came back)."""
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
+           "--out", out_dir, "--max-tokens", str(max_tokens)] + list(extra)
+    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
+    try:
+        for s in steps:
+            proc.stdin.write(json.dumps(s) + "\n")
+            proc.stdin.flush()
+            line = proc.stdout.readline().strip()
+            assert line == f"done {s['step']}", f"trace_run answered {line!r} to step {s['step']}"
+        proc.stdin.close()
+        assert proc.wait(timeout=120) == 0
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    with open(os.path.join(model_dir, "config.json")) as f:
+        vocab = json.load(f)["vocab_size"]
+    out = {}
+    for s in steps:
+        n = sum(len(e.get("want", [])) for e in s["entries"])
+        path = os.path.join(out_dir, f"{s['step']}.f32")
+        if n:
+            out[s["step"]] = np.fromfile(path, dtype="<f4").reshape(n, vocab)
+        else:
+            assert not os.path.exists(path)
+    return out
+
+
+class DictWeights:
+    """A weight source over a dict of host tensors (tests build parts from it)."""
+
+    def __init__(self, tensors):
+        self.tensors = tensors
+
+    def check(self, schema):
+        from cajeta_llm_b200.weights.sources import check_schema
+        check_schema(schema, {n: tuple(t.shape) for n, t in self.tensors.items()}, "test weights")
+
+    def get(self, name, spec):
+        return self.tensors[name]
+
+    def close(self):
+        pass
+
+
+def random_weights_for(part, seed, store_dtype=torch.bfloat16):
+    """Random host tensors for everything ``part.params()`` declares (stored dtype rounding applied)."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, spec in part.params().items():
+        if spec.init == "ones":
+            t = 1.0 + 0.1 * torch.randn(spec.shape, generator=g)
+        else:
+            t = torch.randn(spec.shape, generator=g) * 0.08
+        out[name] = t.to(store_dtype)
+    return out

@@ -1,0 +1,137 @@
+"""The cache manager's books: pages, block tables, windows, slots (no GPU)."""
+import random
+
+import pytest
+from hypothesis import given, settings, strategies as st
+
+from cajeta_llm_b200.cache.manager import CacheManager
+from cajeta_llm_b200.cache.pages import CacheBooks, CacheError, GroupSpec, PageAllocator
+from cajeta_llm_b200.parts.base import KvNeed, StateNeed
+
+
+def test_allocator_refuses_double_free_and_exhaustion():
+    a = PageAllocator(3)
+    p = a.take(2)
+    assert a.take(2) is None and a.free_count == 1          # all or nothing
+    a.give_back(p)
+    with pytest.raises(CacheError, match="freed twice"):
+        a.give_back([p[0]])
+    a.check()
+
+
+def books(pages=8, window=0, page_tokens=4, max_seqs=3, ctx=64):
+    groups = [GroupSpec(2, 16, 0)] + ([GroupSpec(2, 16, window)] if window else [])
+    return CacheBooks(groups, [pages] * len(groups), page_tokens, max_seqs, ctx)
+
+
+def test_page_drawn_only_at_a_boundary_and_released_pages_are_reused():
+    b = books()
+    s = b.admit()
+    assert b.pages_needed(s, 4) == [1] and b.reserve(s, 4)
+    b.commit(s, 4)
+    assert b.pages_needed(s, 1) == [1]                       # position 4 opens page 1
+    assert b.reserve(s, 1)
+    b.commit(s, 1)
+    assert b.pages_needed(s, 3) == [0]                       # positions 5..7 stay in page 1
+    held = b.groups[0].held_pages(s)
+    b.release(s)
+    assert b.free_pages() == [8]
+    s2 = b.admit()
+    assert b.length[s2] == 0                                 # a recycled slot starts at position 0
+    b.reserve(s2, 8)
+    assert set(b.groups[0].held_pages(s2)) & set(held)      # the freed pages are used again
+    b.check()
+
+
+def test_reserve_is_all_or_nothing_across_groups():
+    b = CacheBooks([GroupSpec(2, 16, 0), GroupSpec(1, 8, 0)], [4, 2], 4, 2, 64)
+    s = b.admit()
+    assert not b.reserve(s, 12)                              # group 1 has only 2 pages
+    assert b.free_pages() == [4, 2] and b.groups[0].held_pages(s) == []
+    assert b.reserve(s, 8)
+    b.check()
+
+
+def test_window_pages_are_given_back_once_the_window_has_passed_them():
+    b = books(pages=8, window=6, page_tokens=4)
+    s = b.admit()
+    assert b.reserve(s, 9)
+    b.commit(s, 9)          # next token 9 reads keys [4, 9]: page 0 (positions 0..3) is dead in the window group
+    assert len(b.groups[0].held_pages(s)) == 3 and len(b.groups[1].held_pages(s)) == 2
+    assert b.groups[1].table[s, 0] == -1 and b.groups[1].table[s, 1] >= 0
+    for _ in range(20):
+        assert b.reserve(s, 1)
+        b.commit(s, 1)
+        L = int(b.length[s])
+        live_from = (L + 1 - 6) // 4
+        assert int(b.groups[1].first_live[s]) == live_from
+        assert len(b.groups[1].held_pages(s)) <= 3          # ceil((w - 1) / P) + 1 pages at most
+        b.check()
+    b.release(s)
+    assert b.free_pages() == [8, 8]
+
+
+def test_limits_and_misuse():
+    b = books(ctx=8)
+    s = b.admit()
+    with pytest.raises(CacheError, match="limit"):
+        b.reserve(s, 9)
+    with pytest.raises(CacheError, match="without reserved pages"):
+        b.commit(s, 5)
+    with pytest.raises(CacheError, match="holds no request"):
+        b.reserve(2, 1)
+    b.release(s)
+    with pytest.raises(CacheError, match="holds no request"):
+        b.release(s)
+    assert [b.admit() is not None for _ in range(4)] == [True, True, True, False]
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(0, 2 ** 31), st.sampled_from([0, 5, 9]), st.sampled_from([2, 4, 16]))
+def test_random_orders_lose_no_page(seed, window, page_tokens):
+    rng = random.Random(seed)
+    b = books(pages=12, window=window, page_tokens=page_tokens, max_seqs=4, ctx=40)
+    live = {}
+    for _ in range(120):
+        op = rng.random()
+        if op < 0.25 and b.free_slots:
+            s = b.admit()
+            live[s] = 0
+        elif op < 0.85 and live:
+            s = rng.choice(list(live))
+            n = rng.randint(1, 9)
+            if live[s] + n > 40:
+                continue
+            need = b.pages_needed(s, n)
+            free = b.free_pages()
+            ok = b.reserve(s, n)
+            assert ok == all(x <= f for x, f in zip(need, free))
+            if ok:
+                b.commit(s, n)
+                live[s] += n
+                assert int(b.length[s]) == live[s]
+            else:
+                assert b.free_pages() == free
+        elif live:
+            s = rng.choice(list(live))
+            b.release(s)
+            del live[s]
+        b.check()
+        for g in b.groups:
+            assert g.allocator.free_count + sum(len(g.held_pages(s)) for s in live) == g.allocator.num_pages
+    for s in list(live):
+        b.release(s)
+    assert all(f == 12 for f in b.free_pages())
+
+
+def test_manager_groups_layers_by_their_needs():
+    full, win = KvNeed(2, 16, 0), KvNeed(2, 16, 8)
+    m = CacheManager([full, win, full, win, None], [None, None, None, None, StateNeed((3,))], [None, None, None, 1, None],
+                     page_tokens=4, max_seqs=2, max_tokens_per_seq=32, num_pages=6, cache_dtype=None, device=None)
+    assert m.num_groups == 2
+    assert m.entry_group == [0, 1, 0, 1, None]
+    assert m.entry_plane == [0, 0, 1, 0, None]               # entry 3 reads entry 1's plane
+    with pytest.raises(CacheError, match="caches nothing"):
+        CacheManager([None, full], [None, None], [None, 0], 4, 2, 32, 6, None, None)
+    with pytest.raises(CacheError, match="window"):
+        CacheManager([win, full], [None, None], [None, 0], 4, 2, 32, 6, None, None)

@@ -1,0 +1,193 @@
+"""The engine in one process: the first tokens of a sequence, long decoding, greedy and
+sampled generation through the entry point, scarce pages, and the command line."""
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import helpers
+import plain_qwen2moe as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def runner_for(model_dir, dtype, **kw):
+    import cajeta_llm_b200  # noqa: F401
+    from cajeta_llm_b200.engine.model import load_model
+    from cajeta_llm_b200.engine.step import ModelRunner
+    from cajeta_llm_b200.parts.base import Runtime
+    model, _ = load_model(model_dir, Runtime(dtype, device=DEV))
+    return ModelRunner(model, **kw)
+
+
+def engine_for(model_dir, dtype="float32", **kw):
+    from cajeta_llm_b200.engine.llm_engine import LlmEngine
+    from cajeta_llm_b200.engine.options import EngineOptions
+    return LlmEngine.load(EngineOptions(model=model_dir, dtype=dtype, **kw))
+
+
+def plain_greedy(model_dir, prompt, n, stop=()):
+    toks = list(prompt)
+    out = []
+    for _ in range(n):
+        t = P.argmax_first(helpers.plain_logits(model_dir, toks)[-1])
+        toks.append(t)
+        out.append(t)
+        if t in stop:
+            break
+    return out
+
+
+class PlainXorshift:
+    """The request's random stream, restated: x ^= x << 13; x ^= x >> 7; x ^= x << 17 on 64
+    bits; the uniform number is the top 24 bits over 2^24."""
+
+    def __init__(self, seed):
+        self.x = seed & (2 ** 64 - 1) or 0x9E3779B97F4A7C15
+
+    def unit(self):
+        x = self.x
+        x ^= (x << 13) & (2 ** 64 - 1)
+        x ^= x >> 7
+        x ^= (x << 17) & (2 ** 64 - 1)
+        self.x = x
+        return (x >> 40) / 2.0 ** 24
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_of_a_sequence(name, dtype, model_dirs):
+    from cajeta_llm_b200.engine.step import StepEntry
+    r = runner_for(model_dirs[name], dtype, page_tokens=16, max_seqs=4, max_tokens_per_seq=64)
+    vocab = helpers.CONFIGS[name]["vocab_size"]
+    for n in (1, 2, 3):
+        toks = helpers.random_tokens(vocab, n, seed=n)
+        s = r.admit()
+        got = r.step([StepEntry(s, toks, list(range(n)))]).cpu()
+        helpers.assert_close(got, helpers.plain_logits(model_dirs[name], toks), dtype, f"{n} tokens")
+        r.release(s)
+    # token by token from the very first one
+    toks = helpers.random_tokens(vocab, 5, seed=9)
+    s = r.admit()
+    got = torch.cat([r.step([StepEntry(s, [t], [0])]) for t in toks]).cpu()
+    helpers.assert_close(got, helpers.plain_logits(model_dirs[name], toks), dtype, "one by one")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_across_many_pages(dtype, model_dirs):
+    from cajeta_llm_b200.engine.step import StepEntry
+    name = "B"                                              # a full layer and two windowed ones
+    vocab = helpers.CONFIGS[name]["vocab_size"]
+    toks = helpers.random_tokens(vocab, 230, seed=21)
+    r = runner_for(model_dirs[name], dtype, page_tokens=16, max_seqs=2, max_tokens_per_seq=256)
+    s = r.admit()
+    outs = [r.step([StepEntry(s, toks[:6], [5])])]
+    for t in toks[6:]:
+        outs.append(r.step([StepEntry(s, [t], [0])]))
+    got = torch.cat(outs).cpu()
+    want = helpers.plain_logits(model_dirs[name], toks)[5:]
+    helpers.assert_close(got, want, dtype, "long decoding")
+    books = r.cache.books
+    assert len(books.groups[0].held_pages(s)) == 15         # 230 tokens in pages of 16
+    assert len(books.groups[1].held_pages(s)) <= 2          # the windowed layers gave their pages back
+    books.check()
+
+
+def test_greedy_generation_through_the_entry_point(model_dirs):
+    """configs[0]'s workload: prompts of 5, 9 and 17 tokens, 8 greedy steps each."""
+    from cajeta_llm_b200.sampling.params import SamplingParams
+    eng = engine_for(model_dirs["A"], "float32", ctx=64, max_seqs=4)
+    vocab = helpers.TINY_A["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, seed=30 + n) for n in (5, 9, 17)]
+    got = eng.generate(prompts, SamplingParams(max_new_tokens=8, stop_token_ids=()))
+    for p, g in zip(prompts, got):
+        assert g == plain_greedy(model_dirs["A"], p, 8)
+    assert eng.eog_tokens() == (255,) and eng.is_eog(255) and not eng.is_eog(3)
+    # the end-of-generation set is the default stop set
+    first = got[0][2]
+    rid = eng.submit_tokens(prompts[0], 8, SamplingParams(stop_token_ids=(first,)))
+    eng.run_all()
+    req = eng.request(rid)
+    assert req.generated == got[0][:got[0].index(first) + 1] and req.finish_reason.value == "eos"
+    eng.close()
+
+
+def test_sampled_generation_in_a_mixed_batch_follows_the_plain_sampler(model_dirs):
+    """configs[1]'s workload: 4 requests with prompts of 3, 12, 20 and 31 tokens, prefill
+    portions of 7, temperature 0.8, 10 steps; each request has its own random stream."""
+    from cajeta_llm_b200.sampling.params import SamplingParams
+    eng = engine_for(model_dirs["B"], "float32", ctx=64, max_seqs=4, chunk=7)
+    vocab = helpers.TINY_B["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, seed=40 + n) for n in (3, 12, 20, 31)]
+    params = [SamplingParams(temperature=0.8, seed=100 + i, max_new_tokens=10, stop_token_ids=(),
+                             top_k=(0, 30, 0, 12)[i], top_p=(0.0, 0.0, 0.9, 0.95)[i],
+                             repeat_penalty=(1.0, 1.0, 1.0, 1.2)[i]) for i in range(4)]
+    got = eng.generate(prompts, params)
+    steps = eng.scheduler().counters.steps
+    assert steps >= 10 + 4 and eng.scheduler().counters.preempted == 0
+    for p, sp, g in zip(prompts, params, got):
+        rng = PlainXorshift(sp.seed)
+        toks, out = list(p), []
+        for _ in range(10):
+            dist = P.prepared_distribution(helpers.plain_logits(model_dirs["B"], toks)[-1], sp.temperature, sp.top_k,
+                                           sp.top_p, sp.repeat_penalty, out)
+            t = P.draw(dist, rng.unit())
+            toks.append(t)
+            out.append(t)
+        assert g == out
+    eng.close()
+
+
+def test_scarce_pages_preempt_recompute_and_match_solo(model_dirs):
+    from cajeta_llm_b200.sampling.params import SamplingParams
+    vocab = helpers.TINY_A["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, seed=50 + n) for n in (20, 26, 9)]
+    sp = SamplingParams(max_new_tokens=24, stop_token_ids=())
+    solo = []
+    for p in prompts:
+        eng = engine_for(model_dirs["A"], "float32", ctx=64, max_seqs=1)
+        solo.append(eng.generate([p], sp)[0])
+        eng.close()
+    eng = engine_for(model_dirs["A"], "float32", ctx=64, max_seqs=3, block_tokens=4, num_blocks=22, max_batch_tokens=16)
+    got = eng.generate(prompts, sp)
+    c = eng.scheduler().counters
+    assert c.preempted >= 1 and c.resumed == c.preempted and c.recomputed_tokens > 0
+    assert got == solo
+    assert eng.runner.cache.free_pages() == [22]
+    eng.runner.cache.books.check()
+    eng.close()
+
+
+def test_step_refuses_bad_input_without_touching_the_cache(model_dirs):
+    from cajeta_llm_b200.engine.step import OutOfPages, StepEntry, StepError
+    r = runner_for(model_dirs["A"], "float32", page_tokens=16, max_seqs=2, max_tokens_per_seq=64, num_pages=2)
+    s = r.admit()
+    with pytest.raises(StepError, match="vocabulary"):
+        r.step([StepEntry(s, [1, 256], [])])
+    with pytest.raises(StepError, match="want"):
+        r.step([StepEntry(s, [1, 2], [2])])
+    with pytest.raises(OutOfPages):
+        r.step([StepEntry(s, list(range(40)), [])])
+    assert r.cache.free_pages() == [2] and r.cache.length(s) == 0
+    r.step([StepEntry(s, list(range(32)), [])])
+    with pytest.raises(OutOfPages):
+        r.step([StepEntry(s, [5], [0])])
+    assert r.cache.length(s) == 32
+
+
+def test_command_line(model_dirs, tmp_path):
+    vocab = helpers.TINY_A["vocab_size"]
+    prompt = helpers.random_tokens(vocab, 6, seed=60)
+    cmd = [sys.executable, "-m", "cajeta_llm_b200", "run", "--model", model_dirs["A"], "--prompt",
+           " ".join(map(str, prompt)), "-n", "5", "--dtype", "float32", "--ctx", "64", "--block-size", "16", "--verbose"]
+    out = subprocess.run(cmd, capture_output=True, text=True, cwd=helpers.ROOT, timeout=300)
+    assert out.returncode == 0, out.stderr
+    lines = out.stdout.strip().splitlines()
+    want = plain_greedy(model_dirs["A"], prompt, 5, stop=(255,))
+    assert lines[0].split() == [str(t) for t in want if t != 255]
+    assert lines[1] == f"[{len(want)} tokens, {'eos' if want[-1] == 255 else 'budget'}]"
+    bad = subprocess.run([sys.executable, "-m", "cajeta_llm_b200", "run", "--model", model_dirs["A"], "--frobnicate"],
+                         capture_output=True, text=True, cwd=helpers.ROOT, timeout=300)
+    assert bad.returncode == 2 and "unknown flag '--frobnicate'" in bad.stderr

@@ -1,0 +1,151 @@
+"""Trace replay through ``bin/trace_run`` against the plain implementation.
+
+The same requests are replayed whole; with most of the prompt in one step and the last
+32 tokens one by one; in portions of changing size down to two tokens; and mixed, up to
+four live requests, portions of some beside single tokens of others, in a pool so small
+that pages are used again.  Every wanted position of every mode is compared with the
+plain implementation, in float32 and in bfloat16.
+"""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def round64(n):
+    return -(-n // 64) * 64
+
+
+class TraceBuilder:
+    """Collects steps and remembers which (request, position) each output row is."""
+
+    def __init__(self):
+        self.steps = []
+        self.rows = {}          # step -> [(rid, position)]
+        self.progress = {}      # rid -> tokens fed so far
+        self.peak = 0
+
+    def step(self, parts, end=()):
+        """parts: [(rid, tokens, want_indices)]"""
+        n = len(self.steps)
+        entries, rows = [], []
+        for rid, toks, want in parts:
+            base = self.progress.get(rid, 0)
+            entries.append({"id": rid, "tokens": list(toks), "want": list(want)})
+            rows += [(rid, base + w) for w in want]
+            self.progress[rid] = base + len(toks)
+        self.peak = max(self.peak, sum(round64(v) for v in self.progress.values()))
+        for rid in end:
+            del self.progress[rid]
+        self.steps.append({"step": n, "entries": entries, "end": list(end)})
+        self.rows[n] = rows
+
+
+def add_whole(tb, rid, toks):
+    tb.step([(rid, toks, range(len(toks)))], end=[rid])
+
+
+def add_decode_tail(tb, rid, toks, tail=32):
+    head = len(toks) - tail
+    tb.step([(rid, toks[:head], range(head))])
+    for i in range(head, len(toks)):
+        tb.step([(rid, [toks[i]], [0])], end=[rid] if i == len(toks) - 1 else [])
+
+
+def add_chunks(tb, rid, toks, sizes):
+    i = 0
+    for k, n in enumerate(sizes):
+        last = i + n >= len(toks)
+        tb.step([(rid, toks[i:i + n], range(len(toks[i:i + n])))], end=[rid] if last else [])
+        i += n
+        if last:
+            return
+    raise AssertionError("sizes do not cover the request")
+
+
+def add_mixed(tb, requests, seed, max_live=4):
+    """Up to ``max_live`` requests at a time; each first gets its prompt in portions of
+    2..11 tokens, then its last tokens one by one; a request may sit a step out."""
+    rng = random.Random(seed)
+    waiting = list(requests.items())
+    live = {}
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            rid, toks = waiting.pop(0)
+            live[rid] = [toks, 0, max(2, len(toks) - rng.randint(3, 12))]     # tokens, fed, where single tokens begin
+        parts, ending = [], []
+        for rid, st in list(live.items()):
+            toks, fed, single_from = st
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                                                       # left out of this step
+            if fed < single_from:
+                n = min(rng.randint(2, 11), single_from - fed)
+                if single_from - fed - n == 1:
+                    n += 1                                                     # never leave a portion of one prompt token
+            else:
+                n = 1
+            parts.append((rid, toks[fed:fed + n], range(n)))
+            st[1] = fed + n
+            if st[1] == len(toks):
+                ending.append(rid)
+                del live[rid]
+        if parts:
+            tb.step(parts, end=ending)
+
+
+def build_trace(vocab, seed):
+    tb = TraceBuilder()
+    expect = {}
+    lens = {"w0": 45, "w1": 70, "d0": 50, "d1": 41, "c0": 61, "c1": 37}
+    toks = {rid: helpers.random_tokens(vocab, n, seed + i) for i, (rid, n) in enumerate(lens.items())}
+    add_whole(tb, "w0", toks["w0"])
+    add_whole(tb, "w1", toks["w1"])
+    add_decode_tail(tb, "d0", toks["d0"])
+    add_decode_tail(tb, "d1", toks["d1"])
+    add_chunks(tb, "c0", toks["c0"], [7, 2, 16, 3, 2, 9, 5, 2, 15])
+    add_chunks(tb, "c1", toks["c1"], [2, 2, 17, 16])
+    mixed = {f"m{i}": helpers.random_tokens(vocab, n, seed + 100 + i)
+             for i, n in enumerate([23, 48, 17, 64, 35, 29, 52, 20, 41])}
+    add_mixed(tb, mixed, seed)
+    toks.update(mixed)
+    return tb, toks
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_replay_every_way_of_cutting_matches_the_plain_implementation(name, dtype, model_dirs, tmp_path):
+    vocab = helpers.CONFIGS[name]["vocab_size"]
+    tb, toks = build_trace(vocab, seed=5 + ord(name))
+    assert tb.peak <= 4 * 64 + 64
+    # the pool holds exactly the peak: the mixed part frees and reuses pages all the time
+    out = helpers.run_trace(model_dirs[name], dtype, tb.steps, str(tmp_path), max_tokens=tb.peak)
+    worst = 0.0
+    for s in tb.steps:
+        rows = tb.rows[s["step"]]
+        if not rows:
+            continue
+        got = torch.from_numpy(out[s["step"]].copy())
+        want = torch.stack([helpers.plain_logits(model_dirs[name], toks[rid])[pos] for rid, pos in rows])
+        helpers.assert_close(got, want, dtype, f"{name} {dtype} step {s['step']} rows {rows[:4]}...")
+        worst = max(worst, float((got - want).abs().max()))
+    print(f"\n{name} {dtype}: {len(tb.steps)} steps, worst |diff| {worst:.3e}")
+
+
+def test_replay_writes_nothing_when_nothing_is_wanted_and_reuses_ids(model_dirs, tmp_path):
+    vocab = helpers.CONFIGS["A"]["vocab_size"]
+    t = helpers.random_tokens(vocab, 30, 77)
+    steps = [
+        {"step": 0, "entries": [{"id": "x", "tokens": t[:20], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": "x", "tokens": t[20:], "want": [9]}], "end": ["x"]},
+        {"step": 2, "entries": [{"id": "x", "tokens": t[:30], "want": [29]}], "end": ["x"]},      # the id comes back, empty
+    ]
+    out = helpers.run_trace(model_dirs["A"], "float32", steps, str(tmp_path), max_tokens=64)
+    assert set(out) == {1, 2}
+    want = helpers.plain_logits(model_dirs["A"], t)[29:30]
+    helpers.assert_close(torch.from_numpy(out[1].copy()), want, "float32", "after an unwanted portion")
+    assert np.array_equal(out[1], out[2])
