@@ -1,0 +1,302 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen1.5-MoE-A2.7B sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+A "step" is one decode step of a batch of 8 requests (each holding a 512-token prompt
+in a 4096-token context, 16-token pages), random weights, random token ids.  One JSON
+line is printed:
+
+* ``value``: decoded tokens a second, timed on the device over K steps after W warm-up
+  steps (the step function plus the greedy pick);
+* ``e2e``: the same through ``LlmEngine`` (host token ids in, host token ids out every
+  step, scheduler included);
+* ``prefill``: one step of 2,048 prompt tokens, with the fraction of the bf16 peak;
+* ``roofline``: bytes a decode step must read (every weight it uses once, the cache of
+  the live requests) over its time, against the measured copy bandwidth;
+* ``points``: decode tokens a second at batch 1 and 64.
+
+Every timed region reads far more than the 126 MB of L2 (a decode step reads the
+model's weights, GBs), so no L2 flush is needed between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Qwen1.5-MoE-A2.7B sizes
+A27B = {
+    "architectures": ["Qwen2MoeForCausalLM"], "hidden_size": 2048, "intermediate_size": 5632, "num_hidden_layers": 24,
+    "num_attention_heads": 16, "num_key_value_heads": 16, "head_dim": 128, "vocab_size": 151936,
+    "max_position_embeddings": 8192, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "num_experts": 60,
+    "num_experts_per_tok": 4, "moe_intermediate_size": 1408, "shared_expert_intermediate_size": 5632,
+    "norm_topk_prob": False, "decoder_sparse_step": 1, "mlp_only_layers": [], "tie_word_embeddings": False,
+    "use_sliding_window": False,
+}
+CTX, PROMPT, PAGE, BATCH, PREFILL_TOKENS = 4096, 512, 16, 8, 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+        except (OSError, ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_numbers(cfg, n_layers):
+    """Bytes and flops from the configuration (bf16 weights)."""
+    H, V = cfg["hidden_size"], cfg["vocab_size"]
+    qd = cfg["num_attention_heads"] * cfg["head_dim"]
+    kvd = cfg["num_key_value_heads"] * cfg["head_dim"]
+    E, k, Ie, Is = cfg["num_experts"], cfg["num_experts_per_tok"], cfg["moe_intermediate_size"], cfg["shared_expert_intermediate_size"]
+    per_layer_fixed = 2 * (H * (qd + 2 * kvd) + qd * H + 3 * H * Is) + 4 * (E * H + H + (qd + 2 * kvd) + 2 * H)
+    per_expert = 2 * 3 * H * Ie
+    head = 2 * V * H + 4 * H
+    kv_per_token = 2 * 2 * kvd * n_layers
+
+    def prefill_flops(T):
+        lin = 2 * T * (H * (qd + 2 * kvd) + qd * H + E * H + k * 3 * H * Ie + 3 * H * Is + H)
+        att = 4 * cfg["num_attention_heads"] * cfg["head_dim"] * T * (T + 1) // 2
+        return n_layers * (lin + att) + 2 * V * H
+
+    return dict(per_layer_fixed=per_layer_fixed, per_expert=per_expert, head=head, kv_per_token=kv_per_token,
+                prefill_flops=prefill_flops, H=H)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
+    ap.add_argument("--quick", action="store_true", help="skip the batch-1/64 points and the end-to-end arm")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "jklappenbach/cajeta-llm is cajeta-language source with no Python or C++ build (pip: 'neither setup.py "
+                          "nor pyproject.toml found') and the cajeta toolchain is not on this machine"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+
+    import numpy as np
+    import torch
+
+    import cajeta_llm_b200  # noqa: F401
+    from cajeta_llm_b200.csrc import kernels as K
+    from cajeta_llm_b200.engine.llm_engine import LlmEngine
+    from cajeta_llm_b200.engine.options import EngineOptions
+    from cajeta_llm_b200.engine.step import StepEntry
+    from cajeta_llm_b200.sampling.params import SamplingParams
+
+    cfg = dict(A27B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers > 0:
+        cfg["num_hidden_layers"] = min(args.layers, full_layers)
+    n_layers = cfg["num_hidden_layers"]
+    pk = peaks()
+    nums = model_numbers(cfg, n_layers)
+    max_b = 64 if not args.quick else BATCH
+    # pool: 64 requests of 512 + generated tokens, or 8 at the full context, whichever is larger
+    tokens_needed = max(max_b * (PROMPT + 2 * (warmup + steps) + 64), BATCH * (PROMPT + 256), PREFILL_TOKENS + 64)
+    opts = EngineOptions(config=cfg, random_weights=True, seed=1234, dtype="bfloat16", ctx=CTX, max_seqs=max_b,
+                         block_tokens=PAGE, num_blocks=-(-tokens_needed // PAGE) + max_b, max_batch_tokens=4096)
+    t0 = time.time()
+    engine = LlmEngine.load(opts)
+    torch.cuda.synchronize()
+    load_s = time.time() - t0
+    runner = engine.runner
+    vocab = cfg["vocab_size"]
+    rng = np.random.default_rng(7)
+
+    def prompts(n, length):
+        return [rng.integers(0, vocab, size=length).tolist() for _ in range(n)]
+
+    def event_ms(fn, reps=1):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b)
+
+    def decode_run(batch, n_warm, n_steps, sample_clocks=False):
+        """Prefill ``batch`` prompts, then time ``n_steps`` decode steps on the device."""
+        slots = [runner.admit() for _ in range(batch)]
+        ps = prompts(batch, PROMPT)
+        per_step = max(1, 4096 // PROMPT)
+        for i in range(0, batch, per_step):
+            runner.step([StepEntry(s, p, []) for s, p in zip(slots[i:i + per_step], ps[i:i + per_step])])
+        picks = torch.empty((batch,), dtype=torch.int32, device=runner.runtime.device)
+        toks = rng.integers(0, vocab, size=(n_warm + n_steps, batch))
+
+        def one(i):
+            logits = runner.step([StepEntry(s, [int(toks[i, j])], [0]) for j, s in enumerate(slots)])
+            K.argmax(logits, picks)
+
+        for i in range(n_warm):
+            one(i)
+        clocks = ClockSampler()
+        if sample_clocks:
+            clocks.start()
+        launches0 = K.launches
+        it = iter(range(n_warm, n_warm + n_steps))
+        ms = event_ms(lambda: one(next(it)), reps=n_steps)
+        launches = K.launches - launches0
+        clock_info = clocks.stop() if sample_clocks else None
+        # bytes the last step had to read
+        distinct = 0
+        for blk in runner.model.blocks:
+            off = getattr(blk.feed_forward, "last_offsets", None)
+            if off is not None:
+                o = off.cpu().numpy()
+                distinct += int((o[1:] > o[:-1]).sum())
+        ctx_len = PROMPT + n_warm + n_steps
+        step_bytes = (n_layers * nums["per_layer_fixed"] + distinct * nums["per_expert"] + nums["head"]
+                      + batch * ctx_len * nums["kv_per_token"] + batch * nums["H"] * 2)
+        for s in slots:
+            runner.release(s)
+        return dict(ms_per_step=ms / n_steps, tok_s=batch * n_steps / (ms / 1e3), step_bytes=step_bytes, launches=launches,
+                    clocks=clock_info, distinct_experts=distinct)
+
+    # ---- headline: batch 8 -------------------------------------------------------------
+    main_run = decode_run(BATCH, warmup, steps, sample_clocks=True)
+    achieved = main_run["step_bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9
+
+    # ---- prefill of 2,048 tokens -------------------------------------------------------
+    def prefill_once():
+        s = runner.admit()
+        p = prompts(1, PREFILL_TOKENS)[0]
+        ms = event_ms(lambda: runner.step([StepEntry(s, p, [PREFILL_TOKENS - 1])]))
+        runner.release(s)
+        return ms
+
+    for _ in range(3):
+        prefill_once()
+    pre_ms = statistics.median(prefill_once() for _ in range(5))
+    pre_flops = nums["prefill_flops"](PREFILL_TOKENS)
+    prefill = {"value": PREFILL_TOKENS / (pre_ms / 1e3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
+               "frac": pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+
+    points = {}
+    e2e = None
+    if not args.quick:
+        for b in (1, 64):
+            r = decode_run(b, warmup, max(8, steps // 2))
+            points[f"decode_b{b}"] = r["tok_s"]
+        # ---- end to end through the Python entry point -------------------------------------
+        eng_steps = steps
+        sp = SamplingParams(max_new_tokens=warmup + eng_steps + 2, stop_token_ids=())
+        ids = [engine.submit_tokens(p, sp.max_new_tokens, sp) for p in prompts(BATCH, PROMPT)]
+        sched = engine.scheduler()
+        while any(engine.request(i).generated_count() < warmup for i in ids):
+            engine.step_once()
+        torch.cuda.synchronize()
+        before = sum(engine.request(i).generated_count() for i in ids)
+        t1 = time.perf_counter()
+        for _ in range(eng_steps):
+            engine.step_once()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t1
+        made = sum(engine.request(i).generated_count() for i in ids) - before
+        for i in ids:
+            engine.cancel(i)
+        # per step: the pinned int32 metadata buffer up (tokens, positions, row->request, request tables, wanted rows,
+        # block-table rows) and one int32 token per request down
+        width = -(-(PROMPT + warmup + eng_steps) // PAGE)
+        h2d = 4 * (3 * BATCH + (BATCH + 1) + 2 * BATCH + BATCH + BATCH * width)
+        e2e = {"value": made / dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * BATCH}
+
+    line = {
+        "metric": "decode tokens/s at batch 8 (Qwen1.5-MoE-A2.7B sizes, bf16, random weights)",
+        "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
+        "config": {
+            "model": "Qwen1.5-MoE-A2.7B sizes", "global_batch": BATCH, "seq_len": CTX, "prompt_len": PROMPT,
+            "parallelism": "single GPU", "layers": n_layers, "layers_in_config": full_layers, "hidden": cfg["hidden_size"],
+            "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "experts": cfg["num_experts"], "top_k": cfg["num_experts_per_tok"], "moe_inter": cfg["moe_intermediate_size"],
+            "shared_inter": cfg["shared_expert_intermediate_size"], "vocab": vocab, "page_tokens": PAGE,
+            "l2": "inputs larger than L2 (a step reads GBs of weights)", "peaks": pk["source"],
+        },
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]},
+        "points": points,
+        "clocks": main_run["clocks"],
+        "gpu_launches": main_run["launches"],
+        "load_s": load_s,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -57,8 +57,13 @@ def _stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+launches = 0      # kernels launched through this module since import (each wrapper launches one)
+
+
 def _check(status: int, what: str) -> None:
+    global launches
     if status == 0:
+        launches += 1
         return
     if status in _REFUSALS:
         raise KernelError(f"{what}: refused: {_REFUSALS[status]}")

@@ -82,6 +82,7 @@ class SparseMoE(Part):
         self.w_gate = self.w_up = self.w_down = None
         self.ws_gate = self.ws_up = self.ws_down = None
         self.shared_gate_w = None
+        self.last_offsets = None
 
     def params(self) -> Dict[str, ParamSpec]:
         p = {self.name("gate.weight"): ParamSpec((self.num_experts, self.hidden), role="vector")}
@@ -131,6 +132,7 @@ class SparseMoE(Part):
         slot_token = torch.empty((T * k,), dtype=torch.int32, device=dev)
         slot_of_pick = torch.empty((T * k,), dtype=torch.int32, device=dev)
         K.moe_group(sel, k, E, offsets, slot_token, slot_of_pick)
+        self.last_offsets = offsets          # kept for measurement: which experts the last step touched
 
         act = torch.empty((T * k, self.inter), dtype=rt.act_dtype, device=dev)
         K.gemm(x, self.w_gate, act, w_up=self.w_up, group_offsets=offsets, a_row_index=slot_token)
