@@ -35,8 +35,9 @@ LIBRARIES: Dict[str, str] = {
     "attention_paged": "attention_paged.cu",
     "moe_route": "moe_route.cu",
     "sampling": "sampling.cu",
+    "gemm_tc": "gemm_tc.cu",
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "tc_common.cuh"]
 
 
 class BuildError(RuntimeError):

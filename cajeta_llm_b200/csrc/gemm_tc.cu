@@ -1,0 +1,314 @@
+// Matrix products on the 5th-generation tensor cores (tcgen05) for the bfloat16 path:
+//
+//     out[token, feature] (+)= sum_k X[token, k] * W[feature, k]   (+ bias[feature])
+//
+// X: activations [tokens, K] bf16, W: weights [features, K] bf16 (torch's [out, in]), both
+// K-major, so both feed tcgen05.mma straight from the 128-byte-swizzled tiles that TMA
+// lays into shared memory; accumulators are float32 in tensor memory.
+//
+// One block computes one output tile: warp 0 issues the TMA loads into a ring of stages,
+// warp 1 (one elected thread) issues the products and owns the tensor-memory allocation,
+// warps 2..5 read the accumulator back (each warp its own 32-lane quarter) and run the
+// epilogue.  Two orientations share the code:
+//   * tokens on the 128 rows of the product (SWAP = false): a step with many rows
+//     (prompt portions);
+//   * weights on the 128 rows, tokens on the product's N (SWAP = true, TOK = 16..128): a
+//     step with few rows (decode), so that a tile of 128 x 64 weights costs 16 KB of
+//     shared-memory traffic and the tokens only 2 KB.
+// Epilogues: float32 store (+ bias) [optionally one of several split-K partials], float32
+// accumulate (the residual add of an output projection), SwiGLU of two products to bf16
+// (two weight tiles, two accumulators), bf16 store.
+// Grouped form (mixture of experts): token rows are sorted by expert, offsets[g] is the
+// first row of group g, the weights of group g start at row g * features of W; a block
+// finds its (group, tile) by walking the offsets and masks rows past the group's end.
+//
+// reference counterpart: the indirected per-expert GEMMs over (expert, row range) chunk
+// maps, io/WmmaKernel.cajeta (q4kWmmaIdMwKernel), and the dense projection GEMMs of
+// model/Linear.cajeta; both wmma-class there.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+using namespace tc;
+
+namespace {
+
+constexpr int BK = 64;             // K elements per stage: one 128-byte swizzle row
+constexpr int UMMA_K = 16;         // K of one tcgen05.mma of kind::f16
+constexpr int THREADS = 192;
+
+enum Epilogue { EPI_STORE_F32 = 0, EPI_ACC_F32 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_BF16 = 3 };
+
+struct Args {
+    int tokens;                 // rows of X
+    int features;               // rows of W per group
+    int K;
+    void* out;
+    long long ldo;              // elements between output rows (tokens)
+    const float* bias;          // [features] or null
+    const int* group_offsets;   // [groups + 1] or null
+    int groups;
+    int k_splits;               // > 1: each split stores its partial at out + split * split_stride
+    long long split_stride;
+};
+
+template <int N_MMA, bool SWAP, bool DUAL, int STAGES>
+struct Smem {
+    static constexpr int X_ROWS = SWAP ? N_MMA : 128;
+    static constexpr int W_ROWS = SWAP ? 128 : N_MMA;
+    static constexpr int X_BYTES = X_ROWS * BK * 2;
+    static constexpr int W_BYTES = W_ROWS * BK * 2;
+    static constexpr int STAGE_BYTES = X_BYTES + (DUAL ? 2 : 1) * W_BYTES;
+    static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = TILE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int N_MMA, bool SWAP, bool DUAL, int EPI, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               const __grid_constant__ CUtensorMap map_w2, Args p) {
+    using S = Smem<N_MMA, SWAP, DUAL, STAGES>;
+    constexpr int TOK_TILE = S::X_ROWS;          // token rows a tile covers
+    constexpr int FEAT_TILE = S::W_ROWS;         // weight rows a tile covers
+    constexpr uint32_t ACC_COLS = N_MMA;         // tensor-memory columns of one accumulator
+    constexpr uint32_t TMEM_COLS_NEEDED = ACC_COLS * (DUAL ? 2 : 1);
+    constexpr uint32_t TMEM_COLS = TMEM_COLS_NEEDED <= 32 ? 32 : TMEM_COLS_NEEDED <= 64 ? 64 : TMEM_COLS_NEEDED <= 128 ? 128
+                                   : TMEM_COLS_NEEDED <= 256 ? 256 : 512;
+
+    // ---- which tile ------------------------------------------------------------------
+    int tok0, tok_end, group = 0;
+    if (p.group_offsets) {
+        int tile = blockIdx.y, first = 0;
+        bool found = false;
+        for (int g = 0; g < p.groups; ++g) {
+            int lo = p.group_offsets[g], hi = p.group_offsets[g + 1];
+            int tiles = (hi - lo + TOK_TILE - 1) / TOK_TILE;
+            if (tile < first + tiles) {
+                tok0 = lo + (tile - first) * TOK_TILE;
+                tok_end = min(hi, tok0 + TOK_TILE);
+                group = g;
+                found = true;
+                break;
+            }
+            first += tiles;
+        }
+        if (!found) return;
+    } else {
+        tok0 = blockIdx.y * TOK_TILE;
+        tok_end = min(p.tokens, tok0 + TOK_TILE);
+        if (tok0 >= p.tokens) return;
+    }
+    const int feat0 = blockIdx.x * FEAT_TILE;                       // within the group
+    const int w_row0 = group * p.features + feat0;                  // row of W (all groups stacked)
+    const int k_blocks_total = (p.K + BK - 1) / BK;
+    const int per_split = (k_blocks_total + p.k_splits - 1) / p.k_splits;
+    const int kb_begin = blockIdx.z * per_split;
+    const int kb_end = min(k_blocks_total, kb_begin + per_split);
+    const int n_kb = max(0, kb_end - kb_begin);
+
+    // ---- shared memory -----------------------------------------------------------------
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = (uint64_t*)(tiles + S::TILE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_bar = empty_bar + STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_bar + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(acc_bar, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer ----------------------------------------------------------------
+        if (elect_one()) {
+            tma_prefetch_descriptor(&map_x);
+            tma_prefetch_descriptor(&map_w);
+            if (DUAL) tma_prefetch_descriptor(&map_w2);
+            for (int i = 0; i < n_kb; ++i) {
+                int s = i % STAGES;
+                uint32_t round = i / STAGES;
+                if (i >= STAGES && !mbar_wait(&empty_bar[s], (round - 1) & 1, 1)) break;
+                uint8_t* st = tiles + (size_t)s * S::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+                int k0 = (kb_begin + i) * BK;
+                tma_load_2d(st, &map_x, &full_bar[s], k0, tok0);
+                tma_load_2d(st + S::X_BYTES, &map_w, &full_bar[s], k0, w_row0);
+                if (DUAL) tma_load_2d(st + S::X_BYTES + S::W_BYTES, &map_w2, &full_bar[s], k0, w_row0);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- product issue -----------------------------------------------------------------
+        if (elect_one()) {
+            constexpr uint32_t idesc = umma_idesc_bf16(128, N_MMA);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                int s = i % STAGES;
+                uint32_t round = i / STAGES;
+                ok = mbar_wait(&full_bar[s], round & 1, 2);
+                if (!ok) break;
+                tcgen05_fence_after();
+                uint8_t* st = tiles + (size_t)s * S::STAGE_BYTES;
+                uint64_t dx = umma_desc_sw128(st);
+                uint64_t dw = umma_desc_sw128(st + S::X_BYTES);
+                uint64_t dw2 = DUAL ? umma_desc_sw128(st + S::X_BYTES + S::W_BYTES) : 0;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    uint64_t step = (uint64_t)((k * UMMA_K * 2) >> 4);       // 32 bytes along K inside the swizzle row
+                    uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                    if (SWAP) {
+                        umma_bf16(tmem_base, dw + step, dx + step, idesc, acc);
+                        if (DUAL) umma_bf16(tmem_base + ACC_COLS, dw2 + step, dx + step, idesc, acc);
+                    } else {
+                        umma_bf16(tmem_base, dx + step, dw + step, idesc, acc);
+                        if (DUAL) umma_bf16(tmem_base + ACC_COLS, dx + step, dw2 + step, idesc, acc);
+                    }
+                }
+                umma_commit(&empty_bar[s]);          // the stage is free once these products have read it
+            }
+            umma_commit(acc_bar);                    // the accumulator is complete
+        }
+    } else {
+        // ---- epilogue: warps 2..5, each its own quarter of the 128 lanes --------------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;           // accumulator row of this thread
+        bool ok = n_kb > 0 ? mbar_wait(acc_bar, 0, 3) : true;
+        tcgen05_fence_after();
+        if (ok) {
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const long long split_off = (long long)blockIdx.z * p.split_stride;
+#pragma unroll 1
+            for (int c0 = 0; c0 < N_MMA; c0 += 16) {
+                uint32_t v0[16], v1[16];
+                if (n_kb > 0) {
+                    tmem_ld16(lane_base + c0, v0);
+                    if (DUAL) tmem_ld16(lane_base + ACC_COLS + c0, v1);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v0[j] = v1[j] = 0;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    int c = c0 + j;
+                    int token = SWAP ? tok0 + c : tok0 + r;
+                    int feat = SWAP ? feat0 + r : feat0 + c;
+                    if (token >= tok_end || feat >= p.features) continue;
+                    float v = __uint_as_float(v0[j]);
+                    if (EPI == EPI_SWIGLU_BF16) v = cj::silu(v) * __uint_as_float(v1[j]);
+                    if (p.bias && blockIdx.z == 0) v += p.bias[feat];
+                    long long o = (long long)token * p.ldo + feat;
+                    if (EPI == EPI_STORE_F32) ((float*)p.out)[o + split_off] = v;
+                    else if (EPI == EPI_ACC_F32) ((float*)p.out)[o] += v;
+                    else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int N_MMA, bool SWAP, bool DUAL, int EPI, int STAGES>
+int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2, const Args& a, cudaStream_t stream) {
+    using S = Smem<N_MMA, SWAP, DUAL, STAGES>;
+    auto kern = gemm_tc_kernel<N_MMA, SWAP, DUAL, EPI, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    int tok_tiles = (a.tokens + S::X_ROWS - 1) / S::X_ROWS + (a.group_offsets ? a.groups : 0);
+    dim3 grid((a.features + S::W_ROWS - 1) / S::W_ROWS, tok_tiles, a.k_splits);
+    if (grid.y > 65535 || grid.z > 65535) return CJ_ERR_SIZE;
+    kern<<<grid, THREADS, S::TOTAL, stream>>>(mx, mw, mw2, a);
+    return cj::launch_status();
+}
+
+// stages chosen so that a block stays within ~200 KB of shared memory
+template <int N_MMA, bool SWAP, bool DUAL, int EPI>
+int launch_auto(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2, const Args& a, cudaStream_t stream) {
+    constexpr int stage = Smem<N_MMA, SWAP, DUAL, 1>::STAGE_BYTES;
+    constexpr int STAGES = (200 * 1024 / stage) > 8 ? 8 : (200 * 1024 / stage);
+    return launch<N_MMA, SWAP, DUAL, EPI, STAGES>(mx, mw, mw2, a, stream);
+}
+
+template <bool SWAP, bool DUAL, int EPI>
+int dispatch_n(int n_mma, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2, const Args& a, cudaStream_t s) {
+    if constexpr (SWAP) {
+        switch (n_mma) {
+            case 16: return launch_auto<16, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
+            case 32: return launch_auto<32, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
+            case 64: return launch_auto<64, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
+            case 128: return launch_auto<128, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
+        }
+    } else {
+        switch (n_mma) {
+            case 128: return launch_auto<128, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
+            case 256: if constexpr (!DUAL) return launch_auto<256, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
+        }
+    }
+    return CJ_ERR_SIZE;
+}
+
+}  // namespace
+
+// x: [tokens, K] bf16 with row stride ldx; w (and w2 for SwiGLU): [groups * features, K] bf16,
+// contiguous.  swap: 0 = tokens on the product's rows (tile 128 tokens x n_mma features),
+// 1 = weights on the rows (tile 128 features x n_mma tokens).  epilogue: 0 float32 store,
+// 1 float32 accumulate, 2 SwiGLU to bf16 (needs w2), 3 bf16 store.  k_splits > 1 only with
+// epilogue 0: split s stores its partial sum at out + s * split_stride (the bias goes to
+// split 0).  Refuses (negative code) what it cannot run; never a wrong result.
+CJ_EXPORT int cj_gemm_tc(const void* x, long long ldx, const void* w, const void* w2, const float* bias, void* out,
+                         long long ldo, int tokens, int features, int K, int epilogue, int swap, int n_mma,
+                         const int* group_offsets, int groups, int k_splits, long long split_stride,
+                         cudaStream_t stream) {
+    if (tokens <= 0 || features <= 0) return 0;
+    if (!x || !w || !out || K <= 0) return CJ_ERR_ARG;
+    if (K % 8 != 0 || ldx % 8 != 0) return CJ_ERR_ALIGN;               // TMA: 16-byte strides
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)w2) & 15) return CJ_ERR_ALIGN;
+    if ((epilogue == EPI_SWIGLU_BF16) != (w2 != nullptr)) return CJ_ERR_ARG;
+    if (k_splits < 1 || (k_splits > 1 && epilogue != EPI_STORE_F32)) return CJ_ERR_ARG;
+    if (group_offsets && groups <= 0) return CJ_ERR_ARG;
+    int total_w_rows = (group_offsets ? groups : 1) * features;
+    int x_box = swap ? n_mma : 128, w_box = swap ? 128 : n_mma;
+    CUtensorMap mx, mw, mw2;
+    if (!make_map_bf16(&mx, x, tokens, K, ldx, x_box)) return CJ_ERR_ARG;
+    if (!make_map_bf16(&mw, w, total_w_rows, K, K, w_box)) return CJ_ERR_ARG;
+    if (w2) { if (!make_map_bf16(&mw2, w2, total_w_rows, K, K, w_box)) return CJ_ERR_ARG; }
+    else mw2 = mw;
+    Args a{tokens, features, K, out, ldo, bias, group_offsets, groups, k_splits, split_stride};
+#define CASE(EPI, DUAL)                                                                              \
+    if (swap) return dispatch_n<true, DUAL, EPI>(n_mma, mx, mw, mw2, a, stream);                      \
+    else return dispatch_n<false, DUAL, EPI>(n_mma, mx, mw, mw2, a, stream);
+    switch (epilogue) {
+        case EPI_STORE_F32: CASE(EPI_STORE_F32, false)
+        case EPI_ACC_F32: CASE(EPI_ACC_F32, false)
+        case EPI_SWIGLU_BF16: CASE(EPI_SWIGLU_BF16, true)
+        case EPI_STORE_BF16: CASE(EPI_STORE_BF16, false)
+    }
+#undef CASE
+    return CJ_ERR_ARG;
+}
+
+// 0, or the code of the first bounded wait that ran out (1 producer, 2 product issue,
+// 3 epilogue); reading it synchronises the device.
+CJ_EXPORT int cj_gemm_tc_error() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, tc::g_error_flag, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}

@@ -251,3 +251,47 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
                                        _ptr(repeat_penalty), _ptr(uniform), _ptr(history), _ptr(history_offsets),
                                        _ptr(scratch), _ptr(out), _stream())
     _check(st, "sample")
+
+
+EPI_STORE_F32, EPI_ACC_F32, EPI_SWIGLU_BF16, EPI_STORE_BF16 = 0, 1, 2, 3
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, swap: bool, n_mma: int,
+            bias: Optional[torch.Tensor] = None, w_up: Optional[torch.Tensor] = None,
+            group_offsets: Optional[torch.Tensor] = None, tokens: Optional[int] = None, k_splits: int = 1) -> None:
+    """Tensor-core product out[token, feature] (+)= x[token, :] . w[feature, :] (+ bias) in
+    bfloat16 with float32 accumulation (tcgen05, TMA).
+
+    ``swap`` False: tiles of 128 tokens x ``n_mma`` (128 or 256) features; True: tiles of 128
+    features x ``n_mma`` (16, 32, 64, 128) tokens.  ``epilogue``: EPI_STORE_F32, EPI_ACC_F32,
+    EPI_SWIGLU_BF16 (``w_up`` given), EPI_STORE_BF16.  With ``group_offsets`` the rows of
+    ``x`` are sorted by group and ``w`` is [groups, features, K].  ``k_splits`` > 1 (store
+    only): ``out`` is [k_splits, tokens, features] of partial sums.
+    """
+    _need(x, "x", torch.bfloat16), _need(w, "w", torch.bfloat16), _need(out, "out")
+    features, K = w.shape[-2], w.shape[-1]
+    T = tokens if tokens is not None else x.shape[0]
+    if x.shape[-1] != K or out.shape[-1] != features:
+        raise KernelError(f"gemm_tc: shapes x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)} do not agree")
+    want = torch.bfloat16 if epilogue in (EPI_SWIGLU_BF16, EPI_STORE_BF16) else torch.float32
+    if out.dtype != want:
+        raise KernelError(f"gemm_tc: epilogue {epilogue} writes {want}, out is {out.dtype}")
+    if w_up is not None:
+        _need(w_up, "w_up", torch.bfloat16)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    G = 0
+    if group_offsets is not None:
+        _need(group_offsets, "group_offsets", torch.int32)
+        G = w.shape[0]
+    split_stride = out.stride(0) if k_splits > 1 else 0
+    ldo = out.stride(-2)
+    st = library("gemm_tc").cj_gemm_tc(
+        _ptr(x), _ll(x.stride(0)), _ptr(w), _ptr(w_up), _ptr(bias), _ptr(out), _ll(ldo), _i(T), _i(features), _i(K),
+        _i(epilogue), _i(1 if swap else 0), _i(n_mma), _ptr(group_offsets), _i(G), _i(k_splits), _ll(split_stride), _stream())
+    _check(st, "gemm_tc")
+
+
+def gemm_tc_error() -> int:
+    """0, or the code of a bounded wait inside a tensor-core kernel that ran out of time."""
+    return int(library("gemm_tc").cj_gemm_tc_error())

@@ -1,0 +1,99 @@
+"""The tensor-core (tcgen05 / TMA) products against a float64 product of the same bfloat16
+operands, in both orientations, every epilogue, grouped and split along K, at sizes that
+leave partial tiles in every dimension."""
+import pytest
+import torch
+
+import plain_qwen2moe as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def K():
+    from cajeta_llm_b200.csrc import kernels
+    yield kernels
+    assert kernels.gemm_tc_error() == 0          # no bounded wait ran out during these tests
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).to(DEV)
+
+
+def close(got, want, atol=2e-3, rtol=2e-3):
+    d = (got.double() - want.double()).abs()
+    bound = atol + rtol * want.double().abs()
+    assert bool((d <= bound).all()), f"max diff {float(d.max()):.4e} at {int(d.argmax())}, want max {float(want.abs().max()):.3f}"
+
+
+@pytest.mark.parametrize("swap,n_mma,T,N,Kd", [(False, 128, 300, 384, 512), (False, 256, 129, 520, 264), (False, 128, 128, 128, 64),
+                                                (True, 16, 5, 300, 512), (True, 32, 40, 128, 200), (True, 64, 64, 1000, 2048),
+                                                (True, 128, 130, 260, 128), (True, 16, 1, 2048, 2048)])
+def test_store_accumulate_bias(K, swap, n_mma, T, N, Kd):
+    x, w = rnd(T, Kd, seed=1), rnd(N, Kd, seed=2, scale=0.1)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(3)).to(DEV)
+    want = x.double() @ w.double().t()
+    out = torch.full((T, N), 7.0, device=DEV)
+    K.gemm_tc(x, w, out, K.EPI_STORE_F32, swap, n_mma)
+    close(out, want)
+    K.gemm_tc(x, w, out, K.EPI_STORE_F32, swap, n_mma, bias=bias)
+    close(out, want + bias.double())
+    base = torch.randn(T, N, generator=torch.Generator().manual_seed(4)).to(DEV)
+    acc = base.clone()
+    K.gemm_tc(x, w, acc, K.EPI_ACC_F32, swap, n_mma)
+    close(acc, want + base.double())
+    ob = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tc(x, w, ob, K.EPI_STORE_BF16, swap, n_mma)
+    close(ob, want, atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("swap,n_mma,T", [(False, 128, 200), (True, 16, 9), (True, 64, 50)])
+def test_swiglu(K, swap, n_mma, T):
+    N, Kd = 328, 256
+    x, wg, wu = rnd(T, Kd, seed=5), rnd(N, Kd, seed=6, scale=0.1), rnd(N, Kd, seed=7, scale=0.1)
+    want = P.silu(x.double() @ wg.double().t()) * (x.double() @ wu.double().t())
+    out = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tc(x, wg, out, K.EPI_SWIGLU_BF16, swap, n_mma, w_up=wu)
+    close(out, want, atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("swap,n_mma", [(False, 128), (True, 16), (True, 32)])
+def test_grouped(K, swap, n_mma):
+    E, N, Kd = 6, 200, 192
+    counts = [0, 37, 1, 150, 0, 20] if not swap else [0, 3, 1, 20, 0, 7]
+    T = sum(counts)
+    offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    x = rnd(T, Kd, seed=8)
+    wg, wu = rnd(E, N, Kd, seed=9, scale=0.1), rnd(E, N, Kd, seed=10, scale=0.1)
+    out = torch.full((T, N), -3.0, device=DEV)
+    K.gemm_tc(x, wg, out, K.EPI_STORE_F32, swap, n_mma, group_offsets=offsets)
+    act = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tc(x, wg, act, K.EPI_SWIGLU_BF16, swap, n_mma, w_up=wu, group_offsets=offsets)
+    lo = 0
+    for e, c in enumerate(counts):
+        xe = x[lo:lo + c].double()
+        close(out[lo:lo + c], xe @ wg[e].double().t())
+        close(act[lo:lo + c], P.silu(xe @ wg[e].double().t()) * (xe @ wu[e].double().t()), atol=2e-2, rtol=1e-2)
+        lo += c
+
+
+@pytest.mark.parametrize("splits", [2, 4, 7])
+def test_split_k_partials_sum_to_the_product(K, splits):
+    T, N, Kd = 8, 384, 1408
+    x, w = rnd(T, Kd, seed=11), rnd(N, Kd, seed=12, scale=0.1)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(13)).to(DEV)
+    parts = torch.full((splits, T, N), 9.0, device=DEV)
+    K.gemm_tc(x, w, parts, K.EPI_STORE_F32, True, 16, bias=bias, k_splits=splits)
+    close(parts.sum(0), x.double() @ w.double().t() + bias.double())
+
+
+def test_refusals(K):
+    x, w = rnd(4, 100, seed=14), rnd(8, 100, seed=15)
+    out = torch.empty(4, 8, device=DEV)
+    with pytest.raises(K.KernelError, match="alignment"):
+        K.gemm_tc(x, w, out, K.EPI_STORE_F32, True, 16)               # K = 100 is not a multiple of 8
+    x, w = rnd(4, 64, seed=14), rnd(8, 64, seed=15)
+    with pytest.raises(K.KernelError, match="size"):
+        K.gemm_tc(x, w, out, K.EPI_STORE_F32, True, 24)
