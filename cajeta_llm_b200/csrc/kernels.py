@@ -295,3 +295,10 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
 def gemm_tc_error() -> int:
     """0, or the code of a bounded wait inside a tensor-core kernel that ran out of time."""
     return int(library("gemm_tc").cj_gemm_tc_error())
+
+
+def gather_rows(x: torch.Tensor, index: torch.Tensor, out: torch.Tensor) -> None:
+    """out[s, :] = x[index[s], :]."""
+    _need(x, "x"), _need(index, "index", torch.int32), _need(out, "out", x.dtype)
+    st = library("rowwise").cj_gather_rows(_ptr(out), _ptr(x), _i(_code(x)), _ptr(index), _i(out.shape[0]), _i(x.shape[-1]), _stream())
+    _check(st, "gather_rows")

@@ -212,3 +212,33 @@ CJ_EXPORT int cj_moe_combine(float* hs, const float* y, const int* slot_of_pick,
     moe_combine_kernel<<<T, threads, 0, stream>>>(hs, y, slot_of_pick, w, k, shared, shared_scale, H);
     return launch_status();
 }
+
+// ---------------------------------------------------------------------------------
+// Row gather: out[s, :] = x[index[s], :] (bf16 or f32 rows).  Puts the rows of a mixture
+// of experts into expert order so that each expert reads a contiguous block
+// (model/MoeFfn.cajeta:2644-2777 gathers rows per expert the same way).
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ index, int H) {
+    int s = blockIdx.x;
+    const T* src = x + (size_t)index[s] * H;
+    T* dst = out + (size_t)s * H;
+    if ((H * sizeof(T)) % 16 == 0) {
+        const uint4* s4 = (const uint4*)src;
+        uint4* d4 = (uint4*)dst;
+        int n = H * sizeof(T) / 16;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) d4[i] = s4[i];
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+CJ_EXPORT int cj_gather_rows(void* out, const void* x, int dtype, const int* index, int rows, int H, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (!out || !x || !index || H <= 0) return CJ_ERR_ARG;
+    int threads = H >= 1024 ? 256 : 128;
+    if (dtype == CJ_F32) gather_rows_kernel<float><<<rows, threads, 0, stream>>>((float*)out, (const float*)x, index, H);
+    else if (dtype == CJ_BF16) gather_rows_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, index, H);
+    else return CJ_ERR_DTYPE;
+    return launch_status();
+}

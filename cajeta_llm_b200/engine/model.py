@@ -16,6 +16,7 @@ import torch
 from ..config.base import ModelConfig, get_architecture, load_config
 from ..csrc import kernels as K
 from ..parts.base import KvNeed, Runtime, StateNeed, make_part
+from ..parts.linear import project
 from ..parts.plan import ModelPlan, ParamSpec
 from ..weights.sources import RandomWeights, SafetensorsWeights
 
@@ -78,7 +79,7 @@ class Model:
         (model/CausalLM.cajeta:1712-1718)."""
         x, _ = self.final_norm.forward(hs, row_index=rows)
         out = torch.empty((rows.numel(), self.vocab), dtype=torch.float32, device=hs.device)
-        K.gemm(x, self.lm_head, out)
+        project(self.runtime, x, self.lm_head, out)
         return out
 
     def weight_bytes(self) -> int:

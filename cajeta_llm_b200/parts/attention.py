@@ -25,6 +25,7 @@ import torch
 
 from ..csrc import kernels as K
 from .base import KvNeed, Part, make_part, register_part
+from .linear import project
 from .plan import ParamSpec
 
 
@@ -93,7 +94,7 @@ class PagedAttention(Part):
         write = entry.writes_cache
         n_out = self.q_dim + (2 * self.kv_dim if write else 0)
         qkv = torch.empty((T, n_out), dtype=torch.float32, device=x.device)
-        K.gemm(x, self.w_qkv[:n_out], qkv, bias=None if self.b_qkv is None else self.b_qkv[:n_out])
+        project(rt, x, self.w_qkv[:n_out], qkv, bias=None if self.b_qkv is None else self.b_qkv[:n_out])
         q = torch.empty((T, self.heads, self.head_dim), dtype=rt.act_dtype, device=x.device)
         K.rope_kv_write(qkv, 0, self.q_dim, self.q_dim + self.kv_dim, q, entry.k_plane, entry.v_plane,
                         ctx.positions, ctx.row_req, entry.block_table, entry.page_tokens, self.heads, self.kv_heads,
@@ -101,4 +102,4 @@ class PagedAttention(Part):
         out = torch.empty_like(q)
         K.paged_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
                           entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale)
-        K.gemm(out.view(T, self.q_dim), self.w_o, residual, bias=self.b_o, accumulate=True)
+        project(rt, out.view(T, self.q_dim), self.w_o, residual, bias=self.b_o, accumulate=True)

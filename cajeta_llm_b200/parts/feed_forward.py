@@ -29,6 +29,7 @@ import torch
 
 from ..csrc import kernels as K
 from .base import Part, register_part
+from .linear import project
 from .plan import ParamSpec
 
 
@@ -57,8 +58,8 @@ class DenseSwiGLU(Part):
     def forward(self, x: torch.Tensor, x_f32: Optional[torch.Tensor], residual: torch.Tensor, ctx) -> None:
         T = x.shape[0]
         act = torch.empty((T, self.inter), dtype=self.runtime.act_dtype, device=x.device)
-        K.gemm(x, self.w_gate, act, w_up=self.w_up)
-        K.gemm(act, self.w_down, residual, accumulate=True)
+        project(self.runtime, x, self.w_gate, act, w_up=self.w_up)
+        project(self.runtime, act, self.w_down, residual, accumulate=True)
 
 
 @register_part("feed_forward", "sparse_moe")
@@ -135,14 +136,14 @@ class SparseMoE(Part):
         self.last_offsets = offsets          # kept for measurement: which experts the last step touched
 
         act = torch.empty((T * k, self.inter), dtype=rt.act_dtype, device=dev)
-        K.gemm(x, self.w_gate, act, w_up=self.w_up, group_offsets=offsets, a_row_index=slot_token)
+        project(rt, x, self.w_gate, act, w_up=self.w_up, group_offsets=offsets, a_row_index=slot_token, max_group_rows=T)
         y = torch.empty((T * k, self.hidden), dtype=torch.float32, device=dev)
-        K.gemm(act, self.w_down, y, group_offsets=offsets)
+        project(rt, act, self.w_down, y, group_offsets=offsets, max_group_rows=T)
 
         shared = None
         if self.shared_inter > 0:
             sact = torch.empty((T, self.shared_inter), dtype=rt.act_dtype, device=dev)
-            K.gemm(x, self.ws_gate, sact, w_up=self.ws_up)
+            project(rt, x, self.ws_gate, sact, w_up=self.ws_up)
             shared = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
-            K.gemm(sact, self.ws_down, shared)
+            project(rt, sact, self.ws_down, shared)
         K.moe_combine(residual, y, slot_of_pick, wts, k, shared, shared_scale)

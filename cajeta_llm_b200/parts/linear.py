@@ -1,0 +1,68 @@
+"""One place that decides which matrix-product kernel a part's projection runs on.
+
+``project`` computes ``out[token, feature] (+)= x[token, :] . w[feature, :]`` (+ bias), or
+the SwiGLU of two such products, for a dense weight or for the stacked weights of a
+mixture of experts.  On the bfloat16 path it runs on the tensor cores (tcgen05 / TMA)
+when the shapes allow TMA (K a multiple of 8, 16-byte aligned rows) and are large
+enough to fill a tile; otherwise, and always on the float32 path, it runs on the FMA
+pipe, whose results do not depend on the batch at all.  Few rows (decode) put the
+weights on the rows of the tensor-core product, many rows (prompt portions) the tokens.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..csrc import kernels as K
+
+# below these sizes a tensor-core tile would be mostly padding
+MIN_K = 128
+MIN_FEATURES = 128
+
+
+def _tc_ok(runtime, x: torch.Tensor, w: torch.Tensor) -> bool:
+    if not runtime.fast_kernels or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    Kd, features = w.shape[-1], w.shape[-2]
+    return (Kd >= MIN_K and Kd % 8 == 0 and features >= MIN_FEATURES and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and x.stride(-1) == 1)
+
+
+def _token_tile(rows: int) -> int:
+    for n in (16, 32, 64, 128):
+        if rows <= n:
+            return n
+    return 0
+
+
+def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+            accumulate: bool = False, w_up: Optional[torch.Tensor] = None, group_offsets: Optional[torch.Tensor] = None,
+            a_row_index: Optional[torch.Tensor] = None, max_group_rows: Optional[int] = None) -> None:
+    """``x``: [tokens, K]; ``w``: [features, K] or, with ``group_offsets``, [groups, features, K]
+    where output row s belongs to the group whose range holds s and reads row
+    ``a_row_index[s]`` of ``x`` (or row s).  ``w_up`` selects the SwiGLU form (``out`` in the
+    activation dtype).  ``max_group_rows`` bounds the rows of any one group when known."""
+    if not _tc_ok(runtime, x, w):
+        K.gemm(x, w, out, bias=bias, accumulate=accumulate, w_up=w_up, group_offsets=group_offsets, a_row_index=a_row_index)
+        return
+    rows = out.shape[0]
+    if a_row_index is not None:
+        gathered = torch.empty((rows, x.shape[-1]), dtype=x.dtype, device=x.device)
+        K.gather_rows(x, a_row_index, gathered)
+        x = gathered
+    if w_up is not None:
+        epi = K.EPI_SWIGLU_BF16
+    elif out.dtype == torch.bfloat16:
+        epi = K.EPI_STORE_BF16
+    else:
+        epi = K.EPI_ACC_F32 if accumulate else K.EPI_STORE_F32
+    # few rows: weights on the rows of the product; a group of a mixture rarely has more
+    # rows than the step has tokens, which bounds the token tile
+    bound = rows if max_group_rows is None else min(rows, max_group_rows)
+    tile = _token_tile(bound)
+    if tile:
+        K.gemm_tc(x, w, out, epi, True, tile, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows)
+    else:
+        n_mma = 256 if (w_up is None and w.shape[-2] >= 512) else 128
+        K.gemm_tc(x, w, out, epi, False, n_mma, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows)

@@ -43,8 +43,20 @@ TINY_C = {
     "decoder_sparse_step": 1, "mlp_only_layers": [1], "tie_word_embeddings": False,
     "use_sliding_window": True, "sliding_window": 20, "max_window_layers": 0,
 }
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-SEEDS = {"A": 11, "B": 23, "C": 37}
+# Wide enough for the tensor-core kernels of the bfloat16 path (every product has K >= 128
+# and >= 128 output features); widths are still no power of two where the kernels allow.
+MEDIUM = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "hidden_size": 384, "intermediate_size": 512, "num_hidden_layers": 2,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 1000,
+    "max_position_embeddings": 4096, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "num_experts": 8, "num_experts_per_tok": 2, "moe_intermediate_size": 192,
+    "shared_expert_intermediate_size": 320, "norm_topk_prob": False,
+    "decoder_sparse_step": 1, "mlp_only_layers": [1], "tie_word_embeddings": False,
+    "use_sliding_window": False,
+}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "M": MEDIUM}
+SEEDS = {"A": 11, "B": 23, "C": 37, "M": 41}
 
 
 def write_model(model_dir: str, raw_config: dict, seed: int, store_dtype=torch.bfloat16) -> None:
@@ -72,12 +84,25 @@ def plain_logits(model_dir: str, tokens: Sequence[int]) -> torch.Tensor:
     """Logits [T, vocab] of the plain implementation (float64 arithmetic), cached."""
     import plain_qwen2moe as P
 
+    return _plain(model_dir, tokens)[0]
+
+
+def plain_margins(model_dir: str, tokens: Sequence[int]) -> torch.Tensor:
+    """Each position's smallest routing margin over the layers (see plain_qwen2moe.routing_margin)."""
+    return _plain(model_dir, tokens)[1]
+
+
+def _plain(model_dir, tokens):
+    import plain_qwen2moe as P
+
     key = (model_dir, tuple(tokens))
     if key not in _plain_cache:
         if model_dir not in _plain_cache:
             _plain_cache[model_dir] = P.read_model(model_dir)
         config, weights = _plain_cache[model_dir]
-        _plain_cache[key] = P.forward(config, weights, list(tokens)).to(torch.float32)
+        margins = [1.0] * len(tokens)
+        logits = P.forward(config, weights, list(tokens), margins=margins).to(torch.float32)
+        _plain_cache[key] = (logits, torch.tensor(margins))
     return _plain_cache[key]
 
 
@@ -85,13 +110,29 @@ def plain_logits(model_dir: str, tokens: Sequence[int]) -> torch.Tensor:
 # rounding of float32 sums (measured ~3e-7 on logits of size ~1).  bfloat16: activations
 # between kernels and the cache are rounded to 8 bits of mantissa; on these models the
 # logits differ by ~1e-2 at most (measured), against logits of size ~1.
+#
+# A mixture of experts is discontinuous where two experts are nearly tied for the last
+# pick: rounding upstream of the router can then swap one expert for another, and the row
+# changes by a finite amount (the reference met this too and measures the gap behind each
+# flip, model/MoeFfn.cajeta:135-149).  A bfloat16 row whose routing margin in the plain
+# implementation is below NEAR_TIE may therefore be off by a swapped expert; such rows
+# get the looser bound TIE_FACTOR x and are counted, never skipped.  float32 rows get no
+# such allowance.
 TOL = {"float32": dict(atol=2e-5, rtol=1e-4), "bfloat16": dict(atol=4e-2, rtol=4e-2)}
+NEAR_TIE = 0.01
+TIE_FACTOR = 4.0
+near_tie_rows = {"seen": 0, "rows": 0}
 
 
-def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = "") -> None:
+def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = "", margins=None) -> None:
     tol = TOL[dtype]
     diff = (got.double() - want.double()).abs()
     bound = tol["atol"] + tol["rtol"] * want.double().abs()
+    if dtype == "bfloat16" and margins is not None:
+        tied = margins.to(torch.float64) < NEAR_TIE
+        near_tie_rows["seen"] += int(tied.sum())
+        near_tie_rows["rows"] += int(tied.numel())
+        bound = torch.where(tied[:, None], bound * TIE_FACTOR, bound)
     if bool((diff > bound).any()):
         i = int(torch.argmax(diff - bound))
         r, c = divmod(i, got.shape[-1])

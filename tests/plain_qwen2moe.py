@@ -167,15 +167,31 @@ def swiglu_mlp(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, wd: torch.Te
     return linear(silu(linear(x, wg)) * linear(x, wu), wd)
 
 
+def routing_margin(logits: torch.Tensor, top_k: int) -> float:
+    """How far the row is from another choice of experts: (p_k - p_{k+1}) / p_k of the
+    k-th and (k+1)-th largest router probabilities (1.0 when every expert is picked).
+    The reference measures the same gap behind a routing flip
+    (model/MoeFfn.cajeta:135-149); a row with a tiny margin changes discontinuously
+    under rounding, which a comparison in reduced precision has to know."""
+    if top_k >= logits.shape[0]:
+        return 1.0
+    p = torch.softmax(logits.double(), dim=0).sort(descending=True).values
+    return float((p[top_k - 1] - p[top_k]) / p[top_k - 1])
+
+
 def sparse_moe(x: torch.Tensor, weights: Dict[str, torch.Tensor], prefix: str, num_experts: int, top_k: int,
-               norm_topk: bool, has_shared: bool) -> torch.Tensor:
+               norm_topk: bool, has_shared: bool, margins: Optional[List[float]] = None) -> torch.Tensor:
     """Per row: router, selected experts accumulated in selection order, then the
-    sigmoid-gated shared expert (model/MoeFfn.cajeta:1849-1916 and :1925-1964)."""
+    sigmoid-gated shared expert (model/MoeFfn.cajeta:1849-1916 and :1925-1964).
+    ``margins`` (one entry per row, updated in place) keeps the smallest routing margin."""
     out = torch.zeros_like(x)
     router_w = weights[f"{prefix}.gate.weight"]
     for t in range(x.shape[0]):
         row = x[t]
-        sel, wt = route(linear(row, router_w), top_k, norm_topk)
+        logits = linear(row, router_w)
+        if margins is not None:
+            margins[t] = min(margins[t], routing_margin(logits, top_k))
+        sel, wt = route(logits, top_k, norm_topk)
         acc = torch.zeros_like(row)
         for j, e in enumerate(sel):
             y = swiglu_mlp(row, weights[f"{prefix}.experts.{e}.gate_proj.weight"],
@@ -211,9 +227,10 @@ def layer_window(config: dict, layer: int) -> int:
 # the whole model
 # ----------------------------------------------------------------------------------
 def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int],
-            dtype: torch.dtype = torch.float64) -> torch.Tensor:
+            dtype: torch.dtype = torch.float64, margins: Optional[List[float]] = None) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence (model/CausalLM.cajeta:1424-1608 per
-    layer, :1712-1718 for the head)."""
+    layer, :1712-1718 for the head).  ``margins``: a list of T ones that receives each
+    row's smallest routing margin over the layers."""
     W = {k: v.to(dtype) for k, v in weights.items()}
     heads = config["num_attention_heads"]
     kv_heads = config.get("num_key_value_heads", heads)
@@ -237,7 +254,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int
         if layer_is_sparse(config, l):
             ff = sparse_moe(xn, W, f"{p}.mlp", config["num_experts"], config["num_experts_per_tok"],
                             config.get("norm_topk_prob", False),
-                            config.get("shared_expert_intermediate_size", 0) > 0)
+                            config.get("shared_expert_intermediate_size", 0) > 0, margins)
         else:
             ff = swiglu_mlp(xn, W[f"{p}.mlp.gate_proj.weight"], W[f"{p}.mlp.up_proj.weight"],
                             W[f"{p}.mlp.down_proj.weight"])

@@ -117,7 +117,7 @@ def build_trace(vocab, seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "M"])
 def test_replay_every_way_of_cutting_matches_the_plain_implementation(name, dtype, model_dirs, tmp_path):
     vocab = helpers.CONFIGS[name]["vocab_size"]
     tb, toks = build_trace(vocab, seed=5 + ord(name))
@@ -131,9 +131,12 @@ def test_replay_every_way_of_cutting_matches_the_plain_implementation(name, dtyp
             continue
         got = torch.from_numpy(out[s["step"]].copy())
         want = torch.stack([helpers.plain_logits(model_dirs[name], toks[rid])[pos] for rid, pos in rows])
-        helpers.assert_close(got, want, dtype, f"{name} {dtype} step {s['step']} rows {rows[:4]}...")
+        margins = torch.stack([helpers.plain_margins(model_dirs[name], toks[rid])[pos] for rid, pos in rows])
+        helpers.assert_close(got, want, dtype, f"{name} {dtype} step {s['step']} rows {rows[:4]}...", margins)
         worst = max(worst, float((got - want).abs().max()))
-    print(f"\n{name} {dtype}: {len(tb.steps)} steps, worst |diff| {worst:.3e}")
+    tied = helpers.near_tie_rows
+    print(f"\n{name} {dtype}: {len(tb.steps)} steps, worst |diff| {worst:.3e}; near-tie rows so far {tied['seen']} of {tied['rows']}")
+    assert tied["seen"] <= 0.2 * max(1, tied["rows"])          # the allowance stays the exception
 
 
 def test_replay_writes_nothing_when_nothing_is_wanted_and_reuses_ids(model_dirs, tmp_path):
