@@ -1,0 +1,180 @@
+// Decode attention for the bfloat16 path: few query rows, each over a long stretch of
+// cached keys.  The keys of a row are cut into fixed chunks of 128 ("split-KV"); one
+// block takes one (row, kv head, chunk), each thread one key of the chunk for the scores
+// and a pair of output dims for the weighted sum of values, for every query head of the
+// kv head's group.  A chunk leaves a partial (max, sum, unnormalised accumulator); the
+// block that finishes a (row, head) last merges the partials in chunk order, so the
+// result does not depend on which block arrived when, nor - the chunking being a function
+// of the row's own [from, p] - on what else is in the batch.
+//
+// Formula as in the general kernel (model/PagedKvCache.cajeta:374-470); the split scheme
+// follows the reference's flash-decode kernels and their reduce
+// (model/AttnKernel.cajeta:1227-1459, :2204), which cut by a wave count instead.
+#include "common.cuh"
+
+using namespace cj;
+
+namespace {
+
+constexpr int CHUNK = 128;       // keys per block = threads per block
+
+template <int HD>
+__global__ void __launch_bounds__(CHUNK) decode_attention_kernel(
+    const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ kplane,
+    const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ positions, const int* __restrict__ row_req,
+    const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int window, float scale,
+    float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters, int max_splits) {
+    constexpr int PAIRS = HD / 2;                 // threads that cover the head's dims two at a time
+    constexpr int KPAR = CHUNK / PAIRS;           // key phases working side by side in the value sum
+    __shared__ __align__(16) float qs[HD];
+    __shared__ float es[CHUNK];
+    __shared__ long long bases[CHUNK];
+    __shared__ float red[CHUNK / 32];
+    __shared__ float2 vsum[KPAR][PAIRS];
+    __shared__ int is_last;
+
+    const int t = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int p = positions[t];
+    const int from = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
+    const int n_keys = p - from + 1;
+    const int n_splits = (n_keys + CHUNK - 1) / CHUNK;
+    if (split >= n_splits) return;
+    const int group = n_heads / n_kv;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int key0 = from + split * CHUNK;
+    const int count = min(CHUNK, p - key0 + 1);
+    const int* tab = table + (size_t)row_req[t] * table_stride;
+
+    // where each key of the chunk lives
+    if (tid < count) {
+        int key = key0 + tid;
+        int page = tab[key / page_tokens];
+        bases[tid] = (((long long)page * n_kv + kvh) * page_tokens + key % page_tokens) * HD;
+    }
+
+    for (int hg = 0; hg < group; ++hg) {
+        const int h = kvh * group + hg;
+        __syncthreads();                                        // bases ready; previous head done with qs / es / vsum
+        if (tid < HD) qs[tid] = __bfloat162float(q[((size_t)t * n_heads + h) * HD + tid]);
+        __syncthreads();
+
+        // scores: one key per thread, the key row read in 16-byte pieces
+        float s = -INFINITY;
+        if (tid < count) {
+            const uint4* kr = (const uint4*)(kplane + bases[tid]);
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) {
+                uint4 u = kr[i];
+                const __nv_bfloat162* b2 = (const __nv_bfloat162*)&u;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float2 f = __bfloat1622float2(b2[j]);
+                    dot = fmaf(qs[i * 8 + 2 * j], f.x, dot);
+                    dot = fmaf(qs[i * 8 + 2 * j + 1], f.y, dot);
+                }
+            }
+            s = dot * scale;
+        }
+        float m = warp_max(s);
+        if (lane == 0) red[warp] = m;
+        __syncthreads();
+        m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+        float e = tid < count ? expf(s - m) : 0.0f;
+        es[tid] = e;
+        float l = warp_sum(e);
+        __syncthreads();                                        // everyone has read red
+        if (lane == 0) red[warp] = l;
+        __syncthreads();
+        l = (red[0] + red[1]) + (red[2] + red[3]);
+
+        // values: thread = (dim pair, key phase); keys of its phase in order
+        const int pair = tid % PAIRS, phase = tid / PAIRS;
+        float2 acc = make_float2(0.0f, 0.0f);
+        for (int j = phase; j < count; j += KPAR) {
+            float ej = es[j];
+            __nv_bfloat162 v2 = *(const __nv_bfloat162*)(vplane + bases[j] + 2 * pair);
+            float2 f = __bfloat1622float2(v2);
+            acc.x = fmaf(ej, f.x, acc.x);
+            acc.y = fmaf(ej, f.y, acc.y);
+        }
+        vsum[phase][pair] = acc;
+        __syncthreads();
+        if (tid < PAIRS) {
+            float2 a = vsum[0][tid];
+#pragma unroll
+            for (int ph = 1; ph < KPAR; ++ph) {
+                a.x += vsum[ph][tid].x;
+                a.y += vsum[ph][tid].y;
+            }
+            if (n_splits == 1) {
+                float inv = 1.0f / l;
+                *(__nv_bfloat162*)(out + ((size_t)t * n_heads + h) * HD + 2 * tid) = __floats2bfloat162_rn(a.x * inv, a.y * inv);
+            } else {
+                size_t slot = ((size_t)t * n_heads + h) * max_splits + split;
+                *(float2*)(part_acc + slot * HD + 2 * tid) = a;
+                if (tid == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
+            }
+        }
+    }
+    if (n_splits == 1) return;
+
+    // the last chunk of this (row, kv head) to finish merges all chunks, in chunk order
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int done = atomicAdd(&counters[t * n_kv + kvh], 1);
+        is_last = done == n_splits - 1;
+        if (is_last) counters[t * n_kv + kvh] = 0;             // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int hg = 0; hg < group; ++hg) {
+        const int h = kvh * group + hg;
+        size_t slot0 = ((size_t)t * n_heads + h) * max_splits;
+        float M = -INFINITY;
+        for (int sidx = 0; sidx < n_splits; ++sidx) M = fmaxf(M, part_ml[(slot0 + sidx) * 2]);
+        float L = 0.0f;
+        for (int sidx = 0; sidx < n_splits; ++sidx) L += part_ml[(slot0 + sidx) * 2 + 1] * expf(part_ml[(slot0 + sidx) * 2] - M);
+        if (tid < PAIRS) {
+            float2 a = make_float2(0.0f, 0.0f);
+            for (int sidx = 0; sidx < n_splits; ++sidx) {
+                float f = expf(part_ml[(slot0 + sidx) * 2] - M);
+                float2 v = *(const float2*)(part_acc + (slot0 + sidx) * HD + 2 * tid);
+                a.x = fmaf(v.x, f, a.x);
+                a.y = fmaf(v.y, f, a.y);
+            }
+            float inv = 1.0f / L;
+            *(__nv_bfloat162*)(out + ((size_t)t * n_heads + h) * HD + 2 * tid) = __floats2bfloat162_rn(a.x * inv, a.y * inv);
+        }
+    }
+}
+
+}  // namespace
+
+// q, out: [T, n_heads, hd] bf16; planes [pages, n_kv, page_tokens, hd] bf16.  max_context
+// bounds position + 1 over the rows.  part_acc: scratch float32 [T, n_heads, max_splits, hd],
+// part_ml: [T, n_heads, max_splits, 2], counters: int32 [T * n_kv], zero before the first use
+// (the kernel leaves them zero).  hd must be 64 or 128.
+CJ_EXPORT int cj_decode_attention(const void* q, void* out, const void* kplane, const void* vplane, const int* positions,
+                                  const int* row_req, const int* table, int table_stride, int page_tokens, int T,
+                                  int n_heads, int n_kv, int hd, int window, float scale, int max_context,
+                                  float* part_acc, float* part_ml, int* counters, int max_splits, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (!q || !out || !kplane || !vplane || !positions || !row_req || !table || !part_acc || !part_ml || !counters) return CJ_ERR_ARG;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || page_tokens <= 0) return CJ_ERR_SIZE;
+    if (hd != 64 && hd != 128) return CJ_ERR_SIZE;
+    int span = window > 0 ? min(window, max_context) : max_context;
+    int splits = (span + CHUNK - 1) / CHUNK;
+    if (splits < 1) splits = 1;
+    if (splits > max_splits || splits > 65535 || n_kv > 65535) return CJ_ERR_SIZE;
+    dim3 grid(T, n_kv, splits);
+#define LAUNCH(HD)                                                                                                     \
+    decode_attention_kernel<HD><<<grid, CHUNK, 0, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,              \
+        (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane, positions, row_req, table, table_stride,           \
+        page_tokens, n_heads, n_kv, window, scale, part_acc, part_ml, counters, max_splits)
+    if (hd == 128) LAUNCH(128); else LAUNCH(64);
+#undef LAUNCH
+    return launch_status();
+}

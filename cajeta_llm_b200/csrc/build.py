@@ -36,6 +36,7 @@ LIBRARIES: Dict[str, str] = {
     "moe_route": "moe_route.cu",
     "sampling": "sampling.cu",
     "gemm_tc": "gemm_tc.cu",
+    "attention_decode": "attention_decode.cu",
 }
 HEADERS = ["common.cuh", "tc_common.cuh"]
 

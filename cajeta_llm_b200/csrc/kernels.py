@@ -193,9 +193,13 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
         raise KernelError(f"router_topk: {E} experts; this kernel takes at most 1024")
     if shared_gate is not None:
         _need(shared_gate, "shared_gate", torch.float32), _need(shared_scale, "shared_scale", torch.float32)
+    logits = torch.empty((T, E + 1), dtype=torch.float32, device=x.device)
     st = library("moe_route").cj_router_topk(_ptr(x), _ptr(router_w), _ptr(shared_gate), _i(T), _i(H), _i(E), _i(top_k),
-                                             _i(1 if norm_topk else 0), _ptr(sel), _ptr(weights), _ptr(shared_scale), _stream())
+                                             _i(1 if norm_topk else 0), _ptr(sel), _ptr(weights), _ptr(shared_scale),
+                                             _ptr(logits), _stream())
     _check(st, "router_topk")
+    global launches
+    launches += 1                      # two kernels: logits, then selection
 
 
 def moe_group(sel: torch.Tensor, top_k: int, num_experts: int, offsets: torch.Tensor, slot_token: torch.Tensor,
@@ -302,3 +306,43 @@ def gather_rows(x: torch.Tensor, index: torch.Tensor, out: torch.Tensor) -> None
     _need(x, "x"), _need(index, "index", torch.int32), _need(out, "out", x.dtype)
     st = library("rowwise").cj_gather_rows(_ptr(out), _ptr(x), _i(_code(x)), _ptr(index), _i(out.shape[0]), _i(x.shape[-1]), _stream())
     _check(st, "gather_rows")
+
+
+DECODE_CHUNK = 128
+
+
+def decode_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+                     positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int,
+                     n_heads: int, n_kv: int, head_dim: int, window: int, scale: float, max_context: int,
+                     scratch: "DecodeScratch") -> None:
+    """Split-KV attention of few bfloat16 query rows over their cached keys (head_dim 64 or 128)."""
+    for n, t in (("q", q), ("out", out), ("k_plane", k_plane), ("v_plane", v_plane)):
+        _need(t, n, torch.bfloat16)
+    _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
+    T = q.shape[0]
+    span = min(window, max_context) if window > 0 else max_context
+    splits = max(1, -(-span // DECODE_CHUNK))
+    scratch.ensure(T, n_heads, n_kv, head_dim, splits, q.device)
+    st = library("attention_decode").cj_decode_attention(
+        _ptr(q), _ptr(out), _ptr(k_plane), _ptr(v_plane), _ptr(positions), _ptr(row_req), _ptr(table), _i(table.stride(0)),
+        _i(page_tokens), _i(T), _i(n_heads), _i(n_kv), _i(head_dim), _i(window), _f(scale), _i(max_context),
+        _ptr(scratch.acc), _ptr(scratch.ml), _ptr(scratch.counters), _i(scratch.splits), _stream())
+    _check(st, "decode_attention")
+
+
+class DecodeScratch:
+    """Partial results of the split-KV decode kernel and its arrival counters (kept zero
+    between launches by the kernel itself)."""
+
+    def __init__(self):
+        self.acc = self.ml = self.counters = None
+        self.rows = self.heads = self.kv = self.hd = self.splits = 0
+
+    def ensure(self, rows: int, heads: int, kv: int, hd: int, splits: int, device) -> None:
+        if (self.acc is None or rows > self.rows or heads != self.heads or kv != self.kv or hd != self.hd
+                or splits > self.splits):
+            self.rows, self.heads, self.kv, self.hd = max(rows, self.rows), heads, kv, hd
+            self.splits = max(splits, self.splits)
+            self.acc = torch.empty((self.rows, heads, self.splits, hd), dtype=torch.float32, device=device)
+            self.ml = torch.empty((self.rows, heads, self.splits, 2), dtype=torch.float32, device=device)
+            self.counters = torch.zeros((self.rows * kv,), dtype=torch.int32, device=device)

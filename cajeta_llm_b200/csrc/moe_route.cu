@@ -1,5 +1,5 @@
-// Routing of a mixture of experts: router logits, softmax, top-k (fused, one block per
-// token) and the counting sort of the picks by expert.  Everything here is float32.
+// Routing of a mixture of experts: router logits, softmax and top-k, and the counting
+// sort of the picks by expert.  Everything here is float32.
 #include "common.cuh"
 
 using namespace cj;
@@ -9,39 +9,82 @@ namespace {
 constexpr int ROUTER_THREADS = 256;
 constexpr int MAX_EXPERTS = 1024;
 
-// l_e = sum_j Wr[e, j] * x_j; softmax over ALL experts; top-k by repeated argmax with a
-// strict '>' so that ties go to the lower index; w_k = p_sel; optional renormalisation
-// with the divisor clamped at 2^-14 (model/MoeFfn.cajeta:908-988; device twin
-// io/QuantKernel.cajeta:40849-40942).  Also the shared expert's gate:
-// sigma(sum_j g[j] * x_j) (model/MoeFfn.cajeta:1925-1964).
-__global__ void __launch_bounds__(ROUTER_THREADS) router_topk_kernel(
-    const float* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ shared_gate, int H, int E,
-    int k, int norm_topk, int* __restrict__ sel, float* __restrict__ w, float* __restrict__ shared_scale) {
-    __shared__ float probs[MAX_EXPERTS];
-    int t = blockIdx.x;
-    const float* row = x + (size_t)t * H;
-    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    constexpr int NW = ROUTER_THREADS / 32;
-
-    for (int e = warp; e < E + (shared_gate ? 1 : 0); e += NW) {
-        const float* wr = e < E ? Wr + (size_t)e * H : shared_gate;
-        float dot = 0.0f;
-        for (int j = lane; j < H; j += 32) dot = fmaf(wr[j], row[j], dot);
-        dot = warp_sum(dot);
-        if (lane == 0) {
-            if (e < E) probs[e] = dot;
-            else shared_scale[t] = 1.0f / (1.0f + expf(-dot));
-        }
+// Router in two launches.
+//
+// (1) logits: l[t, e] = sum_j Wr[e, j] * x[t, j] in float32, and in column E the shared
+// expert's gate dot g . x[t].  A block stages TOKB rows of x in shared memory and each of
+// its warps takes experts in turn, reading a weight row once for all TOKB rows; with few
+// rows (decode) the experts are spread over several blocks instead.  A lane sums its own
+// strided share of the row and the warp adds the 32 shares by butterfly, so a row's logits
+// depend on nothing but the row.
+// (2) select: softmax over ALL experts; top-k by repeated argmax with a strict '>' so
+// that ties go to the lower index; w_k = p_sel; optional renormalisation with the divisor
+// clamped at 2^-14 (model/MoeFfn.cajeta:908-988; device twin
+// io/QuantKernel.cajeta:40849-40942); the gate becomes sigma(g . x)
+// (model/MoeFfn.cajeta:1925-1964).
+template <int TOKB>
+__global__ void __launch_bounds__(ROUTER_THREADS) router_logits_kernel(
+    const float* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ shared_gate, int T, int H,
+    int E, int experts_per_block, float* __restrict__ logits) {
+    extern __shared__ __align__(16) float xs[];         // [TOKB][H]
+    const int t0 = blockIdx.x * TOKB;
+    const int n_tok = min(TOKB, T - t0);
+    const int n_cols = E + (shared_gate ? 1 : 0);
+    const int e_begin = blockIdx.y * experts_per_block;
+    const int e_end = min(n_cols, e_begin + experts_per_block);
+    for (int i = threadIdx.x; i < TOKB * H; i += ROUTER_THREADS) {
+        int tt = i / H;
+        xs[i] = tt < n_tok ? x[(size_t)t0 * H + i] : 0.0f;
     }
     __syncthreads();
-    if (warp != 0) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int NW = ROUTER_THREADS / 32;
+    const bool vec = (H % 4) == 0;
+    for (int e = e_begin + warp; e < e_end; e += NW) {
+        const float* wr = e < E ? Wr + (size_t)e * H : shared_gate;
+        float acc[TOKB];
+#pragma unroll
+        for (int tt = 0; tt < TOKB; ++tt) acc[tt] = 0.0f;
+        if (vec) {
+            for (int j = lane * 4; j < H; j += 128) {
+                float4 w4 = *(const float4*)(wr + j);
+#pragma unroll
+                for (int tt = 0; tt < TOKB; ++tt) {
+                    float4 x4 = *(const float4*)(xs + tt * H + j);
+                    acc[tt] = fmaf(w4.x, x4.x, acc[tt]);
+                    acc[tt] = fmaf(w4.y, x4.y, acc[tt]);
+                    acc[tt] = fmaf(w4.z, x4.z, acc[tt]);
+                    acc[tt] = fmaf(w4.w, x4.w, acc[tt]);
+                }
+            }
+        } else {
+            for (int j = lane; j < H; j += 32) {
+                float wv = wr[j];
+#pragma unroll
+                for (int tt = 0; tt < TOKB; ++tt) acc[tt] = fmaf(wv, xs[tt * H + j], acc[tt]);
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < TOKB; ++tt) {
+            float v = warp_sum(acc[tt]);
+            if (lane == 0 && tt < n_tok) logits[(size_t)(t0 + tt) * n_cols + e] = v;
+        }
+    }
+}
 
+__global__ void __launch_bounds__(32) router_select_kernel(
+    const float* __restrict__ logits, int E, int n_cols, int k, int norm_topk, int* __restrict__ sel,
+    float* __restrict__ w, float* __restrict__ shared_scale) {
+    __shared__ float probs[MAX_EXPERTS];
+    const int t = blockIdx.x, lane = threadIdx.x;
+    const float* row = logits + (size_t)t * n_cols;
+    if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-row[E]));
     float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, probs[e]);
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
     mx = warp_max(mx);
     float sum = 0.0f;
     for (int e = lane; e < E; e += 32) {
-        float p = expf(probs[e] - mx);
+        float p = expf(row[e] - mx);
         probs[e] = p;
         sum += p;
     }
@@ -110,13 +153,39 @@ __global__ void moe_group_kernel(const int* __restrict__ sel, int n, int k, int 
 
 }  // namespace
 
+// logits: scratch [T, E + 1] float32 (column E holds the shared gate's dot when a gate is given).
 CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* shared_gate, int T, int H, int E, int k,
-                             int norm_topk, int* sel, float* w, float* shared_scale, cudaStream_t stream) {
+                             int norm_topk, int* sel, float* w, float* shared_scale, float* logits,
+                             cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (!x || !Wr || !sel || !w || H <= 0) return CJ_ERR_ARG;
+    if (!x || !Wr || !sel || !w || !logits || H <= 0) return CJ_ERR_ARG;
     if (shared_gate && !shared_scale) return CJ_ERR_ARG;
     if (E < 1 || E > MAX_EXPERTS || k < 1 || k > E) return CJ_ERR_SIZE;
-    router_topk_kernel<<<T, ROUTER_THREADS, 0, stream>>>(x, Wr, shared_gate, H, E, k, norm_topk, sel, w, shared_scale);
+    const int n_cols = E + (shared_gate ? 1 : 0);
+    // rows of x staged per block: as many as fit 200 KB of shared memory, at most 8
+    int tokb = 8;
+    while (tokb > 1 && (size_t)tokb * H * sizeof(float) > 200 * 1024) tokb >>= 1;
+    if ((size_t)tokb * H * sizeof(float) > 200 * 1024) return CJ_ERR_SIZE;
+    size_t smem = (size_t)tokb * H * sizeof(float);
+    int row_blocks = (T + tokb - 1) / tokb;
+    // few rows: spread the experts over blocks (8 per block, one per warp)
+    int per_block = row_blocks >= 128 ? n_cols : 8;
+    dim3 grid(row_blocks, (n_cols + per_block - 1) / per_block);
+#define LAUNCH(TB)                                                                                                   \
+    {                                                                                                                \
+        static bool configured = false;                                                                              \
+        if (!configured) {                                                                                           \
+            cudaError_t e = cudaFuncSetAttribute(router_logits_kernel<TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            if (e != cudaSuccess) return (int)e;                                                                     \
+            configured = true;                                                                                       \
+        }                                                                                                            \
+        router_logits_kernel<TB><<<grid, ROUTER_THREADS, smem, stream>>>(x, Wr, shared_gate, T, H, E, per_block, logits); \
+    }
+    if (tokb == 8) LAUNCH(8) else if (tokb == 4) LAUNCH(4) else if (tokb == 2) LAUNCH(2) else LAUNCH(1)
+#undef LAUNCH
+    int st = launch_status();
+    if (st) return st;
+    router_select_kernel<<<T, 32, 0, stream>>>(logits, E, n_cols, k, norm_topk, sel, w, shared_gate ? shared_scale : nullptr);
     return launch_status();
 }
 

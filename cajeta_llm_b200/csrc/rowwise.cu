@@ -190,26 +190,28 @@ __global__ void moe_combine_kernel(float* __restrict__ hs, const float* __restri
                                    const float* __restrict__ w, int k, const float* __restrict__ shared,
                                    const float* __restrict__ shared_scale, int H) {
     int t = blockIdx.x;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float acc = 0.0f;
-        for (int j = 0; j < k; ++j) {
-            int s = slot_of_pick[t * k + j];
-            acc += w[t * k + j] * y[(size_t)s * H + i];
-        }
-        if (shared) {
-            float g = shared_scale ? shared_scale[t] : 1.0f;
-            acc += g * shared[(size_t)t * H + i];
-        }
-        hs[(size_t)t * H + i] += acc;
+    int i = blockIdx.y * blockDim.x + threadIdx.x;
+    if (i >= H) return;
+    float acc = 0.0f;
+    for (int j = 0; j < k; ++j) {
+        int s = slot_of_pick[t * k + j];
+        acc += w[t * k + j] * y[(size_t)s * H + i];
     }
+    if (shared) {
+        float g = shared_scale ? shared_scale[t] : 1.0f;
+        acc += g * shared[(size_t)t * H + i];
+    }
+    hs[(size_t)t * H + i] += acc;
 }
 
 CJ_EXPORT int cj_moe_combine(float* hs, const float* y, const int* slot_of_pick, const float* w, int k,
                              const float* shared, const float* shared_scale, int T, int H, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!hs || H <= 0 || k < 0 || (k > 0 && (!y || !slot_of_pick || !w))) return CJ_ERR_ARG;
-    int threads = H >= 1024 ? 256 : 128;
-    moe_combine_kernel<<<T, threads, 0, stream>>>(hs, y, slot_of_pick, w, k, shared, shared_scale, H);
+    int threads = H >= 256 ? 256 : 128;
+    dim3 grid(T, (H + threads - 1) / threads);
+    if (grid.y > 65535) return CJ_ERR_SIZE;
+    moe_combine_kernel<<<grid, threads, 0, stream>>>(hs, y, slot_of_pick, w, k, shared, shared_scale, H);
     return launch_status();
 }
 

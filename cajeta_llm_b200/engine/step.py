@@ -80,11 +80,32 @@ class StepContext:
     all_single: bool = False       # every request brings exactly one token
 
 
+@dataclass
+class _CapturedStep:
+    """A decode step of fixed batch size and context bucket, captured as a CUDA graph."""
+
+    graph: "torch.cuda.CUDAGraph"
+    meta: torch.Tensor          # static device metadata the captured kernels read
+    logits: torch.Tensor        # static output [batch, vocab]
+    launches: int               # kernels the graph replays
+
+
+GRAPH_CONTEXT_BUCKET = 1024     # captured decode steps are keyed by the context rounded up to this
+
+
 class ModelRunner:
-    """Owns a model and its cache; ``step`` is the only way tokens reach the model."""
+    """Owns a model and its cache; ``step`` is the only way tokens reach the model.
+
+    A step in which every request brings exactly one token (pure decode) is launch-bound:
+    hundreds of small kernels.  On the bfloat16 path such a step is captured once per
+    (batch size, context bucket) as a CUDA graph and replayed afterwards; the step's
+    metadata (tokens, positions, block tables) lives in a static device buffer that is
+    refreshed before each replay.  The captured kernels are the same ones an uncaptured
+    step launches, so both give the same logits.
+    """
 
     def __init__(self, model: Model, page_tokens: int = 16, max_seqs: int = 4, max_tokens_per_seq: int = 4096,
-                 num_pages: Optional[int] = None):
+                 num_pages: Optional[int] = None, cuda_graphs: bool = True):
         self.model = model
         self.runtime = model.runtime
         if num_pages is None:
@@ -92,7 +113,12 @@ class ModelRunner:
         self.cache = CacheManager(model.kv_needs(), model.state_needs(), model.cache_from(), page_tokens, max_seqs,
                                   max_tokens_per_seq, num_pages, self.runtime.cache_dtype, self.runtime.device)
         self.page_tokens = page_tokens
+        self.max_tokens_per_seq = max_tokens_per_seq
         self.steps_run = 0
+        self.cuda_graphs = cuda_graphs and self.runtime.fast_kernels and self.runtime.device.type == "cuda"
+        self._graphs: Dict[Tuple[int, int], _CapturedStep] = {}
+        self._graph_pool = None
+        self.graph_replays = 0
 
     # -- requests --------------------------------------------------------------------
     def admit(self) -> Optional[int]:
@@ -109,7 +135,17 @@ class ModelRunner:
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.runtime.device)
+        if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and not self.cache.state:
+            return self._step_captured(entries)
         ctx = self._prepare(entries)
+        logits = self._forward(ctx)
+        for e in entries:
+            self.cache.commit(e.slot, len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def _forward(self, ctx: StepContext) -> torch.Tensor:
+        """Embedding, every schedule entry, then final norm and head on the wanted rows."""
         hs = self.model.embed(ctx.token_ids)
         for i, e in enumerate(self.model.plan.schedule):
             k_plane, v_plane, group = self.cache.plane(i)
@@ -117,14 +153,79 @@ class ModelRunner:
                                 block_table=ctx.tables[group] if group is not None else None,
                                 page_tokens=self.page_tokens, state=self.cache.state.get(i))
             self.model.blocks[e.layer].forward(hs, ctx, ectx)
-        for e in entries:
-            self.cache.commit(e.slot, len(e.tokens))
-        self.steps_run += 1
         if ctx.want_rows.numel() == 0:
             return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.runtime.device)
         return self.model.logits(hs, ctx.want_rows)
 
+    def _step_captured(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Pure decode: logits of every row are computed by a captured graph; the wanted
+        ones are returned.  The first step of a (batch, bucket) runs uncaptured and is
+        then captured for the steps after it."""
+        from ..csrc import kernels as K
+        B = len(entries)
+        for e in entries:
+            if any(w != 0 for w in e.want):
+                raise StepError(f"want index {list(e.want)} is outside the 1 tokens of the entry")
+        longest = max(self.cache.length(e.slot) + 1 for e in entries)
+        bucket = min(-(-longest // GRAPH_CONTEXT_BUCKET) * GRAPH_CONTEXT_BUCKET, self.max_tokens_per_seq)
+        width = self.cache.books.max_pages_per_seq
+        all_rows = [StepEntry(e.slot, e.tokens, [0]) for e in entries]
+        host, layout = self._build_meta(all_rows, width)
+        key = (B, bucket)
+        cap = self._graphs.get(key)
+        if cap is None:
+            meta = torch.empty(host.shape, dtype=torch.int32, device=self.runtime.device)
+            meta.copy_(host, non_blocking=True)
+            ctx = self._context(meta, layout, all_rows, max_context=bucket)
+            logits = self._forward(ctx)                      # this step's result, uncaptured
+            torch.cuda.synchronize()
+            before = K.launches
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                static_logits = self._forward(ctx)
+            self._graphs[key] = _CapturedStep(graph, meta, static_logits, K.launches - before)
+        else:
+            cap.meta.copy_(host, non_blocking=True)
+            cap.graph.replay()
+            K.launches += cap.launches
+            self.graph_replays += 1
+            logits = cap.logits.clone()        # the static buffer is overwritten by the next replay
+        for e in entries:
+            self.cache.commit(e.slot, 1)
+        self.steps_run += 1
+        rows = [i for i, e in enumerate(entries) for _ in e.want]
+        if rows == list(range(B)):
+            return logits
+        if not rows:
+            return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.runtime.device)
+        return logits[torch.tensor(rows, device=logits.device)]
+
     def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        host, layout = self._build_meta(entries, None)
+        dev = host.to(self.runtime.device, non_blocking=True)
+        return self._context(dev, layout, entries)
+
+    def _context(self, dev: torch.Tensor, layout, entries: Sequence[StepEntry], max_context: Optional[int] = None) -> StepContext:
+        offs, R, width, G, req_start, req_prior, slots = layout
+
+        def view(i: int) -> torch.Tensor:
+            return dev[int(offs[i]): int(offs[i + 1])]
+
+        return StepContext(
+            n_rows=req_start[-1], n_requests=R, token_ids=view(0), positions=view(1), row_req=view(2), req_start=view(3),
+            req_prior=view(4), req_slot=view(5), want_rows=view(6),
+            tables=[view(7 + g).view(R, width) for g in range(G)],
+            h_req_start=req_start, h_req_prior=req_prior, h_req_slot=slots,
+            max_rows_per_request=max(len(e.tokens) for e in entries),
+            max_context=max_context if max_context is not None else max(p + len(e.tokens) for p, e in zip(req_prior, entries)),
+            all_single=all(len(e.tokens) == 1 for e in entries))
+
+    def _build_meta(self, entries: Sequence[StepEntry], width: Optional[int]):
+        """Checks the step, reserves its pages and lays its metadata into one pinned int32
+        buffer: tokens | positions | row->request | request starts | prior lengths | slots |
+        wanted rows | one block-table slab per cache group."""
         cache = self.cache
         vocab = self.model.vocab
         slots = [e.slot for e in entries]
@@ -151,9 +252,9 @@ class ModelRunner:
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
         n_want = sum(len(e.want) for e in entries)
-        width = cache.table_width(slots)
+        if width is None:
+            width = cache.table_width(slots)
         G = cache.num_groups
-        # one pinned int32 buffer: tokens | positions | row_req | req_start | req_prior | req_slot | want | tables
         sizes = [T, T, T, R + 1, R, R, n_want] + [R * width] * G
         offs = np.concatenate([[0], np.cumsum(sizes)])
         host = torch.empty((int(offs[-1]),), dtype=torch.int32, pin_memory=True)
@@ -178,16 +279,4 @@ class ModelRunner:
         h[offs[5]: offs[5] + R] = slots
         for g in range(G):
             h[offs[7 + g]: offs[7 + g] + R * width] = cache.table_rows(g, slots, width).reshape(-1)
-        dev = host.to(self.runtime.device, non_blocking=True)
-
-        def view(i: int) -> torch.Tensor:
-            return dev[int(offs[i]): int(offs[i + 1])]
-
-        return StepContext(
-            n_rows=T, n_requests=R, token_ids=view(0), positions=view(1), row_req=view(2), req_start=view(3),
-            req_prior=view(4), req_slot=view(5), want_rows=view(6),
-            tables=[view(7 + g).view(R, width) for g in range(G)],
-            h_req_start=req_start, h_req_prior=req_prior, h_req_slot=slots,
-            max_rows_per_request=max(len(e.tokens) for e in entries),
-            max_context=max(p + len(e.tokens) for p, e in zip(req_prior, entries)),
-            all_single=all(len(e.tokens) == 1 for e in entries))
+        return host, (offs, R, width, G, req_start, req_prior, slots)

@@ -100,6 +100,12 @@ class PagedAttention(Part):
                         ctx.positions, ctx.row_req, entry.block_table, entry.page_tokens, self.heads, self.kv_heads,
                         self.head_dim, pos.rotary_dim, pos.inv_freq, write)
         out = torch.empty_like(q)
-        K.paged_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
-                          entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale)
+        if rt.fast_kernels and getattr(ctx, "all_single", False) and self.head_dim in (64, 128):
+            # every request brings one token: the split-KV decode kernel
+            K.decode_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
+                               entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale,
+                               ctx.max_context, rt.decode_scratch)
+        else:
+            K.paged_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
+                              entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale)
         project(rt, out.view(T, self.q_dim), self.w_o, residual, bias=self.b_o, accumulate=True)

@@ -50,6 +50,15 @@ class Runtime:
         self.cache_dtype = DTYPES[dtype]
         self.device = torch.device(device)
         self.fast_kernels = fast_kernels and dtype == "bfloat16"
+        self._decode_scratch = None
+
+    @property
+    def decode_scratch(self):
+        """Scratch of the split-KV decode attention, shared by all layers (one stream)."""
+        if self._decode_scratch is None:
+            from ..csrc.kernels import DecodeScratch
+            self._decode_scratch = DecodeScratch()
+        return self._decode_scratch
 
     def matrix(self, t: torch.Tensor) -> torch.Tensor:
         return t.to(device=self.device, dtype=self.matrix_dtype).contiguous()

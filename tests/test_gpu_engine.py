@@ -191,3 +191,31 @@ def test_command_line(model_dirs, tmp_path):
     bad = subprocess.run([sys.executable, "-m", "cajeta_llm_b200", "run", "--model", model_dirs["A"], "--frobnicate"],
                          capture_output=True, text=True, cwd=helpers.ROOT, timeout=300)
     assert bad.returncode == 2 and "unknown flag '--frobnicate'" in bad.stderr
+
+
+def test_captured_decode_steps_give_the_same_logits_as_uncaptured_ones(model_dirs):
+    """Pure decode steps are replayed from a CUDA graph; they must equal, bit for bit, the
+    same steps launched kernel by kernel, also when the batch changes and pages move."""
+    from cajeta_llm_b200.engine.step import StepEntry
+    vocab = helpers.MEDIUM["vocab_size"]
+    seqs = [helpers.random_tokens(vocab, n, seed=80 + n) for n in (40, 23, 31)]
+    outs = {}
+    for graphs in (False, True):
+        r = runner_for(model_dirs["M"], "bfloat16", page_tokens=16, max_seqs=4, max_tokens_per_seq=64, cuda_graphs=graphs)
+        slots = [r.admit() for _ in seqs]
+        r.step([StepEntry(s, t[:7], []) for s, t in zip(slots, seqs)])
+        got = []
+        for i in range(7, 23):                       # three rows at a time
+            got.append(r.step([StepEntry(s, [t[i]], [0]) for s, t in zip(slots, seqs)]).clone())
+        r.release(slots[1])                          # then two, one of them wanting nothing
+        for i in range(23, 31):
+            got.append(r.step([StepEntry(slots[0], [seqs[0][i]], [0]), StepEntry(slots[2], [seqs[2][i]], [])]).clone())
+        outs[graphs] = torch.cat(got).cpu()
+        if graphs:
+            assert r.graph_replays >= 20
+    assert torch.equal(outs[True], outs[False])
+    want = torch.cat([torch.stack([helpers.plain_logits(model_dirs["M"], t)[i] for t in seqs]) for i in range(7, 23)]
+                     + [helpers.plain_logits(model_dirs["M"], seqs[0])[23:31]])
+    margins = torch.cat([torch.stack([helpers.plain_margins(model_dirs["M"], t)[i] for t in seqs]) for i in range(7, 23)]
+                        + [helpers.plain_margins(model_dirs["M"], seqs[0])[23:31]])
+    helpers.assert_close(outs[True], want, "bfloat16", "captured decode", margins)

@@ -341,3 +341,37 @@ def test_sampler_distribution_and_draws_follow_the_plain_sampler(K, V):
     want = P.prepared_distribution(logits[1].cpu(), 1.1, 0, 0.0, 1.0, [])
     agree = sum(int(g == P.draw(want, u)) for g, u in zip(out.cpu().tolist(), us))
     assert agree >= m - 1               # a draw within rounding of a boundary may fall either way
+
+
+@pytest.mark.parametrize("heads,n_kv,hd,page,window", [(16, 16, 128, 16, 0), (14, 2, 128, 16, 0), (6, 3, 64, 8, 0),
+                                                         (8, 4, 64, 16, 200), (4, 1, 128, 16, 130)])
+def test_decode_attention_split_kv(K, heads, n_kv, hd, page, window):
+    """Rows of very different lengths (1 key, exactly one chunk, several chunks and a
+    remainder) against the plain attention; run twice to see the arrival counters reset."""
+    lengths = [1, 128, 129, 700, 300, 17]
+    dtype = torch.bfloat16
+    kp, vp, table, ks, vs = paged_setup(lengths, n_kv, hd, page, dtype, seed=70)
+    rows = [(r, L - 1) for r, L in enumerate(lengths)]
+    g = torch.Generator().manual_seed(71)
+    q = torch.randn(len(rows), heads, hd, generator=g).to(dtype).to(DEV)
+    pos = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
+    req = torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    scratch = K.DecodeScratch()
+    outs = []
+    for _ in range(2):
+        out = torch.full_like(q, 7.0)
+        K.decode_attention(q, out, kp, vp, pos, req, table, page, heads, n_kv, hd, window, scale, max(lengths), scratch)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    assert int(scratch.counters.abs().sum()) == 0
+    for i, (r, p) in enumerate(rows):
+        qq = torch.zeros(p + 1, heads, hd, dtype=torch.float64)
+        qq[p] = q[i].double().cpu()
+        want = P.attention(qq, ks[r].to(dtype).double()[:p + 1], vs[r].to(dtype).double()[:p + 1], window, scale)[p]
+        assert torch.allclose(outs[0][i].double().cpu(), want, atol=2e-2, rtol=2e-2), (i, r, p)
+    # the same row alone gives the same bits: the chunking depends on the row only
+    out1 = torch.empty_like(q[3:4])
+    K.decode_attention(q[3:4].contiguous(), out1, kp, vp, pos[3:4].contiguous(), req[3:4].contiguous(), table, page, heads,
+                       n_kv, hd, window, scale, lengths[3], K.DecodeScratch())
+    assert torch.equal(out1[0], outs[0][3])
