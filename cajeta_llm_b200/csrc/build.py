@@ -37,6 +37,7 @@ LIBRARIES: Dict[str, str] = {
     "sampling": "sampling.cu",
     "gemm_tc": "gemm_tc.cu",
     "attention_decode": "attention_decode.cu",
+    "attention_prefill": "attention_prefill.cu",
 }
 HEADERS = ["common.cuh", "tc_common.cuh"]
 

@@ -375,3 +375,29 @@ def test_decode_attention_split_kv(K, heads, n_kv, hd, page, window):
     K.decode_attention(q[3:4].contiguous(), out1, kp, vp, pos[3:4].contiguous(), req[3:4].contiguous(), table, page, heads,
                        n_kv, hd, window, scale, lengths[3], K.DecodeScratch())
     assert torch.equal(out1[0], outs[0][3])
+
+
+@pytest.mark.parametrize("heads,n_kv,hd,page,window", [(4, 4, 128, 16, 0), (6, 2, 64, 16, 0), (8, 1, 128, 8, 70), (4, 2, 64, 16, 17)])
+def test_prefill_attention_tiles(K, heads, n_kv, hd, page, window):
+    """Requests with and without earlier tokens, portions that end inside a tile, a single
+    token riding along; every row against the plain attention."""
+    dtype = torch.bfloat16
+    totals = [200, 64, 131, 40, 300]
+    new = [200, 1, 67, 40, 130]                       # rows this step brings; the rest is already cached
+    kp, vp, table, ks, vs = paged_setup(totals, n_kv, hd, page, dtype, seed=90)
+    starts = [0]
+    for n in new:
+        starts.append(starts[-1] + n)
+    prior = [t - n for t, n in zip(totals, new)]
+    g = torch.Generator().manual_seed(91)
+    q = torch.randn(starts[-1], heads, hd, generator=g).to(dtype).to(DEV)
+    out = torch.full_like(q, 5.0)
+    scale = 1.0 / math.sqrt(hd)
+    K.prefill_attention(q, out, kp, vp, torch.tensor(starts, dtype=torch.int32, device=DEV),
+                        torch.tensor(prior, dtype=torch.int32, device=DEV), table, page, heads, n_kv, hd, window, scale)
+    for r, (T, n) in enumerate(zip(totals, new)):
+        qq = torch.zeros(T, heads, hd, dtype=torch.float64)
+        qq[T - n:] = q[starts[r]:starts[r + 1]].double().cpu()
+        want = P.attention(qq, ks[r].to(dtype).double(), vs[r].to(dtype).double(), window, scale)[T - n:]
+        got = out[starts[r]:starts[r + 1]].double().cpu()
+        assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), (r, float((got - want).abs().max()))
