@@ -6,10 +6,12 @@
 // K-major, so both feed tcgen05.mma straight from the 128-byte-swizzled tiles that TMA
 // lays into shared memory; accumulators are float32 in tensor memory.
 //
-// One block computes one output tile: warp 0 issues the TMA loads into a ring of stages,
-// warp 1 (one elected thread) issues the products and owns the tensor-memory allocation,
-// warps 2..5 read the accumulator back (each warp its own 32-lane quarter) and run the
-// epilogue.  Two orientations share the code:
+// Persistent blocks, one per SM, each taking tiles blockIdx.x, blockIdx.x + gridDim.x, ...:
+// warp 0 issues the TMA loads into a ring of stages and runs ahead across tile boundaries,
+// so the weight stream never stops; warp 1 (one elected thread) issues the products and
+// owns the tensor-memory allocation; warps 2..5 read an accumulator back (each warp its
+// own 32-lane quarter) and run the epilogue while the products of the next tile fill the
+// second accumulator.  Two orientations share the code:
 //   * tokens on the 128 rows of the product (SWAP = false): a step with many rows
 //     (prompt portions);
 //   * weights on the 128 rows, tokens on the product's N (SWAP = true, TOK = 16..128): a
@@ -20,7 +22,8 @@
 // (two weight tiles, two accumulators), bf16 store.
 // Grouped form (mixture of experts): token rows are sorted by expert, offsets[g] is the
 // first row of group g, the weights of group g start at row g * features of W; a block
-// finds its (group, tile) by walking the offsets and masks rows past the group's end.
+// finds the (group, tile) of a tile index in a prefix table built at its start and masks
+// rows past the group's end.
 //
 // reference counterpart: the indirected per-expert GEMMs over (expert, row range) chunk
 // maps, io/WmmaKernel.cajeta (q4kWmmaIdMwKernel), and the dense projection GEMMs of
@@ -62,56 +65,74 @@ struct Smem {
     static constexpr int TOTAL = TILE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
+constexpr int ACC_STAGES = 2;       // accumulators in tensor memory: one is drained while the next is filled
+constexpr int MAX_GROUPS = 1024;
+
+// Work of one block, in the order it takes its tiles: tile = blockIdx.x + i * gridDim.x.
+// A tile index splits into (feature tile, token tile, K split), the feature tile running
+// fastest so that neighbouring blocks stream different weights.
+struct TileCoord {
+    int tok0, tok_end, feat0, w_row0, kb_begin, n_kb, split;
+    bool valid;
+};
+
+template <int TOK_TILE, int FEAT_TILE>
+__device__ __forceinline__ TileCoord decode_tile(const Args& p, int tile, int feat_tiles, int tok_tiles, const int* tiles_before) {
+    TileCoord c;
+    int f = tile % feat_tiles;
+    int rest = tile / feat_tiles;
+    int tt = rest % tok_tiles;
+    c.split = rest / tok_tiles;
+    c.valid = true;
+    int group = 0;
+    if (p.group_offsets) {
+        // tiles_before[g] = token tiles of the groups before g; find the group that holds tile tt
+        int lo = 0, hi = p.groups;                 // invariant: tiles_before[lo] <= tt, answer in [lo, hi)
+        if (tt >= tiles_before[p.groups]) { c.valid = false; return c; }
+        while (hi - lo > 1) {
+            int mid = (lo + hi) >> 1;
+            if (tiles_before[mid] <= tt) lo = mid; else hi = mid;
+        }
+        group = lo;
+        int g_lo = p.group_offsets[group], g_hi = p.group_offsets[group + 1];
+        c.tok0 = g_lo + (tt - tiles_before[group]) * TOK_TILE;
+        c.tok_end = min(g_hi, c.tok0 + TOK_TILE);
+    } else {
+        c.tok0 = tt * TOK_TILE;
+        c.tok_end = min(p.tokens, c.tok0 + TOK_TILE);
+    }
+    c.feat0 = f * FEAT_TILE;
+    c.w_row0 = group * p.features + c.feat0;
+    int k_blocks_total = (p.K + BK - 1) / BK;
+    int per_split = (k_blocks_total + p.k_splits - 1) / p.k_splits;
+    c.kb_begin = c.split * per_split;
+    c.n_kb = max(0, min(k_blocks_total, c.kb_begin + per_split) - c.kb_begin);
+    return c;
+}
+
 template <int N_MMA, bool SWAP, bool DUAL, int EPI, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-               const __grid_constant__ CUtensorMap map_w2, Args p) {
+               const __grid_constant__ CUtensorMap map_w2, Args p, int feat_tiles, int tok_tiles, int total_tiles) {
     using S = Smem<N_MMA, SWAP, DUAL, STAGES>;
     constexpr int TOK_TILE = S::X_ROWS;          // token rows a tile covers
     constexpr int FEAT_TILE = S::W_ROWS;         // weight rows a tile covers
     constexpr uint32_t ACC_COLS = N_MMA;         // tensor-memory columns of one accumulator
-    constexpr uint32_t TMEM_COLS_NEEDED = ACC_COLS * (DUAL ? 2 : 1);
+    constexpr uint32_t STAGE_COLS = ACC_COLS * (DUAL ? 2 : 1);
+    constexpr uint32_t TMEM_COLS_NEEDED = STAGE_COLS * ACC_STAGES;
     constexpr uint32_t TMEM_COLS = TMEM_COLS_NEEDED <= 32 ? 32 : TMEM_COLS_NEEDED <= 64 ? 64 : TMEM_COLS_NEEDED <= 128 ? 128
                                    : TMEM_COLS_NEEDED <= 256 ? 256 : 512;
-
-    // ---- which tile ------------------------------------------------------------------
-    int tok0, tok_end, group = 0;
-    if (p.group_offsets) {
-        int tile = blockIdx.y, first = 0;
-        bool found = false;
-        for (int g = 0; g < p.groups; ++g) {
-            int lo = p.group_offsets[g], hi = p.group_offsets[g + 1];
-            int tiles = (hi - lo + TOK_TILE - 1) / TOK_TILE;
-            if (tile < first + tiles) {
-                tok0 = lo + (tile - first) * TOK_TILE;
-                tok_end = min(hi, tok0 + TOK_TILE);
-                group = g;
-                found = true;
-                break;
-            }
-            first += tiles;
-        }
-        if (!found) return;
-    } else {
-        tok0 = blockIdx.y * TOK_TILE;
-        tok_end = min(p.tokens, tok0 + TOK_TILE);
-        if (tok0 >= p.tokens) return;
-    }
-    const int feat0 = blockIdx.x * FEAT_TILE;                       // within the group
-    const int w_row0 = group * p.features + feat0;                  // row of W (all groups stacked)
-    const int k_blocks_total = (p.K + BK - 1) / BK;
-    const int per_split = (k_blocks_total + p.k_splits - 1) / p.k_splits;
-    const int kb_begin = blockIdx.z * per_split;
-    const int kb_end = min(k_blocks_total, kb_begin + per_split);
-    const int n_kb = max(0, kb_end - kb_begin);
+    static_assert(TMEM_COLS_NEEDED <= 512, "accumulators do not fit tensor memory");
 
     // ---- shared memory -----------------------------------------------------------------
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(tiles + S::TILE_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
-    uint64_t* acc_bar = empty_bar + STAGES;
-    uint32_t* tmem_slot = (uint32_t*)(acc_bar + 1);
+    uint64_t* acc_full = empty_bar + STAGES;
+    uint64_t* acc_empty = acc_full + ACC_STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + ACC_STAGES);
+    __shared__ int tiles_before[MAX_GROUPS + 1];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -119,8 +140,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(acc_bar, 1);
+        for (int s = 0; s < ACC_STAGES; ++s) {
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], 4);          // one arrival per epilogue warp
+        }
         fence_barrier_init();
+    }
+    if (p.group_offsets && warp == 2) {
+        // token tiles before each group (a warp scan over the groups, 32 at a time)
+        int carry = 0;
+        for (int g0 = 0; g0 < p.groups; g0 += 32) {
+            int g = g0 + lane;
+            int n = g < p.groups ? (p.group_offsets[g + 1] - p.group_offsets[g] + TOK_TILE - 1) / TOK_TILE : 0;
+            int inc = n;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int v = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += v;
+            }
+            if (g < p.groups) tiles_before[g] = carry + inc - n;
+            carry += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) tiles_before[p.groups] = carry;
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
     tcgen05_fence_before();
@@ -129,67 +170,92 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---- TMA producer ----------------------------------------------------------------
+        // ---- TMA producer: streams stage after stage, straight across tile boundaries ----------
         if (elect_one()) {
             tma_prefetch_descriptor(&map_x);
             tma_prefetch_descriptor(&map_w);
             if (DUAL) tma_prefetch_descriptor(&map_w2);
-            for (int i = 0; i < n_kb; ++i) {
-                int s = i % STAGES;
-                uint32_t round = i / STAGES;
-                if (i >= STAGES && !mbar_wait(&empty_bar[s], (round - 1) & 1, 1)) break;
-                uint8_t* st = tiles + (size_t)s * S::STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
-                int k0 = (kb_begin + i) * BK;
-                tma_load_2d(st, &map_x, &full_bar[s], k0, tok0);
-                tma_load_2d(st + S::X_BYTES, &map_w, &full_bar[s], k0, w_row0);
-                if (DUAL) tma_load_2d(st + S::X_BYTES + S::W_BYTES, &map_w2, &full_bar[s], k0, w_row0);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                TileCoord c = decode_tile<TOK_TILE, FEAT_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before);
+                if (!c.valid) continue;
+                for (int i = 0; i < c.n_kb; ++i, ++it) {
+                    int s = it % STAGES;
+                    ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, 1);
+                    if (!ok) break;
+                    uint8_t* st = tiles + (size_t)s * S::STAGE_BYTES;
+                    mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+                    int k0 = (c.kb_begin + i) * BK;
+                    tma_load_2d(st, &map_x, &full_bar[s], k0, c.tok0);
+                    tma_load_2d(st + S::X_BYTES, &map_w, &full_bar[s], k0, c.w_row0);
+                    if (DUAL) tma_load_2d(st + S::X_BYTES + S::W_BYTES, &map_w2, &full_bar[s], k0, c.w_row0);
+                }
             }
         }
     } else if (warp == 1) {
         // ---- product issue -----------------------------------------------------------------
         if (elect_one()) {
             constexpr uint32_t idesc = umma_idesc_bf16(128, N_MMA);
+            uint32_t it = 0, acc_it = 0;
             bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                int s = i % STAGES;
-                uint32_t round = i / STAGES;
-                ok = mbar_wait(&full_bar[s], round & 1, 2);
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                TileCoord c = decode_tile<TOK_TILE, FEAT_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before);
+                if (!c.valid) continue;
+                const int as = acc_it % ACC_STAGES;
+                ok = mbar_wait(&acc_empty[as], ((acc_it / ACC_STAGES) & 1) ^ 1, 4);      // the epilogue has drained it
                 if (!ok) break;
                 tcgen05_fence_after();
-                uint8_t* st = tiles + (size_t)s * S::STAGE_BYTES;
-                uint64_t dx = umma_desc_sw128(st);
-                uint64_t dw = umma_desc_sw128(st + S::X_BYTES);
-                uint64_t dw2 = DUAL ? umma_desc_sw128(st + S::X_BYTES + S::W_BYTES) : 0;
+                const uint32_t acc_addr = tmem_base + as * STAGE_COLS;
+                for (int i = 0; i < c.n_kb; ++i, ++it) {
+                    int s = it % STAGES;
+                    ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, 2);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    uint8_t* st = tiles + (size_t)s * S::STAGE_BYTES;
+                    uint64_t dx = umma_desc_sw128(st);
+                    uint64_t dw = umma_desc_sw128(st + S::X_BYTES);
+                    uint64_t dw2 = DUAL ? umma_desc_sw128(st + S::X_BYTES + S::W_BYTES) : 0;
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    uint64_t step = (uint64_t)((k * UMMA_K * 2) >> 4);       // 32 bytes along K inside the swizzle row
-                    uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-                    if (SWAP) {
-                        umma_bf16(tmem_base, dw + step, dx + step, idesc, acc);
-                        if (DUAL) umma_bf16(tmem_base + ACC_COLS, dw2 + step, dx + step, idesc, acc);
-                    } else {
-                        umma_bf16(tmem_base, dx + step, dw + step, idesc, acc);
-                        if (DUAL) umma_bf16(tmem_base + ACC_COLS, dx + step, dw2 + step, idesc, acc);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        uint64_t step = (uint64_t)((k * UMMA_K * 2) >> 4);       // 32 bytes along K inside the swizzle row
+                        uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                        if (SWAP) {
+                            umma_bf16(acc_addr, dw + step, dx + step, idesc, acc);
+                            if (DUAL) umma_bf16(acc_addr + ACC_COLS, dw2 + step, dx + step, idesc, acc);
+                        } else {
+                            umma_bf16(acc_addr, dx + step, dw + step, idesc, acc);
+                            if (DUAL) umma_bf16(acc_addr + ACC_COLS, dx + step, dw2 + step, idesc, acc);
+                        }
                     }
+                    umma_commit(&empty_bar[s]);          // the stage is free once these products have read it
                 }
-                umma_commit(&empty_bar[s]);          // the stage is free once these products have read it
+                if (!ok) break;
+                umma_commit(&acc_full[as]);              // this tile's accumulator is complete
+                ++acc_it;
             }
-            umma_commit(acc_bar);                    // the accumulator is complete
         }
     } else {
         // ---- epilogue: warps 2..5, each its own quarter of the 128 lanes --------------------
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;           // accumulator row of this thread
-        bool ok = n_kb > 0 ? mbar_wait(acc_bar, 0, 3) : true;
-        tcgen05_fence_after();
-        if (ok) {
-            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            const long long split_off = (long long)blockIdx.z * p.split_stride;
+        uint32_t acc_it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            TileCoord c = decode_tile<TOK_TILE, FEAT_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before);
+            if (!c.valid) continue;
+            const int as = acc_it % ACC_STAGES;
+            ok = mbar_wait(&acc_full[as], (acc_it / ACC_STAGES) & 1, 3);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const uint32_t lane_base = tmem_base + as * STAGE_COLS + ((uint32_t)(quarter * 32) << 16);
+            const long long split_off = (long long)c.split * p.split_stride;
+            const bool add_bias = p.bias != nullptr && c.split == 0;
 #pragma unroll 1
             for (int c0 = 0; c0 < N_MMA; c0 += 16) {
+                if (SWAP && c.tok0 + c0 >= c.tok_end) break;           // no token left in these columns
                 uint32_t v0[16], v1[16];
-                if (n_kb > 0) {
+                if (c.n_kb > 0) {
                     tmem_ld16(lane_base + c0, v0);
                     if (DUAL) tmem_ld16(lane_base + ACC_COLS + c0, v1);
                     tmem_ld_wait();
@@ -197,21 +263,79 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v0[j] = v1[j] = 0;
                 }
+                float v[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    int c = c0 + j;
-                    int token = SWAP ? tok0 + c : tok0 + r;
-                    int feat = SWAP ? feat0 + r : feat0 + c;
-                    if (token >= tok_end || feat >= p.features) continue;
-                    float v = __uint_as_float(v0[j]);
-                    if (EPI == EPI_SWIGLU_BF16) v = cj::silu(v) * __uint_as_float(v1[j]);
-                    if (p.bias && blockIdx.z == 0) v += p.bias[feat];
-                    long long o = (long long)token * p.ldo + feat;
-                    if (EPI == EPI_STORE_F32) ((float*)p.out)[o + split_off] = v;
-                    else if (EPI == EPI_ACC_F32) ((float*)p.out)[o] += v;
-                    else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
+                    v[j] = __uint_as_float(v0[j]);
+                    if (EPI == EPI_SWIGLU_BF16) v[j] = cj::silu(v[j]) * __uint_as_float(v1[j]);
+                }
+                if (!SWAP) {
+                    // this thread owns one token row and 16 consecutive features of it
+                    const int token = c.tok0 + r, feat = c.feat0 + c0;
+                    if (token >= c.tok_end || feat >= p.features) continue;
+                    const long long o = (long long)token * p.ldo + feat;
+                    const bool whole = feat + 16 <= p.features;
+                    if (add_bias) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (whole || feat + j < p.features) v[j] += p.bias[feat + j];
+                    }
+                    if (EPI == EPI_STORE_F32 || EPI == EPI_ACC_F32) {
+                        float* dst = (float*)p.out + o + (EPI == EPI_STORE_F32 ? split_off : 0);
+                        if (whole && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 4) {
+                                float4 w4 = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                if (EPI == EPI_ACC_F32) {
+                                    float4 old = *(float4*)(dst + j);
+                                    w4.x += old.x; w4.y += old.y; w4.z += old.z; w4.w += old.w;
+                                }
+                                *(float4*)(dst + j) = w4;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (feat + j < p.features) dst[j] = EPI == EPI_ACC_F32 ? dst[j] + v[j] : v[j];
+                        }
+                    } else {
+                        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + o;
+                        if (whole && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 8) {
+                                uint4 u;
+                                __nv_bfloat162* b2 = (__nv_bfloat162*)&u;
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) b2[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+                                *(uint4*)(dst + j) = u;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (feat + j < p.features) dst[j] = __float2bfloat16_rn(v[j]);
+                        }
+                    }
+                } else {
+                    // this thread owns one feature; column j is token tok0 + c0 + j, so a warp
+                    // writes 32 consecutive features of a token at a time
+                    const int feat = c.feat0 + r;
+                    if (feat >= p.features) continue;
+                    const float b = add_bias ? p.bias[feat] : 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        int token = c.tok0 + c0 + j;
+                        if (token >= c.tok_end) break;
+                        long long o = (long long)token * p.ldo + feat;
+                        float val = v[j] + b;
+                        if (EPI == EPI_STORE_F32) ((float*)p.out)[o + split_off] = val;
+                        else if (EPI == EPI_ACC_F32) ((float*)p.out)[o] += val;
+                        else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val);
+                    }
                 }
             }
+            // this warp has read its quarter of the accumulator: hand the stage back
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[as]);
+            ++acc_it;
         }
     }
     tcgen05_fence_before();
@@ -220,6 +344,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
+}
+
+inline int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
 }
 
 template <int N_MMA, bool SWAP, bool DUAL, int EPI, int STAGES>
@@ -232,10 +366,13 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2,
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
+    if (a.group_offsets && a.groups > MAX_GROUPS) return CJ_ERR_SIZE;
+    int feat_tiles = (a.features + S::W_ROWS - 1) / S::W_ROWS;
     int tok_tiles = (a.tokens + S::X_ROWS - 1) / S::X_ROWS + (a.group_offsets ? a.groups : 0);
-    dim3 grid((a.features + S::W_ROWS - 1) / S::W_ROWS, tok_tiles, a.k_splits);
-    if (grid.y > 65535 || grid.z > 65535) return CJ_ERR_SIZE;
-    kern<<<grid, THREADS, S::TOTAL, stream>>>(mx, mw, mw2, a);
+    long long total = (long long)feat_tiles * tok_tiles * a.k_splits;
+    if (total > 0x7fffffffLL) return CJ_ERR_SIZE;
+    int grid = (int)(total < sm_count() ? total : sm_count());
+    kern<<<grid, THREADS, S::TOTAL, stream>>>(mx, mw, mw2, a, feat_tiles, tok_tiles, (int)total);
     return cj::launch_status();
 }
 
