@@ -214,7 +214,7 @@ def main() -> int:
         for blk in runner.model.blocks:
             off = getattr(blk.feed_forward, "last_offsets", None)
             if off is not None:
-                o = off.cpu().numpy()
+                o = off.cpu().numpy()[: cfg["num_experts"] + 1]       # the routed groups (shared chunks follow them)
                 distinct += int((o[1:] > o[:-1]).sum())
         ctx_len = PROMPT + n_warm + n_steps
         step_bytes = (n_layers * nums["per_layer_fixed"] + distinct * nums["per_expert"] + nums["head"]

@@ -203,11 +203,15 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
 
 
 def moe_group(sel: torch.Tensor, top_k: int, num_experts: int, offsets: torch.Tensor, slot_token: torch.Tensor,
-              slot_of_pick: torch.Tensor) -> None:
-    """Counting sort of the picks by expert: offsets [E + 1], slot_token, slot_of_pick."""
+              slot_of_pick: torch.Tensor, extra_groups: int = 0) -> None:
+    """Counting sort of the picks by expert: offsets [E + extra + 1], slot_token, slot_of_pick.
+    ``extra_groups`` groups that hold every token follow the routed ones."""
     for n, t in (("sel", sel), ("offsets", offsets), ("slot_token", slot_token), ("slot_of_pick", slot_of_pick)):
         _need(t, n, torch.int32)
-    st = library("moe_route").cj_moe_group(_ptr(sel), _i(sel.numel()), _i(top_k), _i(num_experts), _ptr(offsets),
+    n = sel.numel()
+    if offsets.numel() < num_experts + extra_groups + 1 or slot_token.numel() < n + extra_groups * (n // top_k):
+        raise KernelError("moe_group: offsets or slot_token too small for the extra groups")
+    st = library("moe_route").cj_moe_group(_ptr(sel), _i(n), _i(top_k), _i(num_experts), _i(extra_groups), _ptr(offsets),
                                            _ptr(slot_token), _ptr(slot_of_pick), _stream())
     _check(st, "moe_group")
 
@@ -215,7 +219,8 @@ def moe_group(sel: torch.Tensor, top_k: int, num_experts: int, offsets: torch.Te
 def moe_combine(hs: torch.Tensor, y: Optional[torch.Tensor], slot_of_pick: Optional[torch.Tensor],
                 weights: Optional[torch.Tensor], top_k: int, shared: Optional[torch.Tensor],
                 shared_scale: Optional[torch.Tensor]) -> None:
-    """hs[t] += sum_j weights[t, j] * y[slot_of_pick[t, j]] (+ shared_scale[t] * shared[t])."""
+    """hs[t] += sum_j weights[t, j] * y[slot_of_pick[t, j]] (+ shared_scale[t] * sum_c shared[c, t]).
+    ``shared`` is [T, H] or, computed in chunks, [chunks, T, H]."""
     _need(hs, "hs", torch.float32)
     T, H = hs.shape
     for n, t in (("y", y), ("weights", weights), ("shared", shared), ("shared_scale", shared_scale)):
@@ -223,8 +228,11 @@ def moe_combine(hs: torch.Tensor, y: Optional[torch.Tensor], slot_of_pick: Optio
             _need(t, n, torch.float32)
     if slot_of_pick is not None:
         _need(slot_of_pick, "slot_of_pick", torch.int32)
+    chunks, stride = 1, 0
+    if shared is not None and shared.dim() == 3:
+        chunks, stride = shared.shape[0], shared.stride(0)
     st = library("rowwise").cj_moe_combine(_ptr(hs), _ptr(y), _ptr(slot_of_pick), _ptr(weights), _i(top_k), _ptr(shared),
-                                           _ptr(shared_scale), _i(T), _i(H), _stream())
+                                           _i(chunks), _ll(stride), _ptr(shared_scale), _i(T), _i(H), _stream())
     _check(st, "moe_combine")
 
 

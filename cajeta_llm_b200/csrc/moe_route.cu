@@ -46,6 +46,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_logits_kernel(
 #pragma unroll
         for (int tt = 0; tt < TOKB; ++tt) acc[tt] = 0.0f;
         if (vec) {
+#pragma unroll 4
             for (int j = lane * 4; j < H; j += 128) {
                 float4 w4 = *(const float4*)(wr + j);
 #pragma unroll
@@ -125,10 +126,24 @@ __global__ void __launch_bounds__(32) router_select_kernel(
 // expert: it counts the picks of lower experts (its first slot) and then places its own
 // in pick order.  reference: model/MoeFfn.cajeta:2064-2099 (groupPicks), device
 // io/QuantKernel.cajeta:41069.
-__global__ void moe_group_kernel(const int* __restrict__ sel, int n, int k, int E, int* __restrict__ offsets,
+//
+// After the E routed groups come `extra` groups that every token belongs to (the chunks
+// of a shared expert run through the same grouped products): group E + c owns slots
+// [n + c * T, n + (c + 1) * T) and slot n + c * T + t reads token t.
+__global__ void moe_group_kernel(const int* __restrict__ sel, int n, int k, int E, int extra, int* __restrict__ offsets,
                                  int* __restrict__ slot_token, int* __restrict__ slot_of_pick) {
     int e = blockIdx.x;
     int lane = threadIdx.x;
+    const int T = n / k;
+    if (e >= E) {
+        int c = e - E;
+        for (int t = lane; t < T; t += 32) slot_token[n + c * T + t] = t;
+        if (lane == 0) {
+            offsets[E + c] = n + c * T;
+            if (c == extra - 1) offsets[E + extra] = n + extra * T;
+        }
+        return;
+    }
     int below = 0;
     for (int i = lane; i < n; i += 32) below += sel[i] < e ? 1 : 0;
 #pragma unroll
@@ -147,7 +162,7 @@ __global__ void moe_group_kernel(const int* __restrict__ sel, int n, int k, int 
     }
     if (lane == 0) {
         offsets[e] = below;
-        if (e == E - 1) offsets[E] = cursor;
+        if (e == E - 1 && extra == 0) offsets[E] = cursor;
     }
 }
 
@@ -169,7 +184,7 @@ CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* share
     size_t smem = (size_t)tokb * H * sizeof(float);
     int row_blocks = (T + tokb - 1) / tokb;
     // few rows: spread the experts over blocks (8 per block, one per warp)
-    int per_block = row_blocks >= 128 ? n_cols : 8;
+    int per_block = row_blocks >= 128 ? n_cols : (row_blocks >= 16 ? 32 : 8);
     dim3 grid(row_blocks, (n_cols + per_block - 1) / per_block);
 #define LAUNCH(TB)                                                                                                   \
     {                                                                                                                \
@@ -189,12 +204,12 @@ CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* share
     return launch_status();
 }
 
-// sel: [n_picks] expert of pick i = t * k + j.  Outputs: offsets [E + 1], slot_token
-// [n_picks] (the token whose row feeds sorted slot s), slot_of_pick [n_picks].
-CJ_EXPORT int cj_moe_group(const int* sel, int n_picks, int k, int E, int* offsets, int* slot_token,
+// sel: [n_picks] expert of pick i = t * k + j.  Outputs: offsets [E + extra + 1], slot_token
+// [n_picks + extra * T] (the token whose row feeds sorted slot s), slot_of_pick [n_picks].
+CJ_EXPORT int cj_moe_group(const int* sel, int n_picks, int k, int E, int extra, int* offsets, int* slot_token,
                            int* slot_of_pick, cudaStream_t stream) {
-    if (E < 1 || k < 1 || n_picks < 0) return CJ_ERR_SIZE;
+    if (E < 1 || k < 1 || n_picks < 0 || extra < 0) return CJ_ERR_SIZE;
     if (!sel || !offsets || !slot_token || !slot_of_pick) return CJ_ERR_ARG;
-    moe_group_kernel<<<E, 32, 0, stream>>>(sel, n_picks, k, E, offsets, slot_token, slot_of_pick);
+    moe_group_kernel<<<E + extra, 32, 0, stream>>>(sel, n_picks, k, E, extra, offsets, slot_token, slot_of_pick);
     return launch_status();
 }

@@ -181,14 +181,16 @@ CJ_EXPORT int cj_rope_kv_write(const float* qkv, int ld, int q_off, int k_off, i
 
 // ---------------------------------------------------------------------------------
 // Combine of the mixture's outputs into the residual stream, per token and in a fixed
-// order: acc = sum_j w[t,j] * y[slot(t,j)] for j = 0..k-1 (selection order), then
-// acc += gate[t] * shared[t]; hs[t] += acc.  No atomics: one thread owns an element.
+// order: acc = sum_j w[t,j] * y[slot(t,j)] for j = 0..k-1 (selection order), then the
+// shared expert: acc += gate[t] * sum_c shared[c][t] over its `chunks` partial results in
+// chunk order (one chunk when it was computed whole); hs[t] += acc.  No atomics: one
+// thread owns an element.
 // reference: model/MoeFfn.cajeta:1849-1916 (row form), combine kernel
 // io/QuantKernel.cajeta:40747; shared expert model/Prim.cajeta:1652-1664.
 // ---------------------------------------------------------------------------------
 __global__ void moe_combine_kernel(float* __restrict__ hs, const float* __restrict__ y, const int* __restrict__ slot_of_pick,
-                                   const float* __restrict__ w, int k, const float* __restrict__ shared,
-                                   const float* __restrict__ shared_scale, int H) {
+                                   const float* __restrict__ w, int k, const float* __restrict__ shared, int chunks,
+                                   long long chunk_stride, const float* __restrict__ shared_scale, int H) {
     int t = blockIdx.x;
     int i = blockIdx.y * blockDim.x + threadIdx.x;
     if (i >= H) return;
@@ -198,20 +200,24 @@ __global__ void moe_combine_kernel(float* __restrict__ hs, const float* __restri
         acc += w[t * k + j] * y[(size_t)s * H + i];
     }
     if (shared) {
+        float sh = 0.0f;
+        for (int c = 0; c < chunks; ++c) sh += shared[c * chunk_stride + (size_t)t * H + i];
         float g = shared_scale ? shared_scale[t] : 1.0f;
-        acc += g * shared[(size_t)t * H + i];
+        acc += g * sh;
     }
     hs[(size_t)t * H + i] += acc;
 }
 
 CJ_EXPORT int cj_moe_combine(float* hs, const float* y, const int* slot_of_pick, const float* w, int k,
-                             const float* shared, const float* shared_scale, int T, int H, cudaStream_t stream) {
+                             const float* shared, int chunks, long long chunk_stride, const float* shared_scale, int T,
+                             int H, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!hs || H <= 0 || k < 0 || (k > 0 && (!y || !slot_of_pick || !w))) return CJ_ERR_ARG;
+    if (shared && chunks < 1) return CJ_ERR_ARG;
     int threads = H >= 256 ? 256 : 128;
     dim3 grid(T, (H + threads - 1) / threads);
     if (grid.y > 65535) return CJ_ERR_SIZE;
-    moe_combine_kernel<<<grid, threads, 0, stream>>>(hs, y, slot_of_pick, w, k, shared, shared_scale, H);
+    moe_combine_kernel<<<grid, threads, 0, stream>>>(hs, y, slot_of_pick, w, k, shared, chunks, chunk_stride, shared_scale, H);
     return launch_status();
 }
 

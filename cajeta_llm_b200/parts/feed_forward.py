@@ -12,7 +12,11 @@ probabilities, optionally renormalised with the divisor clamped at 2^-14
 (model/MoeFfn.cajeta:1849-1916); an optional shared expert of
 ``shared_intermediate_size`` is added, scaled by ``sigma(g . x)`` when it has a gate
 (model/MoeFfn.cajeta:1925-1964).  Tokens are grouped by expert with a counting sort and
-each expert multiplies its own rows (model/MoeFfn.cajeta:2064-2099,2644-2777).
+each expert multiplies its own rows (model/MoeFfn.cajeta:2064-2099,2644-2777).  When the
+shared expert's width is a multiple of the experts' width it is cut into chunks of that
+width which ride through the same two grouped products as extra groups that every token
+belongs to (their partial down-projections are summed in chunk order by the combine):
+one launch streams all expert weights of the layer.
 Parameters: ``hidden_size``, ``num_experts``, ``top_k``, ``expert_intermediate_size``,
 ``shared_intermediate_size`` (0 = none), ``shared_gate``, ``norm_topk_prob``.
 
@@ -84,6 +88,10 @@ class SparseMoE(Part):
         self.ws_gate = self.ws_up = self.ws_down = None
         self.shared_gate_w = None
         self.last_offsets = None
+        # chunks of the shared expert that run as extra groups of the grouped products
+        self.shared_chunks = 0
+        if self.shared_inter > 0 and self.shared_inter % self.inter == 0 and self.shared_inter // self.inter <= 64:
+            self.shared_chunks = self.shared_inter // self.inter
 
     def params(self) -> Dict[str, ParamSpec]:
         p = {self.name("gate.weight"): ParamSpec((self.num_experts, self.hidden), role="vector")}
@@ -103,19 +111,28 @@ class SparseMoE(Part):
         rt = self.runtime
         self.router = self.fetch(source, self.name("gate.weight"))
 
+        E, C, I = self.num_experts, self.shared_chunks, self.inter
+
         def slab(proj: str, rows: int, cols: int) -> torch.Tensor:
-            out = torch.empty((self.num_experts, rows, cols), dtype=rt.matrix_dtype, device=rt.device)
-            for e in range(self.num_experts):
+            out = torch.empty((E + C, rows, cols), dtype=rt.matrix_dtype, device=rt.device)
+            for e in range(E):
                 out[e].copy_(self.fetch(source, self.name(f"experts.{e}.{proj}.weight")))
             return out
 
-        self.w_gate = slab("gate_proj", self.inter, self.hidden)
-        self.w_up = slab("up_proj", self.inter, self.hidden)
-        self.w_down = slab("down_proj", self.hidden, self.inter)
+        self.w_gate = slab("gate_proj", I, self.hidden)
+        self.w_up = slab("up_proj", I, self.hidden)
+        self.w_down = slab("down_proj", self.hidden, I)
         if self.shared_inter > 0:
-            self.ws_gate = self.fetch(source, self.name("shared_expert.gate_proj.weight"))
-            self.ws_up = self.fetch(source, self.name("shared_expert.up_proj.weight"))
-            self.ws_down = self.fetch(source, self.name("shared_expert.down_proj.weight"))
+            ws_gate = self.fetch(source, self.name("shared_expert.gate_proj.weight"))
+            ws_up = self.fetch(source, self.name("shared_expert.up_proj.weight"))
+            ws_down = self.fetch(source, self.name("shared_expert.down_proj.weight"))
+            if C > 0:
+                # chunk c of the shared expert: rows [c I, (c + 1) I) of gate and up, columns of down
+                self.w_gate[E:].copy_(ws_gate.view(C, I, self.hidden))
+                self.w_up[E:].copy_(ws_up.view(C, I, self.hidden))
+                self.w_down[E:].copy_(ws_down.view(self.hidden, C, I).permute(1, 0, 2))
+            else:
+                self.ws_gate, self.ws_up, self.ws_down = ws_gate, ws_up, ws_down
             if self.shared_gate:
                 self.shared_gate_w = self.fetch(source, self.name("shared_expert_gate.weight")).reshape(-1).contiguous()
 
@@ -129,19 +146,23 @@ class SparseMoE(Part):
         shared_scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.shared_gate else None
         K.router_topk(x_f32, self.router, self.shared_gate_w, k, self.norm_topk, sel, wts, shared_scale)
 
-        offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
-        slot_token = torch.empty((T * k,), dtype=torch.int32, device=dev)
+        C = self.shared_chunks
+        n_slots = T * k + C * T
+        offsets = torch.empty((E + C + 1,), dtype=torch.int32, device=dev)
+        slot_token = torch.empty((n_slots,), dtype=torch.int32, device=dev)
         slot_of_pick = torch.empty((T * k,), dtype=torch.int32, device=dev)
-        K.moe_group(sel, k, E, offsets, slot_token, slot_of_pick)
+        K.moe_group(sel, k, E, offsets, slot_token, slot_of_pick, extra_groups=C)
         self.last_offsets = offsets          # kept for measurement: which experts the last step touched
 
-        act = torch.empty((T * k, self.inter), dtype=rt.act_dtype, device=dev)
+        act = torch.empty((n_slots, self.inter), dtype=rt.act_dtype, device=dev)
         project(rt, x, self.w_gate, act, w_up=self.w_up, group_offsets=offsets, a_row_index=slot_token, max_group_rows=T)
-        y = torch.empty((T * k, self.hidden), dtype=torch.float32, device=dev)
+        y = torch.empty((n_slots, self.hidden), dtype=torch.float32, device=dev)
         project(rt, act, self.w_down, y, group_offsets=offsets, max_group_rows=T)
 
         shared = None
-        if self.shared_inter > 0:
+        if C > 0:
+            shared = y[T * k:].view(C, T, self.hidden)
+        elif self.shared_inter > 0:
             sact = torch.empty((T, self.shared_inter), dtype=rt.act_dtype, device=dev)
             project(rt, x, self.ws_gate, sact, w_up=self.ws_up)
             shared = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)

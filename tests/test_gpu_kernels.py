@@ -144,6 +144,18 @@ def test_gemm_swiglu_and_grouped(K, dtype):
         want[t] += acc
     K.moe_combine(hs, y, slot_of_pick, w, k, shared, gate)
     assert torch.allclose(hs.double(), want, atol=1e-5, rtol=1e-5)
+    # groups that hold every token follow the routed ones; the shared rows come in chunks
+    C = 3
+    offsets2 = torch.empty(E + C + 1, dtype=torch.int32, device=DEV)
+    slot_token2 = torch.empty(T * k + C * T, dtype=torch.int32, device=DEV)
+    K.moe_group(sel, k, E, offsets2, slot_token2, slot_of_pick, extra_groups=C)
+    assert offsets2.cpu().tolist() == off + [T * k + (c + 1) * T for c in range(C)]
+    assert slot_token2[:T * k].cpu().tolist() == st and slot_token2[T * k:].cpu().tolist() == list(range(T)) * C
+    chunks = rnd(C, T, H, seed=19)
+    hs2 = rnd(T, H, seed=18)
+    K.moe_combine(hs2, y, slot_of_pick, w, k, chunks, gate)
+    want2 = want - gate.double()[:, None] * shared.double() + gate.double()[:, None] * chunks.double().sum(0)
+    assert torch.allclose(hs2.double(), want2, atol=1e-5, rtol=1e-5)
 
 
 def test_router_kernel_meets_the_reference_constants(K):

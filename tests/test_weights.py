@@ -106,7 +106,16 @@ def test_dtypes_the_engine_holds(model_dirs):
         att = m.blocks[0].mixer
         moe = m.blocks[0].feed_forward
         assert m.embedding.dtype == want and att.w_qkv.dtype == want and moe.w_gate.dtype == want
-        assert att.w_qkv.shape == (64 + 2 * 32, 64) and moe.w_gate.shape == (4, 32, 64) and moe.w_down.shape == (4, 64, 32)
+        # 4 experts of width 32, then the shared expert (width 64) as 2 chunks of that width
+        assert att.w_qkv.shape == (64 + 2 * 32, 64) and moe.w_gate.shape == (6, 32, 64) and moe.w_down.shape == (6, 64, 32)
+        ck = Checkpoint(model_dirs["A"])
+        sg = ck.load("model.layers.0.mlp.shared_expert.gate_proj.weight").to(want)
+        sd = ck.load("model.layers.0.mlp.shared_expert.down_proj.weight").to(want)
+        e3 = ck.load("model.layers.0.mlp.experts.3.up_proj.weight").to(want)
+        ck.close()
+        assert torch.equal(moe.w_gate[4], sg[:32]) and torch.equal(moe.w_gate[5], sg[32:])
+        assert torch.equal(moe.w_down[4], sd[:, :32]) and torch.equal(moe.w_down[5], sd[:, 32:])
+        assert torch.equal(moe.w_up[3], e3)
         # small tensors used in 32-bit arithmetic are held in float32 (exact for a bfloat16 file)
         assert att.b_qkv.dtype == torch.float32 and moe.router.dtype == torch.float32
         assert m.final_norm.weight.dtype == torch.float32
