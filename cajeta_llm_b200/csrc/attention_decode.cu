@@ -24,13 +24,14 @@ __global__ void __launch_bounds__(CHUNK) decode_attention_kernel(
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ positions, const int* __restrict__ row_req,
     const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int window, float scale,
     float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters, int max_splits) {
-    constexpr int PAIRS = HD / 2;                 // threads that cover the head's dims two at a time
-    constexpr int KPAR = CHUNK / PAIRS;           // key phases working side by side in the value sum
+    constexpr int VEC = 8;                        // dims one thread owns in the value sum (one 16-byte load)
+    constexpr int COLS = HD / VEC;                // threads that cover a value row
+    constexpr int KPAR = CHUNK / COLS;            // key phases working side by side in the value sum
     __shared__ __align__(16) float qs[HD];
     __shared__ float es[CHUNK];
     __shared__ long long bases[CHUNK];
     __shared__ float red[CHUNK / 32];
-    __shared__ float2 vsum[KPAR][PAIRS];
+    __shared__ float vsum[KPAR][HD + 4];
     __shared__ int is_last;
 
     const int t = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -88,24 +89,32 @@ __global__ void __launch_bounds__(CHUNK) decode_attention_kernel(
         __syncthreads();
         l = (red[0] + red[1]) + (red[2] + red[3]);
 
-        // values: thread = (dim pair, key phase); keys of its phase in order
-        const int pair = tid % PAIRS, phase = tid / PAIRS;
-        float2 acc = make_float2(0.0f, 0.0f);
+        // values: thread = (8 dims, key phase); the keys of its phase in order, 16 bytes a load
+        const int col = tid % COLS, phase = tid / COLS;
+        float acc[VEC];
+#pragma unroll
+        for (int d = 0; d < VEC; ++d) acc[d] = 0.0f;
+#pragma unroll 4
         for (int j = phase; j < count; j += KPAR) {
             float ej = es[j];
-            __nv_bfloat162 v2 = *(const __nv_bfloat162*)(vplane + bases[j] + 2 * pair);
-            float2 f = __bfloat1622float2(v2);
-            acc.x = fmaf(ej, f.x, acc.x);
-            acc.y = fmaf(ej, f.y, acc.y);
-        }
-        vsum[phase][pair] = acc;
-        __syncthreads();
-        if (tid < PAIRS) {
-            float2 a = vsum[0][tid];
+            uint4 u = *(const uint4*)(vplane + bases[j] + VEC * col);
+            const __nv_bfloat162* b2 = (const __nv_bfloat162*)&u;
 #pragma unroll
-            for (int ph = 1; ph < KPAR; ++ph) {
-                a.x += vsum[ph][tid].x;
-                a.y += vsum[ph][tid].y;
+            for (int d = 0; d < VEC / 2; ++d) {
+                float2 f = __bfloat1622float2(b2[d]);
+                acc[2 * d] = fmaf(ej, f.x, acc[2 * d]);
+                acc[2 * d + 1] = fmaf(ej, f.y, acc[2 * d + 1]);
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < VEC; ++d) vsum[phase][VEC * col + d] = acc[d];
+        __syncthreads();
+        if (tid < HD / 2) {
+            float2 a = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int ph = 0; ph < KPAR; ++ph) {
+                a.x += vsum[ph][2 * tid];
+                a.y += vsum[ph][2 * tid + 1];
             }
             if (n_splits == 1) {
                 float inv = 1.0f / l;
@@ -137,7 +146,7 @@ __global__ void __launch_bounds__(CHUNK) decode_attention_kernel(
         for (int sidx = 0; sidx < n_splits; ++sidx) M = fmaxf(M, part_ml[(slot0 + sidx) * 2]);
         float L = 0.0f;
         for (int sidx = 0; sidx < n_splits; ++sidx) L += part_ml[(slot0 + sidx) * 2 + 1] * expf(part_ml[(slot0 + sidx) * 2] - M);
-        if (tid < PAIRS) {
+        if (tid < HD / 2) {
             float2 a = make_float2(0.0f, 0.0f);
             for (int sidx = 0; sidx < n_splits; ++sidx) {
                 float f = expf(part_ml[(slot0 + sidx) * 2] - M);

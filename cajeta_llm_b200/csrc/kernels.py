@@ -94,9 +94,11 @@ def embed_gather(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> N
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-            out_f32: Optional[torch.Tensor] = None, row_index: Optional[torch.Tensor] = None) -> None:
+            out_f32: Optional[torch.Tensor] = None, row_index: Optional[torch.Tensor] = None,
+            partials: Optional[torch.Tensor] = None) -> None:
     """out[r] = rmsnorm(x[row_index[r] or r]) * weight; x, weight float32; out float32 or
-    bfloat16; out_f32 an optional float32 copy of the result."""
+    bfloat16; out_f32 an optional float32 copy of the result.  ``partials`` ([S, rows, H]
+    float32): x[r] += sum_s partials[s, r] first, and x keeps the sum."""
     _need(x, "x", torch.float32), _need(weight, "weight", torch.float32), _need(out, "out")
     rows, H = out.shape
     if x.shape[-1] != H or weight.numel() != H:
@@ -105,8 +107,14 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
         _need(out_f32, "out_f32", torch.float32)
     if row_index is not None:
         _need(row_index, "row_index", torch.int32)
+    n_part, part_stride = 0, 0
+    if partials is not None:
+        _need(partials, "partials", torch.float32)
+        if partials.dim() != 3 or partials.shape[1] != rows or partials.shape[2] != H or row_index is not None:
+            raise KernelError(f"rmsnorm: partials {tuple(partials.shape)} do not fit {rows} rows of {H}")
+        n_part, part_stride = partials.shape[0], partials.stride(0)
     st = library("rowwise").cj_rmsnorm(_ptr(x), _ptr(weight), _f(eps), _i(rows), _i(H), _ptr(out), _i(_code(out)),
-                                       _ptr(out_f32), _ptr(row_index), _stream())
+                                       _ptr(out_f32), _ptr(row_index), _ptr(partials), _i(n_part), _ll(part_stride), _stream())
     _check(st, "rmsnorm")
 
 

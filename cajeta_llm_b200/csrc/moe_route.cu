@@ -73,6 +73,55 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_logits_kernel(
     }
 }
 
+// The same logits for a handful of rows (decode): one warp per expert reads its weight row
+// and the rows of x straight from global memory (they sit in L2), with the same lane-strided
+// sum as above, so both kernels give the same bits for a row.
+constexpr int SMALL_WARPS = 4;
+__global__ void __launch_bounds__(SMALL_WARPS * 32) router_logits_small_kernel(
+    const float* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ shared_gate, int T, int H,
+    int E, float* __restrict__ logits) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_cols = E + (shared_gate ? 1 : 0);
+    const int e = blockIdx.x * SMALL_WARPS + warp;
+    if (e >= n_cols) return;
+    const float* wr = e < E ? Wr + (size_t)e * H : shared_gate;
+    const bool vec = (H % 4) == 0;
+    for (int t0 = 0; t0 < T; t0 += 8) {
+        const int n_tok = min(8, T - t0);
+        float acc[8];
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) acc[tt] = 0.0f;
+        if (vec) {
+#pragma unroll 2
+            for (int j = lane * 4; j < H; j += 128) {
+                float4 w4 = *(const float4*)(wr + j);
+#pragma unroll
+                for (int tt = 0; tt < 8; ++tt) {
+                    if (tt < n_tok) {
+                        float4 x4 = *(const float4*)(x + (size_t)(t0 + tt) * H + j);
+                        acc[tt] = fmaf(w4.x, x4.x, acc[tt]);
+                        acc[tt] = fmaf(w4.y, x4.y, acc[tt]);
+                        acc[tt] = fmaf(w4.z, x4.z, acc[tt]);
+                        acc[tt] = fmaf(w4.w, x4.w, acc[tt]);
+                    }
+                }
+            }
+        } else {
+            for (int j = lane; j < H; j += 32) {
+                float wv = wr[j];
+#pragma unroll
+                for (int tt = 0; tt < 8; ++tt)
+                    if (tt < n_tok) acc[tt] = fmaf(wv, x[(size_t)(t0 + tt) * H + j], acc[tt]);
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) {
+            float v = warp_sum(acc[tt]);
+            if (lane == 0 && tt < n_tok) logits[(size_t)(t0 + tt) * n_cols + e] = v;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(32) router_select_kernel(
     const float* __restrict__ logits, int E, int n_cols, int k, int norm_topk, int* __restrict__ sel,
     float* __restrict__ w, float* __restrict__ shared_scale) {
@@ -177,6 +226,14 @@ CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* share
     if (shared_gate && !shared_scale) return CJ_ERR_ARG;
     if (E < 1 || E > MAX_EXPERTS || k < 1 || k > E) return CJ_ERR_SIZE;
     const int n_cols = E + (shared_gate ? 1 : 0);
+    if (T <= 32) {
+        router_logits_small_kernel<<<(n_cols + SMALL_WARPS - 1) / SMALL_WARPS, SMALL_WARPS * 32, 0, stream>>>(
+            x, Wr, shared_gate, T, H, E, logits);
+        int st0 = launch_status();
+        if (st0) return st0;
+        router_select_kernel<<<T, 32, 0, stream>>>(logits, E, n_cols, k, norm_topk, sel, w, shared_gate ? shared_scale : nullptr);
+        return launch_status();
+    }
     // rows of x staged per block: as many as fit 200 KB of shared memory, at most 8
     int tokb = 8;
     while (tokb > 1 && (size_t)tokb * H * sizeof(float) > 200 * 1024) tokb >>= 1;

@@ -41,16 +41,22 @@ CJ_EXPORT int cj_embed_gather(float* out, const void* table, int table_dtype, co
 // in the activation dtype and, when asked, a float32 copy (the router's input).
 // ---------------------------------------------------------------------------------
 template <typename TO>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int H,
+__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ w, float eps, int H,
                                TO* __restrict__ out, float* __restrict__ out_f32,
-                               const int* __restrict__ row_index) {
+                               const int* __restrict__ row_index, const float* __restrict__ partials, int n_partials,
+                               long long partial_stride) {
     __shared__ float partial[32];
     __shared__ float scale_s;
     int r = blockIdx.x;
-    const float* src = x + (size_t)(row_index ? row_index[r] : r) * H;
+    float* src = x + (size_t)(row_index ? row_index[r] : r) * H;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = src[i];
+        if (partials) {
+            // the split sums of the product before this norm: added in split order, stored back
+            for (int s = 0; s < n_partials; ++s) v += partials[s * partial_stride + (size_t)r * H + i];
+            src[i] = v;
+        }
         ss = fmaf(v, v, ss);
     }
     ss = warp_sum(ss);
@@ -71,15 +77,20 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     }
 }
 
-CJ_EXPORT int cj_rmsnorm(const float* x, const float* w, float eps, int rows, int H, void* out, int out_dtype,
-                         float* out_f32, const int* row_index, cudaStream_t stream) {
+// partials (optional): [n_partials][rows][H] float32 with partial_stride elements between
+// them; x[r] += sum of its partials first (the residual add of a product that was split
+// along K), and x keeps the sum.  Not combined with row_index.
+CJ_EXPORT int cj_rmsnorm(float* x, const float* w, float eps, int rows, int H, void* out, int out_dtype,
+                         float* out_f32, const int* row_index, const float* partials, int n_partials,
+                         long long partial_stride, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (!x || !w || !out || H <= 0) return CJ_ERR_ARG;
+    if (partials && (row_index || n_partials < 1)) return CJ_ERR_ARG;
     int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (out_dtype == CJ_F32)
-        rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(x, w, eps, H, (float*)out, out_f32, row_index);
+        rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(x, w, eps, H, (float*)out, out_f32, row_index, partials, n_partials, partial_stride);
     else if (out_dtype == CJ_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(x, w, eps, H, (__nv_bfloat16*)out, out_f32, row_index);
+        rmsnorm_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(x, w, eps, H, (__nv_bfloat16*)out, out_f32, row_index, partials, n_partials, partial_stride);
     else
         return CJ_ERR_DTYPE;
     return launch_status();

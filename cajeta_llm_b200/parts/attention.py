@@ -25,7 +25,7 @@ import torch
 
 from ..csrc import kernels as K
 from .base import KvNeed, Part, make_part, register_part
-from .linear import project
+from .linear import project, project_split
 from .plan import ParamSpec
 
 
@@ -87,7 +87,7 @@ class PagedAttention(Part):
             self.b_o = self.fetch(source, self.name("o_proj.bias"))
 
     # -- one step --------------------------------------------------------------------
-    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, entry) -> None:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, entry) -> Optional[torch.Tensor]:
         rt = self.runtime
         T = x.shape[0]
         pos = self.position
@@ -112,4 +112,8 @@ class PagedAttention(Part):
         else:
             K.paged_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
                               entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale)
+        parts = project_split(rt, out.view(T, self.q_dim), self.w_o, bias=self.b_o)
+        if parts is not None:
+            return parts                     # owed to the residual stream; the next norm adds them
         project(rt, out.view(T, self.q_dim), self.w_o, residual, bias=self.b_o, accumulate=True)
+        return None

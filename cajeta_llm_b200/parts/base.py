@@ -8,14 +8,15 @@ its spec or in the step's context.
 
 Categories and what each must offer
 -----------------------------------
-``norm``          ``forward(x_f32, want_f32=False, row_index=None) -> (y, y_f32 | None)``
+``norm``          ``forward(x_f32, want_f32=False, row_index=None, pending=None) -> (y, y_f32 | None)``
 ``position``      ``rotary_dim`` and ``inv_freq`` (float32 device tensor, rotary_dim / 2)
-``mixer``         ``cache_need()``, ``state_need()``, ``forward(x, residual, ctx, entry)``
+``mixer``         ``cache_need()``, ``state_need()``, ``forward(x, residual, ctx, entry) -> None | pending``
 ``feed_forward``  ``needs_f32_input``, ``forward(x, x_f32, residual, ctx)``
 ``block``         ``forward(hs, ctx, entry)`` over its mixer, feed-forward and norms
 
 ``x`` is the normed input in the activation dtype, ``residual`` the float32 residual
-stream the part adds its result into (the residual sum is always 32-bit), ``ctx`` the
+stream the part adds its result into (the residual sum is always 32-bit; a mixer may
+instead return ``pending``, float32 partial sums [S, rows, H] that the next norm adds), ``ctx`` the
 :class:`cajeta_llm_b200.engine.step.StepContext` of the step and ``entry`` the
 :class:`cajeta_llm_b200.engine.step.EntryContext` of the schedule entry being run
 (its cache plane, block table and state slots).

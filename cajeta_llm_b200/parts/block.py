@@ -40,6 +40,9 @@ class PreNormBlock(Part):
 
     def forward(self, hs: torch.Tensor, ctx, entry) -> None:
         x, _ = self.mixer_norm.forward(hs)
-        self.mixer.forward(x, hs, ctx, entry)
-        x, x_f32 = self.feed_forward_norm.forward(hs, want_f32=getattr(self.feed_forward, "needs_f32_input", False))
+        # a mixer may return partial sums it still owes the residual stream ([S, rows, H]
+        # float32, from a product split along K); the next norm adds them as it reads hs
+        pending = self.mixer.forward(x, hs, ctx, entry)
+        x, x_f32 = self.feed_forward_norm.forward(hs, want_f32=getattr(self.feed_forward, "needs_f32_input", False),
+                                                  pending=pending)
         self.feed_forward.forward(x, x_f32, hs, ctx)

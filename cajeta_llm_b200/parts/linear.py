@@ -66,3 +66,25 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
     else:
         n_mma = 256 if (w_up is None and w.shape[-2] >= 512) else 128
         K.gemm_tc(x, w, out, epi, False, n_mma, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows)
+
+
+def project_split(runtime, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """For a few rows and a weight with few output features: the product cut along K into
+    enough pieces to occupy the machine.  Returns the partial sums [S, tokens, features]
+    (float32; the bias is in the first), to be added by the consumer in order - or None
+    when the shapes do not call for it (the caller then uses :func:`project`)."""
+    if not _tc_ok(runtime, x, w):
+        return None
+    rows = x.shape[0]
+    tile = _token_tile(rows)
+    if not tile:
+        return None
+    features, Kd = w.shape[-2], w.shape[-1]
+    feature_tiles = -(-features // 128) * -(-rows // tile)
+    k_blocks = -(-Kd // 64)
+    splits = min(8, max(1, 128 // feature_tiles), max(1, k_blocks // 4))
+    if splits < 2:
+        return None
+    parts = torch.empty((splits, rows, features), dtype=torch.float32, device=x.device)
+    K.gemm_tc(x, w, parts, K.EPI_STORE_F32, True, tile, bias=bias, k_splits=splits)
+    return parts

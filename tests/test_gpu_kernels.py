@@ -57,6 +57,19 @@ def test_rmsnorm(K, H):
     assert torch.equal(out_b, out_f.to(torch.bfloat16))            # one rounding, from the float32 value
 
 
+def test_rmsnorm_adds_pending_partial_sums_first(K):
+    H = 200
+    x = rnd(5, H, seed=2, scale=2.0)
+    parts = rnd(3, 5, H, seed=8)
+    w = rnd(H, seed=3)
+    total = x.double() + parts.double().sum(0)
+    out = torch.empty(5, H, device=DEV, dtype=torch.bfloat16)
+    out32 = torch.empty(5, H, device=DEV)
+    K.rmsnorm(x, w, 1e-6, out, out32, None, parts)
+    assert torch.allclose(x.double(), total, atol=1e-6)                      # the residual stream keeps the sum
+    assert torch.allclose(out32.double().cpu(), P.rmsnorm(total.cpu(), w.double().cpu(), 1e-6), atol=1e-5, rtol=1e-5)
+
+
 @pytest.mark.parametrize("M,N,K_", [(1, 5, 7), (3, 70, 100), (65, 129, 33), (130, 64, 257)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gemm_plain_bias_accumulate(K, M, N, K_, dtype):
