@@ -92,17 +92,28 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32) router_logits_small_kernel(
 #pragma unroll
         for (int tt = 0; tt < 8; ++tt) acc[tt] = 0.0f;
         if (vec) {
-#pragma unroll 2
-            for (int j = lane * 4; j < H; j += 128) {
-                float4 w4 = *(const float4*)(wr + j);
+            // the weight row is cold (the experts' weights have flushed L2 since the last
+            // layer): eight loads are put in flight before the first is used
+            for (int j0 = lane * 4; j0 < H; j0 += 128 * 8) {
+                float4 wv[8];
 #pragma unroll
-                for (int tt = 0; tt < 8; ++tt) {
-                    if (tt < n_tok) {
-                        float4 x4 = *(const float4*)(x + (size_t)(t0 + tt) * H + j);
-                        acc[tt] = fmaf(w4.x, x4.x, acc[tt]);
-                        acc[tt] = fmaf(w4.y, x4.y, acc[tt]);
-                        acc[tt] = fmaf(w4.z, x4.z, acc[tt]);
-                        acc[tt] = fmaf(w4.w, x4.w, acc[tt]);
+                for (int u = 0; u < 8; ++u) {
+                    int j = j0 + 128 * u;
+                    wv[u] = j < H ? __ldg((const float4*)(wr + j)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    int j = j0 + 128 * u;
+                    if (j >= H) break;
+#pragma unroll
+                    for (int tt = 0; tt < 8; ++tt) {
+                        if (tt < n_tok) {
+                            float4 x4 = *(const float4*)(x + (size_t)(t0 + tt) * H + j);
+                            acc[tt] = fmaf(wv[u].x, x4.x, acc[tt]);
+                            acc[tt] = fmaf(wv[u].y, x4.y, acc[tt]);
+                            acc[tt] = fmaf(wv[u].z, x4.z, acc[tt]);
+                            acc[tt] = fmaf(wv[u].w, x4.w, acc[tt]);
+                        }
                     }
                 }
             }
