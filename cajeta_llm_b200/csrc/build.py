@@ -39,7 +39,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_decode": "attention_decode.cu",
     "attention_prefill": "attention_prefill.cu",
 }
-HEADERS = ["common.cuh", "tc_common.cuh"]
+HEADERS = ["common.cuh", "tc_common.cuh", "sampling_static.h"]
 
 
 class BuildError(RuntimeError):

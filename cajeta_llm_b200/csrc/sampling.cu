@@ -17,6 +17,7 @@
 // (normalising them gives the post-filter distribution the reference's `prepare`
 // exposes to tests).
 #include "common.cuh"
+#include "sampling_static.h"
 
 using namespace cj;
 
@@ -304,5 +305,46 @@ CJ_EXPORT int cj_sample(const float* logits, int rows, int V, const float* tempe
     if (history && !history_offsets) return CJ_ERR_ARG;
     sample_kernel<<<rows, ST, 0, stream>>>(logits, V, temperature, top_k, top_p, repeat_penalty, uniform, history,
                                            history_offsets, scratch, out);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+// The same sampler for callers that cannot allocate (see sampling_static.h): the scratch
+// is a fixed array in the library image instead of a buffer from the caller.
+//
+// In host code the name of a __device__ array is only a stand-in of the host side; it is
+// not an address a kernel may use.  The device address is asked for once per device, with
+// that device current, and kept.
+// ---------------------------------------------------------------------------------
+static __device__ __align__(256) float g_sample_static_scratch[CJ_SAMPLE_STATIC_MAX_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_ptr[MAX_DEVICES] = {nullptr};
+}  // namespace
+
+CJ_EXPORT long long cj_sample_static_capacity(void) { return (long long)CJ_SAMPLE_STATIC_MAX_FLOATS; }
+
+CJ_EXPORT int cj_sample_static(const float* logits, int rows, int V, const float* temperature, const int* top_k,
+                               const float* top_p, const float* repeat_penalty, const float* uniform,
+                               const int* history, const int* history_offsets, int* out, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (!logits || !temperature || !uniform || !out || V <= 0) return CJ_ERR_ARG;
+    if (history && !history_offsets) return CJ_ERR_ARG;
+    if ((long long)rows * (long long)V > (long long)CJ_SAMPLE_STATIC_MAX_FLOATS) return CJ_SAMPLE_STATIC_TOO_LARGE;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= MAX_DEVICES) return CJ_ERR_ARG;
+    if (!g_static_scratch_ptr[dev]) {
+        // set-up, first call on this device: the device address of the array
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_sample_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!ptr) return CJ_ERR_ARG;
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    sample_kernel<<<rows, ST, 0, stream>>>(logits, V, temperature, top_k, top_p, repeat_penalty, uniform, history,
+                                           history_offsets, g_static_scratch_ptr[dev], out);
     return launch_status();
 }
