@@ -129,6 +129,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
     ap.add_argument("--quick", action="store_true", help="skip the batch-1/64 points and the end-to-end arm")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profilers)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -163,7 +164,8 @@ def main() -> int:
     # pool: 64 requests of 512 + generated tokens, or 8 at the full context, whichever is larger
     tokens_needed = max(max_b * (PROMPT + 2 * (warmup + steps) + 64), BATCH * (PROMPT + 256), PREFILL_TOKENS + 64)
     opts = EngineOptions(config=cfg, random_weights=True, seed=1234, dtype="bfloat16", ctx=CTX, max_seqs=max_b,
-                         block_tokens=PAGE, num_blocks=-(-tokens_needed // PAGE) + max_b, max_batch_tokens=4096)
+                         block_tokens=PAGE, num_blocks=-(-tokens_needed // PAGE) + max_b, max_batch_tokens=4096,
+                         cuda_graphs=not args.no_graphs)
     t0 = time.time()
     engine = LlmEngine.load(opts)
     torch.cuda.synchronize()

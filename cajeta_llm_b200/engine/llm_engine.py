@@ -35,7 +35,8 @@ class LlmEngine:
         self._eog = tuple(sorted(set(eog)))
         self.runner = ModelRunner(model, page_tokens=options.block_tokens, max_seqs=options.max_seqs,
                                   max_tokens_per_seq=options.ctx,
-                                  num_pages=options.num_blocks if options.num_blocks > 0 else None)
+                                  num_pages=options.num_blocks if options.num_blocks > 0 else None,
+                                  cuda_graphs=options.cuda_graphs)
         self.sampler = BatchSampler(model.runtime.device, model.vocab)
         self._scheduler = Scheduler(self.runner, self.sampler, max_batch_tokens=options.max_batch_tokens,
                                     chunk=options.chunk, eog_token_ids=self._eog)

@@ -30,6 +30,7 @@ class EngineOptions:
     seed: int = 0
     config: Optional[object] = None    # a ModelConfig (or config.json dict) for random weights without a folder
     verbose: bool = False
+    cuda_graphs: bool = True           # replay pure decode steps of the bfloat16 path from CUDA graphs
 
     def validate(self) -> None:
         if self.ctx < 1:
