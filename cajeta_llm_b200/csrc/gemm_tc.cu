@@ -79,25 +79,35 @@ struct TileCoord {
 template <int TOK_TILE, int FEAT_TILE>
 __device__ __forceinline__ TileCoord decode_tile(const Args& p, int tile, int feat_tiles, int tok_tiles, const int* tiles_before) {
     TileCoord c;
-    int f = tile % feat_tiles;
-    int rest = tile / feat_tiles;
-    int tt = rest % tok_tiles;
-    c.split = rest / tok_tiles;
     c.valid = true;
-    int group = 0;
+    int group = 0, f, tt;
     if (p.group_offsets) {
-        // tiles_before[g] = token tiles of the groups before g; find the group that holds tile tt
-        int lo = 0, hi = p.groups;                 // invariant: tiles_before[lo] <= tt, answer in [lo, hi)
-        if (tt >= tiles_before[p.groups]) { c.valid = false; return c; }
+        // grouped: tiles are ordered (split, group, feature tile, token tile), the token tile
+        // running fastest, so that the blocks working side by side share a weight tile and
+        // a slab is streamed from memory once.  tiles_before[g] = token tiles of the groups
+        // before g.
+        int per_split = tiles_before[p.groups] * feat_tiles;
+        c.split = tile / per_split;
+        int local = tile - c.split * per_split;
+        int lo = 0, hi = p.groups;                 // invariant: tiles_before[lo] * feat_tiles <= local
         while (hi - lo > 1) {
             int mid = (lo + hi) >> 1;
-            if (tiles_before[mid] <= tt) lo = mid; else hi = mid;
+            if (tiles_before[mid] * feat_tiles <= local) lo = mid; else hi = mid;
         }
         group = lo;
+        int n_tt = tiles_before[group + 1] - tiles_before[group];
+        local -= tiles_before[group] * feat_tiles;
+        f = local / n_tt;
+        tt = local - f * n_tt;
         int g_lo = p.group_offsets[group], g_hi = p.group_offsets[group + 1];
-        c.tok0 = g_lo + (tt - tiles_before[group]) * TOK_TILE;
+        c.tok0 = g_lo + tt * TOK_TILE;
         c.tok_end = min(g_hi, c.tok0 + TOK_TILE);
     } else {
+        // dense: the feature tile runs fastest, so that neighbouring blocks stream different weights
+        f = tile % feat_tiles;
+        int rest = tile / feat_tiles;
+        tt = rest % tok_tiles;
+        c.split = rest / tok_tiles;
         c.tok0 = tt * TOK_TILE;
         c.tok_end = min(p.tokens, c.tok0 + TOK_TILE);
     }
@@ -168,6 +178,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // a grouped launch knows its number of tiles only now (it depends on the routing)
+    if (p.group_offsets) total_tiles = tiles_before[p.groups] * feat_tiles * p.k_splits;
 
     if (warp == 0) {
         // ---- TMA producer: streams stage after stage, straight across tile boundaries ----------
@@ -196,7 +208,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     } else if (warp == 1) {
         // ---- product issue -----------------------------------------------------------------
         if (elect_one()) {
-            constexpr uint32_t idesc = umma_idesc_bf16(128, N_MMA);
             uint32_t it = 0, acc_it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -207,6 +218,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t acc_addr = tmem_base + as * STAGE_COLS;
+                // weights on the rows: the product is only as wide as the tile has tokens (in 16s)
+                const int n_mma = SWAP ? min(N_MMA, ((c.tok_end - c.tok0 + 15) >> 4) << 4) : N_MMA;
+                const uint32_t idesc = umma_idesc_bf16(128, n_mma);
                 for (int i = 0; i < c.n_kb; ++i, ++it) {
                     int s = it % STAGES;
                     ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, 2);

@@ -39,36 +39,58 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_logits_kernel(
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int NW = ROUTER_THREADS / 32;
+    constexpr int EB = 8;                     // experts a warp keeps accumulators for at a time
     const bool vec = (H % 4) == 0;
-    for (int e = e_begin + warp; e < e_end; e += NW) {
-        const float* wr = e < E ? Wr + (size_t)e * H : shared_gate;
-        float acc[TOKB];
+    // a warp takes experts e_begin + warp + NW * i; EB of them at a time, so that a chunk of x
+    // read from shared memory is used EB times (the loop over j is the outer one)
+    for (int eb = e_begin + warp; eb < e_end; eb += NW * EB) {
+        float acc[EB][TOKB];
 #pragma unroll
-        for (int tt = 0; tt < TOKB; ++tt) acc[tt] = 0.0f;
+        for (int q = 0; q < EB; ++q)
+#pragma unroll
+            for (int tt = 0; tt < TOKB; ++tt) acc[q][tt] = 0.0f;
         if (vec) {
-#pragma unroll 4
             for (int j = lane * 4; j < H; j += 128) {
-                float4 w4 = *(const float4*)(wr + j);
+                float4 x4[TOKB];
 #pragma unroll
-                for (int tt = 0; tt < TOKB; ++tt) {
-                    float4 x4 = *(const float4*)(xs + tt * H + j);
-                    acc[tt] = fmaf(w4.x, x4.x, acc[tt]);
-                    acc[tt] = fmaf(w4.y, x4.y, acc[tt]);
-                    acc[tt] = fmaf(w4.z, x4.z, acc[tt]);
-                    acc[tt] = fmaf(w4.w, x4.w, acc[tt]);
+                for (int tt = 0; tt < TOKB; ++tt) x4[tt] = *(const float4*)(xs + tt * H + j);
+#pragma unroll
+                for (int q = 0; q < EB; ++q) {
+                    int e = eb + q * NW;
+                    if (e < e_end) {
+                        const float* wr = e < E ? Wr + (size_t)e * H : shared_gate;
+                        float4 w4 = __ldg((const float4*)(wr + j));
+#pragma unroll
+                        for (int tt = 0; tt < TOKB; ++tt) {
+                            acc[q][tt] = fmaf(w4.x, x4[tt].x, acc[q][tt]);
+                            acc[q][tt] = fmaf(w4.y, x4[tt].y, acc[q][tt]);
+                            acc[q][tt] = fmaf(w4.z, x4[tt].z, acc[q][tt]);
+                            acc[q][tt] = fmaf(w4.w, x4[tt].w, acc[q][tt]);
+                        }
+                    }
                 }
             }
         } else {
             for (int j = lane; j < H; j += 32) {
-                float wv = wr[j];
 #pragma unroll
-                for (int tt = 0; tt < TOKB; ++tt) acc[tt] = fmaf(wv, xs[tt * H + j], acc[tt]);
+                for (int q = 0; q < EB; ++q) {
+                    int e = eb + q * NW;
+                    if (e < e_end) {
+                        float wv = (e < E ? Wr + (size_t)e * H : shared_gate)[j];
+#pragma unroll
+                        for (int tt = 0; tt < TOKB; ++tt) acc[q][tt] = fmaf(wv, xs[tt * H + j], acc[q][tt]);
+                    }
+                }
             }
         }
 #pragma unroll
-        for (int tt = 0; tt < TOKB; ++tt) {
-            float v = warp_sum(acc[tt]);
-            if (lane == 0 && tt < n_tok) logits[(size_t)(t0 + tt) * n_cols + e] = v;
+        for (int q = 0; q < EB; ++q) {
+            int e = eb + q * NW;
+#pragma unroll
+            for (int tt = 0; tt < TOKB; ++tt) {
+                float v = warp_sum(acc[q][tt]);
+                if (lane == 0 && e < e_end && tt < n_tok) logits[(size_t)(t0 + tt) * n_cols + e] = v;
+            }
         }
     }
 }
@@ -182,36 +204,58 @@ __global__ void __launch_bounds__(32) router_select_kernel(
     }
 }
 
-// Counting sort of the picks (token t, choice j) by expert, stable.  One warp per
-// expert: it counts the picks of lower experts (its first slot) and then places its own
-// in pick order.  reference: model/MoeFfn.cajeta:2064-2099 (groupPicks), device
+// Counting sort of the picks (token t, choice j) by expert, stable.  One block per
+// expert: its warps each take a contiguous stretch of the picks, count the picks of lower
+// experts (the expert's first slot) and their own, and then place their own in pick order.  reference: model/MoeFfn.cajeta:2064-2099 (groupPicks), device
 // io/QuantKernel.cajeta:41069.
 //
 // After the E routed groups come `extra` groups that every token belongs to (the chunks
 // of a shared expert run through the same grouped products): group E + c owns slots
 // [n + c * T, n + (c + 1) * T) and slot n + c * T + t reads token t.
-__global__ void moe_group_kernel(const int* __restrict__ sel, int n, int k, int E, int extra, int* __restrict__ offsets,
-                                 int* __restrict__ slot_token, int* __restrict__ slot_of_pick) {
-    int e = blockIdx.x;
-    int lane = threadIdx.x;
+constexpr int GROUP_WARPS = 8;
+__global__ void __launch_bounds__(GROUP_WARPS * 32) moe_group_kernel(
+    const int* __restrict__ sel, int n, int k, int E, int extra, int* __restrict__ offsets,
+    int* __restrict__ slot_token, int* __restrict__ slot_of_pick) {
+    __shared__ int lt_s[GROUP_WARPS], eq_s[GROUP_WARPS];
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int T = n / k;
     if (e >= E) {
         int c = e - E;
-        for (int t = lane; t < T; t += 32) slot_token[n + c * T + t] = t;
-        if (lane == 0) {
+        for (int t = threadIdx.x; t < T; t += blockDim.x) slot_token[n + c * T + t] = t;
+        if (threadIdx.x == 0) {
             offsets[E + c] = n + c * T;
             if (c == extra - 1) offsets[E + extra] = n + extra * T;
         }
         return;
     }
-    int below = 0;
-    for (int i = lane; i < n; i += 32) below += sel[i] < e ? 1 : 0;
+    // each warp owns a contiguous segment of the picks (a multiple of 32 long)
+    const int seg = (((n + GROUP_WARPS - 1) / GROUP_WARPS) + 31) & ~31;
+    const int lo = min(n, warp * seg), hi = min(n, lo + seg);
+    int lt = 0, eq = 0;
+    for (int i = lo + lane; i < hi; i += 32) {
+        int v = sel[i];
+        lt += v < e ? 1 : 0;
+        eq += v == e ? 1 : 0;
+    }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) below += __shfl_xor_sync(0xffffffffu, below, o);
-    int cursor = below;
-    for (int base = 0; base < n; base += 32) {
+    for (int o = 16; o > 0; o >>= 1) {
+        lt += __shfl_xor_sync(0xffffffffu, lt, o);
+        eq += __shfl_xor_sync(0xffffffffu, eq, o);
+    }
+    if (lane == 0) { lt_s[warp] = lt; eq_s[warp] = eq; }
+    __syncthreads();
+    int below = 0, cursor = 0;
+#pragma unroll
+    for (int w = 0; w < GROUP_WARPS; ++w) {
+        below += lt_s[w];
+        if (w < warp) cursor += eq_s[w];
+    }
+    cursor += below;
+    // placement in pick order: the segments are in order, and so is each warp's walk
+    for (int base = lo; base < hi; base += 32) {
         int i = base + lane;
-        bool mine = i < n && sel[i] == e;
+        bool mine = i < hi && sel[i] == e;
         unsigned ballot = __ballot_sync(0xffffffffu, mine);
         if (mine) {
             int pos = cursor + __popc(ballot & ((1u << lane) - 1u));
@@ -220,9 +264,13 @@ __global__ void moe_group_kernel(const int* __restrict__ sel, int n, int k, int 
         }
         cursor += __popc(ballot);
     }
-    if (lane == 0) {
+    if (threadIdx.x == 0) {
         offsets[e] = below;
-        if (e == E - 1 && extra == 0) offsets[E] = cursor;
+        if (e == E - 1 && extra == 0) {
+            int total = below;
+            for (int w = 0; w < GROUP_WARPS; ++w) total += eq_s[w];
+            offsets[E] = total;
+        }
     }
 }
 
@@ -278,6 +326,6 @@ CJ_EXPORT int cj_moe_group(const int* sel, int n_picks, int k, int E, int extra,
                            int* slot_of_pick, cudaStream_t stream) {
     if (E < 1 || k < 1 || n_picks < 0 || extra < 0) return CJ_ERR_SIZE;
     if (!sel || !offsets || !slot_token || !slot_of_pick) return CJ_ERR_ARG;
-    moe_group_kernel<<<E + extra, 32, 0, stream>>>(sel, n_picks, k, E, extra, offsets, slot_token, slot_of_pick);
+    moe_group_kernel<<<E + extra, GROUP_WARPS * 32, 0, stream>>>(sel, n_picks, k, E, extra, offsets, slot_token, slot_of_pick);
     return launch_status();
 }

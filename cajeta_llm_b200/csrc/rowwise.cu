@@ -108,6 +108,13 @@ CJ_EXPORT int cj_rmsnorm(float* x, const float* w, float eps, int rows, int H, v
 // cache plane is [pages, n_kv, page_tokens, hd]; position p of request r lies in page
 // table[r * table_stride + p / page_tokens] at slot p % page_tokens.
 // ---------------------------------------------------------------------------------
+template <typename T> struct Pair;
+template <> struct Pair<float> { using type = float2; static __device__ __forceinline__ float2 make(float a, float b) { return make_float2(a, b); } };
+template <> struct Pair<__nv_bfloat16> { using type = __nv_bfloat162; static __device__ __forceinline__ __nv_bfloat162 make(float a, float b) { return __floats2bfloat162_rn(a, b); } };
+
+// One block per row.  The row's angles are computed once (they are the same for every
+// head) and kept in shared memory; then each thread takes units of two adjacent dims:
+// for q and k a unit is dims (d, d+1) and their partners (d + half, d + half + 1).
 template <typename TQ, typename TC>
 __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, int v_off,
                                      TQ* __restrict__ q_out, TC* __restrict__ kplane, TC* __restrict__ vplane,
@@ -115,55 +122,89 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int 
                                      const int* __restrict__ table, int table_stride, int page_tokens,
                                      int n_heads, int n_kv, int hd, int rot, const float* __restrict__ inv_freq,
                                      int write_kv) {
-    int t = blockIdx.x;
-    int slot = blockIdx.y;                 // [0, n_heads): q head; then k heads; then v heads
-    int pos = positions[t];
+    extern __shared__ float cs[];                 // cos[half] then sin[half]
+    const int t = blockIdx.x;
+    const int pos = positions[t];
     const float* row = qkv + (size_t)t * ld;
-    int half = rot >> 1;
-    if (slot < n_heads) {
-        const float* src = row + q_off + slot * hd;
-        TQ* dst = q_out + ((size_t)t * n_heads + slot) * hd;
-        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-            float v;
-            if (d < rot) {
-                int dd = d < half ? d : d - half;
-                float ang = (float)pos * inv_freq[dd];
-                float c = cosf(ang), s = sinf(ang);
-                float a = src[dd], b = src[dd + half];
-                v = d < half ? a * c - b * s : a * s + b * c;
+    const int half = rot >> 1;
+    for (int d = threadIdx.x; d < half; d += blockDim.x) {
+        float ang = (float)pos * inv_freq[d];
+        cs[d] = cosf(ang);
+        cs[half + d] = sinf(ang);
+    }
+    __syncthreads();
+    size_t kv_base = 0;
+    bool have_page = false;
+    if (write_kv) {
+        int page = table[(size_t)row_req[t] * table_stride + pos / page_tokens];
+        have_page = page >= 0;                     // no page: the host never schedules this
+        kv_base = ((size_t)(have_page ? page : 0) * n_kv) * page_tokens * hd + (size_t)(pos % page_tokens) * hd;
+    }
+    const bool even = (hd % 2 == 0) && (half % 2 == 0);
+    if (even) {
+        // rotated part of q and k: units of (head slot, dim pair below half)
+        const int units_per_slot = half / 2;
+        const int rot_slots = n_heads + (write_kv && have_page ? n_kv : 0);
+        for (int u = threadIdx.x; u < rot_slots * units_per_slot; u += blockDim.x) {
+            int slot = u / units_per_slot, d = (u % units_per_slot) * 2;
+            bool is_q = slot < n_heads;
+            const float* src = is_q ? row + q_off + slot * hd : row + k_off + (slot - n_heads) * hd;
+            float2 a = *(const float2*)(src + d), b = *(const float2*)(src + d + half);
+            float c0 = cs[d], c1 = cs[d + 1], s0 = cs[half + d], s1 = cs[half + d + 1];
+            float lo0 = a.x * c0 - b.x * s0, lo1 = a.y * c1 - b.y * s1;
+            float hi0 = a.x * s0 + b.x * c0, hi1 = a.y * s1 + b.y * c1;
+            if (is_q) {
+                TQ* dst = q_out + ((size_t)t * n_heads + slot) * hd;
+                *(typename Pair<TQ>::type*)(dst + d) = Pair<TQ>::make(lo0, lo1);
+                *(typename Pair<TQ>::type*)(dst + d + half) = Pair<TQ>::make(hi0, hi1);
             } else {
-                v = src[d];
+                TC* dst = kplane + kv_base + (size_t)(slot - n_heads) * page_tokens * hd;
+                *(typename Pair<TC>::type*)(dst + d) = Pair<TC>::make(lo0, lo1);
+                *(typename Pair<TC>::type*)(dst + d + half) = Pair<TC>::make(hi0, hi1);
             }
-            dst[d] = from_f32<TQ>(v);
+        }
+        // dims past the rotary part of q and k pass through; v is copied whole
+        const int tail = hd - rot;
+        if (tail > 0) {
+            for (int u = threadIdx.x; u < rot_slots * (tail / 2); u += blockDim.x) {
+                int slot = u / (tail / 2), d = rot + (u % (tail / 2)) * 2;
+                bool is_q = slot < n_heads;
+                const float* src = is_q ? row + q_off + slot * hd : row + k_off + (slot - n_heads) * hd;
+                float2 a = *(const float2*)(src + d);
+                if (is_q) *(typename Pair<TQ>::type*)(q_out + ((size_t)t * n_heads + slot) * hd + d) = Pair<TQ>::make(a.x, a.y);
+                else *(typename Pair<TC>::type*)(kplane + kv_base + (size_t)(slot - n_heads) * page_tokens * hd + d) = Pair<TC>::make(a.x, a.y);
+            }
+        }
+        if (write_kv && have_page) {
+            for (int u = threadIdx.x; u < n_kv * (hd / 2); u += blockDim.x) {
+                int kh = u / (hd / 2), d = (u % (hd / 2)) * 2;
+                float2 a = *(const float2*)(row + v_off + kh * hd + d);
+                *(typename Pair<TC>::type*)(vplane + kv_base + (size_t)kh * page_tokens * hd + d) = Pair<TC>::make(a.x, a.y);
+            }
         }
         return;
     }
-    if (!write_kv) return;
-    int page = table[(size_t)row_req[t] * table_stride + pos / page_tokens];
-    if (page < 0) return;                  // no page: the host never schedules this
-    int in_page = pos % page_tokens;
-    if (slot < n_heads + n_kv) {
-        int kh = slot - n_heads;
-        const float* src = row + k_off + kh * hd;
-        TC* dst = kplane + (((size_t)page * n_kv + kh) * page_tokens + in_page) * hd;
-        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    // general sizes: one element at a time
+    const int slots = n_heads + (write_kv && have_page ? 2 * n_kv : 0);
+    for (int e = threadIdx.x; e < slots * hd; e += blockDim.x) {
+        int slot = e / hd, d = e % hd;
+        if (slot < n_heads + n_kv) {
+            bool is_q = slot < n_heads;
+            const float* src = is_q ? row + q_off + slot * hd : row + k_off + (slot - n_heads) * hd;
             float v;
             if (d < rot) {
                 int dd = d < half ? d : d - half;
-                float ang = (float)pos * inv_freq[dd];
-                float c = cosf(ang), s = sinf(ang);
                 float a = src[dd], b = src[dd + half];
-                v = d < half ? a * c - b * s : a * s + b * c;
+                v = d < half ? a * cs[dd] - b * cs[half + dd] : a * cs[half + dd] + b * cs[dd];
             } else {
                 v = src[d];
             }
-            dst[d] = from_f32<TC>(v);
+            if (is_q) q_out[((size_t)t * n_heads + slot) * hd + d] = from_f32<TQ>(v);
+            else kplane[kv_base + (size_t)(slot - n_heads) * page_tokens * hd + d] = from_f32<TC>(v);
+        } else {
+            int kh = slot - n_heads - n_kv;
+            vplane[kv_base + (size_t)kh * page_tokens * hd + d] = from_f32<TC>(row[v_off + kh * hd + d]);
         }
-    } else {
-        int kh = slot - n_heads - n_kv;
-        const float* src = row + v_off + kh * hd;
-        TC* dst = vplane + (((size_t)page * n_kv + kh) * page_tokens + in_page) * hd;
-        for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = from_f32<TC>(src[d]);
     }
 }
 
@@ -177,10 +218,13 @@ CJ_EXPORT int cj_rope_kv_write(const float* qkv, int ld, int q_off, int k_off, i
     if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return CJ_ERR_SIZE;
     if (rotary_dim > 0 && !inv_freq) return CJ_ERR_ARG;
     if (write_kv && (!kplane || !vplane || !row_req || !table || page_tokens <= 0 || n_kv <= 0)) return CJ_ERR_ARG;
-    dim3 grid(T, n_heads + (write_kv ? 2 * n_kv : 0));
-    int threads = hd <= 32 ? 32 : (hd <= 64 ? 64 : 128);
+    // the paired fast path reads float2: row stride and offsets must keep 8-byte alignment
+    if ((ld | q_off | k_off | v_off) & 1) return CJ_ERR_ALIGN;
+    int work = (n_heads + (write_kv ? 2 * n_kv : 0)) * hd / 2;
+    int threads = work >= 2048 ? 256 : (work >= 512 ? 128 : 64);
+    size_t smem = (size_t)rotary_dim * sizeof(float);
 #define LAUNCH(TQ, TC)                                                                                          \
-    rope_kv_write_kernel<TQ, TC><<<grid, threads, 0, stream>>>(qkv, ld, q_off, k_off, v_off, (TQ*)q_out,        \
+    rope_kv_write_kernel<TQ, TC><<<T, threads, smem, stream>>>(qkv, ld, q_off, k_off, v_off, (TQ*)q_out,        \
         (TC*)kplane, (TC*)vplane, positions, row_req, table, table_stride, page_tokens, n_heads, n_kv, hd,      \
         rotary_dim, inv_freq, write_kv)
     if (q_dtype == CJ_F32 && cache_dtype == CJ_F32) LAUNCH(float, float);
@@ -199,24 +243,52 @@ CJ_EXPORT int cj_rope_kv_write(const float* qkv, int ld, int q_off, int k_off, i
 // reference: model/MoeFfn.cajeta:1849-1916 (row form), combine kernel
 // io/QuantKernel.cajeta:40747; shared expert model/Prim.cajeta:1652-1664.
 // ---------------------------------------------------------------------------------
+template <int VEC>
 __global__ void moe_combine_kernel(float* __restrict__ hs, const float* __restrict__ y, const int* __restrict__ slot_of_pick,
                                    const float* __restrict__ w, int k, const float* __restrict__ shared, int chunks,
                                    long long chunk_stride, const float* __restrict__ shared_scale, int H) {
     int t = blockIdx.x;
-    int i = blockIdx.y * blockDim.x + threadIdx.x;
+    int i = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
     if (i >= H) return;
-    float acc = 0.0f;
+    float acc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
     for (int j = 0; j < k; ++j) {
         int s = slot_of_pick[t * k + j];
-        acc += w[t * k + j] * y[(size_t)s * H + i];
+        float wj = w[t * k + j];
+        const float* src = y + (size_t)s * H + i;
+        if (VEC == 4) {
+            float4 v4 = *(const float4*)src;
+            acc[0] += wj * v4.x; acc[1] += wj * v4.y; acc[2] += wj * v4.z; acc[3] += wj * v4.w;
+        } else {
+            acc[0] += wj * src[0];
+        }
     }
     if (shared) {
-        float sh = 0.0f;
-        for (int c = 0; c < chunks; ++c) sh += shared[c * chunk_stride + (size_t)t * H + i];
+        float sh[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) sh[v] = 0.0f;
+        for (int c = 0; c < chunks; ++c) {
+            const float* src = shared + c * chunk_stride + (size_t)t * H + i;
+            if (VEC == 4) {
+                float4 v4 = *(const float4*)src;
+                sh[0] += v4.x; sh[1] += v4.y; sh[2] += v4.z; sh[3] += v4.w;
+            } else {
+                sh[0] += src[0];
+            }
+        }
         float g = shared_scale ? shared_scale[t] : 1.0f;
-        acc += g * sh;
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[v] += g * sh[v];
     }
-    hs[(size_t)t * H + i] += acc;
+    float* dst = hs + (size_t)t * H + i;
+    if (VEC == 4) {
+        float4 o = *(float4*)dst;
+        o.x += acc[0]; o.y += acc[1]; o.z += acc[2]; o.w += acc[3];
+        *(float4*)dst = o;
+    } else {
+        dst[0] += acc[0];
+    }
 }
 
 CJ_EXPORT int cj_moe_combine(float* hs, const float* y, const int* slot_of_pick, const float* w, int k,
@@ -225,10 +297,13 @@ CJ_EXPORT int cj_moe_combine(float* hs, const float* y, const int* slot_of_pick,
     if (T <= 0) return 0;
     if (!hs || H <= 0 || k < 0 || (k > 0 && (!y || !slot_of_pick || !w))) return CJ_ERR_ARG;
     if (shared && chunks < 1) return CJ_ERR_ARG;
-    int threads = H >= 256 ? 256 : 128;
-    dim3 grid(T, (H + threads - 1) / threads);
+    bool vec = H % 4 == 0 && chunk_stride % 4 == 0 && ((((uintptr_t)hs) | ((uintptr_t)y) | ((uintptr_t)shared)) & 15) == 0;
+    int per = vec ? 4 : 1;
+    int threads = H / per >= 256 ? 256 : 128;
+    dim3 grid(T, (H / per + threads - 1) / threads + (H % per ? 1 : 0));
     if (grid.y > 65535) return CJ_ERR_SIZE;
-    moe_combine_kernel<<<grid, threads, 0, stream>>>(hs, y, slot_of_pick, w, k, shared, chunks, chunk_stride, shared_scale, H);
+    if (vec) moe_combine_kernel<4><<<grid, threads, 0, stream>>>(hs, y, slot_of_pick, w, k, shared, chunks, chunk_stride, shared_scale, H);
+    else moe_combine_kernel<1><<<grid, threads, 0, stream>>>(hs, y, slot_of_pick, w, k, shared, chunks, chunk_stride, shared_scale, H);
     return launch_status();
 }
 

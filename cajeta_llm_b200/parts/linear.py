@@ -61,6 +61,10 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
     # rows than the step has tokens, which bounds the token tile
     bound = rows if max_group_rows is None else min(rows, max_group_rows)
     tile = _token_tile(bound)
+    if not tile and group_offsets is not None:
+        # ragged groups: weights on the rows, up to 128 tokens on the product's N, which is
+        # cut to the tokens a tile really has - a group of 136 rows costs 128 + 16, not 256
+        tile = 128
     if tile:
         K.gemm_tc(x, w, out, epi, True, tile, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows)
     else:
