@@ -65,7 +65,7 @@ struct Smem {
     static constexpr int TOTAL = TILE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
-constexpr int ACC_STAGES = 2;       // accumulators in tensor memory: one is drained while the next is filled
+constexpr int MAX_ACC_STAGES = 2;   // accumulators in tensor memory: one is drained while the next is filled
 constexpr int MAX_GROUPS = 1024;
 
 // Work of one block, in the order it takes its tiles: tile = blockIdx.x + i * gridDim.x.
@@ -129,6 +129,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     constexpr int FEAT_TILE = S::W_ROWS;         // weight rows a tile covers
     constexpr uint32_t ACC_COLS = N_MMA;         // tensor-memory columns of one accumulator
     constexpr uint32_t STAGE_COLS = ACC_COLS * (DUAL ? 2 : 1);
+    // two accumulator stages when they fit the 512 columns of tensor memory, else one (the
+    // products of the next tile then wait for the epilogue; the loads still run ahead)
+    constexpr int ACC_STAGES = STAGE_COLS * MAX_ACC_STAGES <= 512 ? MAX_ACC_STAGES : 1;
     constexpr uint32_t TMEM_COLS_NEEDED = STAGE_COLS * ACC_STAGES;
     constexpr uint32_t TMEM_COLS = TMEM_COLS_NEEDED <= 32 ? 32 : TMEM_COLS_NEEDED <= 64 ? 64 : TMEM_COLS_NEEDED <= 128 ? 128
                                    : TMEM_COLS_NEEDED <= 256 ? 256 : 512;
@@ -140,8 +143,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint64_t* full_bar = (uint64_t*)(tiles + S::TILE_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* acc_full = empty_bar + STAGES;
-    uint64_t* acc_empty = acc_full + ACC_STAGES;
-    uint32_t* tmem_slot = (uint32_t*)(acc_empty + ACC_STAGES);
+    uint64_t* acc_empty = acc_full + MAX_ACC_STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + MAX_ACC_STAGES);
     __shared__ int tiles_before[MAX_GROUPS + 1];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -405,7 +408,11 @@ int dispatch_n(int n_mma, const CUtensorMap& mx, const CUtensorMap& mw, const CU
             case 16: return launch_auto<16, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
             case 32: return launch_auto<32, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
             case 64: return launch_auto<64, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
+            case 96: return launch_auto<96, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
             case 128: return launch_auto<128, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
+            case 160: return launch_auto<160, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
+            case 192: return launch_auto<192, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
+            case 256: return launch_auto<256, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
         }
     } else {
         switch (n_mma) {

@@ -283,7 +283,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     bfloat16 with float32 accumulation (tcgen05, TMA).
 
     ``swap`` False: tiles of 128 tokens x ``n_mma`` (128 or 256) features; True: tiles of 128
-    features x ``n_mma`` (16, 32, 64, 128) tokens.  ``epilogue``: EPI_STORE_F32, EPI_ACC_F32,
+    features x ``n_mma`` (16, 32, 64, 96, 128, 160, 192, 256) tokens.  ``epilogue``: EPI_STORE_F32, EPI_ACC_F32,
     EPI_SWIGLU_BF16 (``w_up`` given), EPI_STORE_BF16.  With ``group_offsets`` the rows of
     ``x`` are sorted by group and ``w`` is [groups, features, K].  ``k_splits`` > 1 (store
     only): ``out`` is [k_splits, tokens, features] of partial sums.

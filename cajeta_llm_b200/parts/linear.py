@@ -29,11 +29,25 @@ def _tc_ok(runtime, x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and x.stride(-1) == 1)
 
 
+TOKEN_TILES = (16, 32, 64, 96, 128, 160, 192, 256)     # token tiles of the weights-on-rows orientation
+
+
 def _token_tile(rows: int) -> int:
     for n in (16, 32, 64, 128):
         if rows <= n:
             return n
     return 0
+
+
+def _group_tile(total_rows: int, groups: int) -> int:
+    """Token tile for ragged groups: wide enough that a typical group (mean + two standard
+    deviations of an even split) is one tile, so its weights are streamed once."""
+    mean = total_rows / max(1, groups)
+    want = mean + 2.0 * mean ** 0.5
+    for n in TOKEN_TILES:
+        if want <= n:
+            return n
+    return TOKEN_TILES[-1]
 
 
 def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
@@ -62,9 +76,11 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
     bound = rows if max_group_rows is None else min(rows, max_group_rows)
     tile = _token_tile(bound)
     if not tile and group_offsets is not None:
-        # ragged groups: weights on the rows, up to 128 tokens on the product's N, which is
-        # cut to the tokens a tile really has - a group of 136 rows costs 128 + 16, not 256
-        tile = 128
+        # ragged groups: weights on the rows, tokens on the product's N (cut to the tokens a
+        # tile really has), the tile wide enough that most groups stream their weights once
+        # (the SwiGLU form keeps two accumulators per stage: beyond 128 tokens tensor memory
+        # holds one stage only and the epilogue no longer overlaps the next tile)
+        tile = min(128, _group_tile(rows, w.shape[0])) if w_up is not None else _group_tile(rows, w.shape[0])
     if tile:
         K.gemm_tc(x, w, out, epi, True, tile, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows)
     else:

@@ -59,10 +59,10 @@ def test_swiglu(K, swap, n_mma, T):
     close(out, want, atol=2e-2, rtol=1e-2)
 
 
-@pytest.mark.parametrize("swap,n_mma", [(False, 128), (True, 16), (True, 32)])
+@pytest.mark.parametrize("swap,n_mma", [(False, 128), (True, 16), (True, 32), (True, 96), (True, 128), (True, 160), (True, 192), (True, 256)])
 def test_grouped(K, swap, n_mma):
     E, N, Kd = 6, 200, 192
-    counts = [0, 37, 1, 150, 0, 20] if not swap else [0, 3, 1, 20, 0, 7]
+    counts = [0, 3, 1, 20, 0, 7] if (swap and n_mma <= 32) else [0, 37, 1, 300, 0, 520]
     T = sum(counts)
     offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
     x = rnd(T, Kd, seed=8)
