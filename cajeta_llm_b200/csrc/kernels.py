@@ -58,6 +58,7 @@ def _stream() -> ctypes.c_void_p:
 
 
 launches = 0      # kernels launched through this module since import (each wrapper launches one)
+_router_tickets: Dict[torch.device, torch.Tensor] = {}      # arrival tickets of the small-batch router (kept zero by the kernel)
 
 
 def _check(status: int, what: str) -> None:
@@ -202,12 +203,16 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
     if shared_gate is not None:
         _need(shared_gate, "shared_gate", torch.float32), _need(shared_scale, "shared_scale", torch.float32)
     logits = torch.empty((T, E + 1), dtype=torch.float32, device=x.device)
+    tickets = _router_tickets.get(x.device)
+    if tickets is None:
+        tickets = _router_tickets[x.device] = torch.zeros((4,), dtype=torch.int32, device=x.device)
     st = library("moe_route").cj_router_topk(_ptr(x), _ptr(router_w), _ptr(shared_gate), _i(T), _i(H), _i(E), _i(top_k),
                                              _i(1 if norm_topk else 0), _ptr(sel), _ptr(weights), _ptr(shared_scale),
-                                             _ptr(logits), _stream())
+                                             _ptr(logits), _ptr(tickets), _stream())
     _check(st, "router_topk")
-    global launches
-    launches += 1                      # two kernels: logits, then selection
+    if T > 32:
+        global launches
+        launches += 1                  # many rows take two kernels: logits, then selection
 
 
 def moe_group(sel: torch.Tensor, top_k: int, num_experts: int, offsets: torch.Tensor, slot_token: torch.Tensor,

@@ -95,72 +95,10 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_logits_kernel(
     }
 }
 
-// The same logits for a handful of rows (decode): one warp per expert reads its weight row
-// and the rows of x straight from global memory (they sit in L2), with the same lane-strided
-// sum as above, so both kernels give the same bits for a row.
-constexpr int SMALL_WARPS = 4;
-__global__ void __launch_bounds__(SMALL_WARPS * 32) router_logits_small_kernel(
-    const float* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ shared_gate, int T, int H,
-    int E, float* __restrict__ logits) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n_cols = E + (shared_gate ? 1 : 0);
-    const int e = blockIdx.x * SMALL_WARPS + warp;
-    if (e >= n_cols) return;
-    const float* wr = e < E ? Wr + (size_t)e * H : shared_gate;
-    const bool vec = (H % 4) == 0;
-    for (int t0 = 0; t0 < T; t0 += 8) {
-        const int n_tok = min(8, T - t0);
-        float acc[8];
-#pragma unroll
-        for (int tt = 0; tt < 8; ++tt) acc[tt] = 0.0f;
-        if (vec) {
-            // the weight row is cold (the experts' weights have flushed L2 since the last
-            // layer): eight loads are put in flight before the first is used
-            for (int j0 = lane * 4; j0 < H; j0 += 128 * 8) {
-                float4 wv[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    int j = j0 + 128 * u;
-                    wv[u] = j < H ? __ldg((const float4*)(wr + j)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    int j = j0 + 128 * u;
-                    if (j >= H) break;
-#pragma unroll
-                    for (int tt = 0; tt < 8; ++tt) {
-                        if (tt < n_tok) {
-                            float4 x4 = *(const float4*)(x + (size_t)(t0 + tt) * H + j);
-                            acc[tt] = fmaf(wv[u].x, x4.x, acc[tt]);
-                            acc[tt] = fmaf(wv[u].y, x4.y, acc[tt]);
-                            acc[tt] = fmaf(wv[u].z, x4.z, acc[tt]);
-                            acc[tt] = fmaf(wv[u].w, x4.w, acc[tt]);
-                        }
-                    }
-                }
-            }
-        } else {
-            for (int j = lane; j < H; j += 32) {
-                float wv = wr[j];
-#pragma unroll
-                for (int tt = 0; tt < 8; ++tt)
-                    if (tt < n_tok) acc[tt] = fmaf(wv, x[(size_t)(t0 + tt) * H + j], acc[tt]);
-            }
-        }
-#pragma unroll
-        for (int tt = 0; tt < 8; ++tt) {
-            float v = warp_sum(acc[tt]);
-            if (lane == 0 && tt < n_tok) logits[(size_t)(t0 + tt) * n_cols + e] = v;
-        }
-    }
-}
-
-__global__ void __launch_bounds__(32) router_select_kernel(
-    const float* __restrict__ logits, int E, int n_cols, int k, int norm_topk, int* __restrict__ sel,
-    float* __restrict__ w, float* __restrict__ shared_scale) {
-    __shared__ float probs[MAX_EXPERTS];
-    const int t = blockIdx.x, lane = threadIdx.x;
-    const float* row = logits + (size_t)t * n_cols;
+// softmax over all experts, top-k, optional renormalisation, the shared gate's sigmoid: one
+// warp per row; probs is the warp's scratch of E floats in shared memory
+__device__ __forceinline__ void select_row(const float* row, int t, int E, int k, int norm_topk, int* __restrict__ sel,
+                                           float* __restrict__ w, float* __restrict__ shared_scale, float* probs, int lane) {
     if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-row[E]));
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
@@ -202,6 +140,74 @@ __global__ void __launch_bounds__(32) router_select_kernel(
         if (wsum < 0.00006103515625f) wsum = 0.00006103515625f;
         for (int j = 0; j < k; ++j) w[t * k + j] = w[t * k + j] / wsum;
     }
+}
+
+// The same logits for a handful of rows (decode), and the selection, in ONE launch: a block
+// is one expert and up to eight rows, one row per warp, each warp with the same
+// lane-strided sum as above (so both kernels give the same bits for a row); all loads of a
+// warp are independent and go out together, which matters because the weight row is cold
+// (the experts' weights have flushed L2 since the last layer).  The block that finishes a
+// group of rows last (a ticket in global memory, left at zero again) runs the selection for
+// those rows.
+constexpr int SMALL_ROWS = 8;
+__global__ void __launch_bounds__(SMALL_ROWS * 32) router_small_kernel(
+    const float* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ shared_gate, int T, int H,
+    int E, int k, int norm_topk, float* __restrict__ logits, int* __restrict__ sel, float* __restrict__ w,
+    float* __restrict__ shared_scale, int* __restrict__ tickets) {
+    __shared__ float probs[SMALL_ROWS][MAX_EXPERTS];
+    __shared__ int is_last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_cols = E + (shared_gate ? 1 : 0);
+    const int e = blockIdx.x;
+    const int t = blockIdx.y * SMALL_ROWS + warp;
+    if (t < T) {
+        const float* wr = e < E ? Wr + (size_t)e * H : shared_gate;
+        const float* xr = x + (size_t)t * H;
+        float acc = 0.0f;
+        if ((H % 4) == 0) {
+            for (int j0 = lane * 4; j0 < H; j0 += 128 * 8) {
+                float4 wv[8], xv[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    int j = j0 + 128 * u;
+                    wv[u] = j < H ? __ldg((const float4*)(wr + j)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    xv[u] = j < H ? *(const float4*)(xr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (j0 + 128 * u >= H) break;
+                    acc = fmaf(wv[u].x, xv[u].x, acc);
+                    acc = fmaf(wv[u].y, xv[u].y, acc);
+                    acc = fmaf(wv[u].z, xv[u].z, acc);
+                    acc = fmaf(wv[u].w, xv[u].w, acc);
+                }
+            }
+        } else {
+            for (int j = lane; j < H; j += 32) acc = fmaf(wr[j], xr[j], acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) logits[(size_t)t * n_cols + e] = acc;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int done = atomicAdd(&tickets[blockIdx.y], 1);
+        is_last = done == n_cols - 1;
+        if (is_last) tickets[blockIdx.y] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (t < T) {
+        select_row(logits + (size_t)t * n_cols, t, E, k, norm_topk, sel, w, shared_scale, probs[warp], lane);
+    }
+}
+
+__global__ void __launch_bounds__(32) router_select_kernel(
+    const float* __restrict__ logits, int E, int n_cols, int k, int norm_topk, int* __restrict__ sel,
+    float* __restrict__ w, float* __restrict__ shared_scale) {
+    __shared__ float probs[MAX_EXPERTS];
+    select_row(logits + (size_t)blockIdx.x * n_cols, blockIdx.x, E, k, norm_topk, sel, w, shared_scale, probs, threadIdx.x);
 }
 
 // Counting sort of the picks (token t, choice j) by expert, stable.  One block per
@@ -277,20 +283,19 @@ __global__ void __launch_bounds__(GROUP_WARPS * 32) moe_group_kernel(
 }  // namespace
 
 // logits: scratch [T, E + 1] float32 (column E holds the shared gate's dot when a gate is given).
+// tickets: int32 [4], zero before the first use (the kernel leaves them zero); may be null, the two-launch form is then used.
 CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* shared_gate, int T, int H, int E, int k,
-                             int norm_topk, int* sel, float* w, float* shared_scale, float* logits,
+                             int norm_topk, int* sel, float* w, float* shared_scale, float* logits, int* tickets,
                              cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!x || !Wr || !sel || !w || !logits || H <= 0) return CJ_ERR_ARG;
     if (shared_gate && !shared_scale) return CJ_ERR_ARG;
     if (E < 1 || E > MAX_EXPERTS || k < 1 || k > E) return CJ_ERR_SIZE;
     const int n_cols = E + (shared_gate ? 1 : 0);
-    if (T <= 32) {
-        router_logits_small_kernel<<<(n_cols + SMALL_WARPS - 1) / SMALL_WARPS, SMALL_WARPS * 32, 0, stream>>>(
-            x, Wr, shared_gate, T, H, E, logits);
-        int st0 = launch_status();
-        if (st0) return st0;
-        router_select_kernel<<<T, 32, 0, stream>>>(logits, E, n_cols, k, norm_topk, sel, w, shared_gate ? shared_scale : nullptr);
+    if (T <= 32 && tickets) {
+        dim3 grid_small(n_cols, (T + SMALL_ROWS - 1) / SMALL_ROWS);
+        router_small_kernel<<<grid_small, SMALL_ROWS * 32, 0, stream>>>(x, Wr, shared_gate, T, H, E, k, norm_topk, logits, sel, w,
+                                                                         shared_gate ? shared_scale : nullptr, tickets);
         return launch_status();
     }
     // rows of x staged per block: as many as fit 200 KB of shared memory, at most 8

@@ -40,7 +40,9 @@ CJ_EXPORT int cj_embed_gather(float* out, const void* table, int table_dtype, co
 // be picked through row_index (the rows whose logits are wanted).  Writes the result
 // in the activation dtype and, when asked, a float32 copy (the router's input).
 // ---------------------------------------------------------------------------------
-template <typename TO>
+// The row is read once into registers (with the weight, whose load is then in flight during
+// the reduction) when it fits PER elements a thread; otherwise it is read twice.
+template <typename TO, int PER>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ w, float eps, int H,
                                TO* __restrict__ out, float* __restrict__ out_f32,
                                const int* __restrict__ row_index, const float* __restrict__ partials, int n_partials,
@@ -50,14 +52,39 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     int r = blockIdx.x;
     float* src = x + (size_t)(row_index ? row_index[r] : r) * H;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = src[i];
+    float xv[PER > 0 ? PER : 1], wv[PER > 0 ? PER : 1];
+    if (PER > 0) {
+#pragma unroll
+        for (int q = 0; q < PER; ++q) {
+            int i = threadIdx.x + q * blockDim.x;
+            xv[q] = i < H ? src[i] : 0.0f;
+            wv[q] = i < H ? w[i] : 0.0f;
+        }
         if (partials) {
             // the split sums of the product before this norm: added in split order, stored back
-            for (int s = 0; s < n_partials; ++s) v += partials[s * partial_stride + (size_t)r * H + i];
-            src[i] = v;
+            for (int s = 0; s < n_partials; ++s)
+#pragma unroll
+                for (int q = 0; q < PER; ++q) {
+                    int i = threadIdx.x + q * blockDim.x;
+                    if (i < H) xv[q] += partials[s * partial_stride + (size_t)r * H + i];
+                }
+#pragma unroll
+            for (int q = 0; q < PER; ++q) {
+                int i = threadIdx.x + q * blockDim.x;
+                if (i < H) src[i] = xv[q];
+            }
         }
-        ss = fmaf(v, v, ss);
+#pragma unroll
+        for (int q = 0; q < PER; ++q) ss = fmaf(xv[q], xv[q], ss);
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = src[i];
+            if (partials) {
+                for (int s = 0; s < n_partials; ++s) v += partials[s * partial_stride + (size_t)r * H + i];
+                src[i] = v;
+            }
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = warp_sum(ss);
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -70,10 +97,22 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     }
     __syncthreads();
     float scale = scale_s;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float y = src[i] * scale * w[i];
-        out[(size_t)r * H + i] = from_f32<TO>(y);
-        if (out_f32) out_f32[(size_t)r * H + i] = y;
+    if (PER > 0) {
+#pragma unroll
+        for (int q = 0; q < PER; ++q) {
+            int i = threadIdx.x + q * blockDim.x;
+            if (i < H) {
+                float y = xv[q] * scale * wv[q];
+                out[(size_t)r * H + i] = from_f32<TO>(y);
+                if (out_f32) out_f32[(size_t)r * H + i] = y;
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float y = src[i] * scale * w[i];
+            out[(size_t)r * H + i] = from_f32<TO>(y);
+            if (out_f32) out_f32[(size_t)r * H + i] = y;
+        }
     }
 }
 
@@ -87,12 +126,17 @@ CJ_EXPORT int cj_rmsnorm(float* x, const float* w, float eps, int rows, int H, v
     if (!x || !w || !out || H <= 0) return CJ_ERR_ARG;
     if (partials && (row_index || n_partials < 1)) return CJ_ERR_ARG;
     int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    if (out_dtype == CJ_F32)
-        rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(x, w, eps, H, (float*)out, out_f32, row_index, partials, n_partials, partial_stride);
-    else if (out_dtype == CJ_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(x, w, eps, H, (__nv_bfloat16*)out, out_f32, row_index, partials, n_partials, partial_stride);
-    else
-        return CJ_ERR_DTYPE;
+    int per = (H + threads - 1) / threads;
+#define LAUNCH(TO, PER) rmsnorm_kernel<TO, PER><<<rows, threads, 0, stream>>>(x, w, eps, H, (TO*)out, out_f32, row_index, partials, n_partials, partial_stride)
+#define PICK(TO)                                   \
+    if (per <= 4) LAUNCH(TO, 4);                   \
+    else if (per <= 8) LAUNCH(TO, 8);              \
+    else LAUNCH(TO, 0)
+    if (out_dtype == CJ_F32) { PICK(float); }
+    else if (out_dtype == CJ_BF16) { PICK(__nv_bfloat16); }
+    else return CJ_ERR_DTYPE;
+#undef PICK
+#undef LAUNCH
     return launch_status();
 }
 
@@ -124,6 +168,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int 
                                      int write_kv) {
     extern __shared__ float cs[];                 // cos[half] then sin[half]
     const int t = blockIdx.x;
+    // with few rows the units of a row are shared out over gridDim.y blocks
+    const int part = blockIdx.y, parts = gridDim.y;
     const int pos = positions[t];
     const float* row = qkv + (size_t)t * ld;
     const int half = rot >> 1;
@@ -145,7 +191,7 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int 
         // rotated part of q and k: units of (head slot, dim pair below half)
         const int units_per_slot = half / 2;
         const int rot_slots = n_heads + (write_kv && have_page ? n_kv : 0);
-        for (int u = threadIdx.x; u < rot_slots * units_per_slot; u += blockDim.x) {
+        for (int u = part * blockDim.x + threadIdx.x; u < rot_slots * units_per_slot; u += parts * blockDim.x) {
             int slot = u / units_per_slot, d = (u % units_per_slot) * 2;
             bool is_q = slot < n_heads;
             const float* src = is_q ? row + q_off + slot * hd : row + k_off + (slot - n_heads) * hd;
@@ -166,7 +212,7 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int 
         // dims past the rotary part of q and k pass through; v is copied whole
         const int tail = hd - rot;
         if (tail > 0) {
-            for (int u = threadIdx.x; u < rot_slots * (tail / 2); u += blockDim.x) {
+            for (int u = part * blockDim.x + threadIdx.x; u < rot_slots * (tail / 2); u += parts * blockDim.x) {
                 int slot = u / (tail / 2), d = rot + (u % (tail / 2)) * 2;
                 bool is_q = slot < n_heads;
                 const float* src = is_q ? row + q_off + slot * hd : row + k_off + (slot - n_heads) * hd;
@@ -176,7 +222,7 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int 
             }
         }
         if (write_kv && have_page) {
-            for (int u = threadIdx.x; u < n_kv * (hd / 2); u += blockDim.x) {
+            for (int u = part * blockDim.x + threadIdx.x; u < n_kv * (hd / 2); u += parts * blockDim.x) {
                 int kh = u / (hd / 2), d = (u % (hd / 2)) * 2;
                 float2 a = *(const float2*)(row + v_off + kh * hd + d);
                 *(typename Pair<TC>::type*)(vplane + kv_base + (size_t)kh * page_tokens * hd + d) = Pair<TC>::make(a.x, a.y);
@@ -186,7 +232,7 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int 
     }
     // general sizes: one element at a time
     const int slots = n_heads + (write_kv && have_page ? 2 * n_kv : 0);
-    for (int e = threadIdx.x; e < slots * hd; e += blockDim.x) {
+    for (int e = part * blockDim.x + threadIdx.x; e < slots * hd; e += parts * blockDim.x) {
         int slot = e / hd, d = e % hd;
         if (slot < n_heads + n_kv) {
             bool is_q = slot < n_heads;
@@ -223,8 +269,12 @@ CJ_EXPORT int cj_rope_kv_write(const float* qkv, int ld, int q_off, int k_off, i
     int work = (n_heads + (write_kv ? 2 * n_kv : 0)) * hd / 2;
     int threads = work >= 2048 ? 256 : (work >= 512 ? 128 : 64);
     size_t smem = (size_t)rotary_dim * sizeof(float);
+    int parts = T >= 128 ? 1 : (work + threads * 2 - 1) / (threads * 2);      // few rows: ~2 units a thread
+    if (parts < 1) parts = 1;
+    if (parts > 16) parts = 16;
+    dim3 grid(T, parts);
 #define LAUNCH(TQ, TC)                                                                                          \
-    rope_kv_write_kernel<TQ, TC><<<T, threads, smem, stream>>>(qkv, ld, q_off, k_off, v_off, (TQ*)q_out,        \
+    rope_kv_write_kernel<TQ, TC><<<grid, threads, smem, stream>>>(qkv, ld, q_off, k_off, v_off, (TQ*)q_out,     \
         (TC*)kplane, (TC*)vplane, positions, row_req, table, table_stride, page_tokens, n_heads, n_kv, hd,      \
         rotary_dim, inv_freq, write_kv)
     if (q_dtype == CJ_F32 && cache_dtype == CJ_F32) LAUNCH(float, float);
