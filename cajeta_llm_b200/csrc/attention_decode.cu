@@ -1,8 +1,8 @@
 // Decode attention for the bfloat16 path: few query rows, each over a long stretch of
 // cached keys.  The keys of a row are cut into fixed chunks of 128 ("split-KV"); one
-// block takes one (row, kv head, chunk), each thread one key of the chunk for the scores
-// and a pair of output dims for the weighted sum of values, for every query head of the
-// kv head's group.  A chunk leaves a partial (max, sum, unnormalised accumulator); the
+// block takes one (row, kv head, chunk), stages the chunk's keys and values in shared
+// memory, and then each thread takes one key for the scores and eight output dims of a
+// key phase for the weighted sum of values, for every query head of the kv head's group.  A chunk leaves a partial (max, sum, unnormalised accumulator); the
 // block that finishes a (row, head) last merges the partials in chunk order, so the
 // result does not depend on which block arrived when, nor - the chunking being a function
 // of the row's own [from, p] - on what else is in the batch.
@@ -18,15 +18,29 @@ namespace {
 
 constexpr int CHUNK = 128;       // keys per block = threads per block
 
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// The chunk's keys and values are fetched with cp.async in one go (every load of the block
+// is in flight at once) into shared memory, 16-byte pieces XOR-swizzled by row so that both
+// the per-key reads of the scores and the per-column reads of the value sum are free of
+// bank conflicts; all query heads of the kv head's group then work from shared memory.
 template <int HD>
 __global__ void __launch_bounds__(CHUNK) decode_attention_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ kplane,
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ positions, const int* __restrict__ row_req,
     const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int window, float scale,
     float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters, int max_splits) {
-    constexpr int VEC = 8;                        // dims one thread owns in the value sum (one 16-byte load)
-    constexpr int COLS = HD / VEC;                // threads that cover a value row
+    constexpr int VEC = 8;                        // dims one thread owns in the value sum (one 16-byte piece)
+    constexpr int COLS = HD / VEC;                // pieces of a row
     constexpr int KPAR = CHUNK / COLS;            // key phases working side by side in the value sum
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;             // [CHUNK][HD], pieces swizzled
+    __nv_bfloat16* vs = ks + CHUNK * HD;                      // [CHUNK][HD], pieces swizzled
     __shared__ __align__(16) float qs[HD];
     __shared__ float es[CHUNK];
     __shared__ long long bases[CHUNK];
@@ -52,27 +66,39 @@ __global__ void __launch_bounds__(CHUNK) decode_attention_kernel(
         int page = tab[key / page_tokens];
         bases[tid] = (((long long)page * n_kv + kvh) * page_tokens + key % page_tokens) * HD;
     }
+    __syncthreads();
+    // all keys, then all values, on their way to shared memory
+    for (int i = tid; i < count * COLS; i += CHUNK) {
+        int r = i / COLS, c = i % COLS;
+        cp_async16(ks + r * HD + ((c ^ (r & 7)) * VEC), kplane + bases[r] + c * VEC);
+    }
+    cp_async_commit();
+    for (int i = tid; i < count * COLS; i += CHUNK) {
+        int r = i / COLS, c = i % COLS;
+        cp_async16(vs + r * HD + ((c ^ (r & 7)) * VEC), vplane + bases[r] + c * VEC);
+    }
+    cp_async_commit();
 
     for (int hg = 0; hg < group; ++hg) {
         const int h = kvh * group + hg;
-        __syncthreads();                                        // bases ready; previous head done with qs / es / vsum
+        __syncthreads();                                        // previous head done with qs / es / vsum
         if (tid < HD) qs[tid] = __bfloat162float(q[((size_t)t * n_heads + h) * HD + tid]);
-        __syncthreads();
+        if (hg == 0) cp_async_wait<1>();                        // this thread's key pieces have landed
+        __syncthreads();                                        // everyone's
 
-        // scores: one key per thread, the key row read in 16-byte pieces
+        // scores: one key per thread
         float s = -INFINITY;
         if (tid < count) {
-            const uint4* kr = (const uint4*)(kplane + bases[tid]);
             float dot = 0.0f;
 #pragma unroll
-            for (int i = 0; i < HD / 8; ++i) {
-                uint4 u = kr[i];
+            for (int c = 0; c < COLS; ++c) {
+                uint4 u = *(const uint4*)(ks + tid * HD + ((c ^ (tid & 7)) * VEC));
                 const __nv_bfloat162* b2 = (const __nv_bfloat162*)&u;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     float2 f = __bfloat1622float2(b2[j]);
-                    dot = fmaf(qs[i * 8 + 2 * j], f.x, dot);
-                    dot = fmaf(qs[i * 8 + 2 * j + 1], f.y, dot);
+                    dot = fmaf(qs[c * 8 + 2 * j], f.x, dot);
+                    dot = fmaf(qs[c * 8 + 2 * j + 1], f.y, dot);
                 }
             }
             s = dot * scale;
@@ -84,12 +110,13 @@ __global__ void __launch_bounds__(CHUNK) decode_attention_kernel(
         float e = tid < count ? expf(s - m) : 0.0f;
         es[tid] = e;
         float l = warp_sum(e);
-        __syncthreads();                                        // everyone has read red
+        if (hg == 0) cp_async_wait<0>();                        // this thread's value pieces have landed
+        __syncthreads();                                        // everyone has read red; es and values visible
         if (lane == 0) red[warp] = l;
         __syncthreads();
         l = (red[0] + red[1]) + (red[2] + red[3]);
 
-        // values: thread = (8 dims, key phase); the keys of its phase in order, 16 bytes a load
+        // values: thread = (8 dims, key phase); the keys of its phase in order
         const int col = tid % COLS, phase = tid / COLS;
         float acc[VEC];
 #pragma unroll
@@ -97,7 +124,7 @@ __global__ void __launch_bounds__(CHUNK) decode_attention_kernel(
 #pragma unroll 4
         for (int j = phase; j < count; j += KPAR) {
             float ej = es[j];
-            uint4 u = *(const uint4*)(vplane + bases[j] + VEC * col);
+            uint4 u = *(const uint4*)(vs + j * HD + ((col ^ (j & 7)) * VEC));
             const __nv_bfloat162* b2 = (const __nv_bfloat162*)&u;
 #pragma unroll
             for (int d = 0; d < VEC / 2; ++d) {
@@ -180,10 +207,19 @@ CJ_EXPORT int cj_decode_attention(const void* q, void* out, const void* kplane, 
     if (splits > max_splits || splits > 65535 || n_kv > 65535) return CJ_ERR_SIZE;
     dim3 grid(T, n_kv, splits);
 #define LAUNCH(HD)                                                                                                     \
-    decode_attention_kernel<HD><<<grid, CHUNK, 0, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,              \
-        (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane, positions, row_req, table, table_stride,           \
-        page_tokens, n_heads, n_kv, window, scale, part_acc, part_ml, counters, max_splits)
-    if (hd == 128) LAUNCH(128); else LAUNCH(64);
+    {                                                                                                                  \
+        constexpr int smem = 2 * CHUNK * HD * (int)sizeof(__nv_bfloat16);                                              \
+        static bool configured = false;                                                                                \
+        if (!configured) {                                                                                             \
+            cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+            if (e != cudaSuccess) return (int)e;                                                                       \
+            configured = true;                                                                                         \
+        }                                                                                                              \
+        decode_attention_kernel<HD><<<grid, CHUNK, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,       \
+            (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane, positions, row_req, table, table_stride,       \
+            page_tokens, n_heads, n_kv, window, scale, part_acc, part_ml, counters, max_splits);                       \
+    }
+    if (hd == 128) LAUNCH(128) else LAUNCH(64)
 #undef LAUNCH
     return launch_status();
 }
