@@ -1,4 +1,4 @@
-// Attention for steps that carry portions of prompts (bfloat16 path): tiles of 64 query
+// Attention for steps that carry portions of prompts (bfloat16 path): tiles of 64 or 128 query
 // rows of one request against tiles of 64 cached keys, scores and weighted values on the
 // tensor cores (mma.sync m16n8k16, bf16 in, f32 out), softmax statistics in float32
 // registers, keys and values fetched from cache pages through the block table with
@@ -18,7 +18,7 @@ using namespace cj;
 
 namespace {
 
-constexpr int BM = 64, BN = 64, THREADS = 128;
+constexpr int BN = 64;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -55,8 +55,8 @@ __device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat16* base, int row,
     return base + row * HD + chunk * 8 + (col & 7);
 }
 
-template <int HD>
-__global__ void __launch_bounds__(THREADS) prefill_attention_kernel(
+template <int HD, int BM>
+__global__ void __launch_bounds__(BM * 2) prefill_attention_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ kplane,
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ req_start, const int* __restrict__ req_prior,
     int n_requests, const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int window,
@@ -66,9 +66,12 @@ __global__ void __launch_bounds__(THREADS) prefill_attention_kernel(
     __nv_bfloat16* ks = qs + BM * HD;                             // [2][BN][HD]
     __nv_bfloat16* vs = ks + 2 * BN * HD;                         // [2][BN][HD]
     constexpr int CH = HD / 8;                                    // 16-byte chunks per row
+    constexpr int THREADS = BM * 2;                               // one warp per 16 query rows
 
-    // ---- which request and which 64-row tile of it ------------------------------------
-    int tile = blockIdx.x, req = -1, row0 = 0, rows = 0, first = 0;
+    // ---- which request and which BM-row tile of it --------------------------------------
+    // the grid walks the tiles from the last to the first: in a causal prompt the late tiles
+    // have the most keys, and starting them first evens out the tail
+    int tile = (int)gridDim.x - 1 - (int)blockIdx.x, req = -1, row0 = 0, rows = 0, first = 0;
     for (int r = 0; r < n_requests; ++r) {
         int lo = req_start[r], hi = req_start[r + 1];
         int tiles = (hi - lo + BM - 1) / BM;
@@ -236,31 +239,34 @@ __global__ void __launch_bounds__(THREADS) prefill_attention_kernel(
 
 // q, out: [T, n_heads, hd] bf16; planes [pages, n_kv, page_tokens, hd] bf16; req_start
 // [n_requests + 1], req_prior [n_requests] as the step function lays them out.  hd must be
-// 64 or 128.
+// 64 or 128.  block_rows: 64 or 128 query rows a block, 0 = chosen from the step's shape.
 CJ_EXPORT int cj_prefill_attention(const void* q, void* out, const void* kplane, const void* vplane, const int* req_start,
                                    const int* req_prior, int n_requests, int total_rows, const int* table, int table_stride,
                                    int page_tokens, int n_heads, int n_kv, int hd, int window, float scale,
-                                   cudaStream_t stream) {
+                                   int block_rows, cudaStream_t stream) {
     if (total_rows <= 0 || n_requests <= 0) return 0;
     if (!q || !out || !kplane || !vplane || !req_start || !req_prior || !table) return CJ_ERR_ARG;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || page_tokens <= 0 || n_heads > 65535) return CJ_ERR_SIZE;
     if (hd != 64 && hd != 128) return CJ_ERR_SIZE;
-    dim3 grid((total_rows + BM - 1) / BM + n_requests, n_heads);
-    size_t smem = (size_t)(BM + 4 * BN) * hd * sizeof(__nv_bfloat16);
     float scale_log2 = scale * 1.4426950408889634f;
-#define LAUNCH(HD)                                                                                                      \
+    // query tile: 128 rows when the step is mostly long portions, 64 otherwise
+    const int bm = (block_rows == 128 || (block_rows == 0 && total_rows >= 128 * n_requests)) ? 128 : 64;
+#define LAUNCH(HD, BM)                                                                                                  \
     {                                                                                                                   \
+        dim3 grid((total_rows + BM - 1) / BM + n_requests, n_heads);                                                    \
+        size_t smem = (size_t)(BM + 4 * BN) * HD * sizeof(__nv_bfloat16);                                               \
         static bool configured = false;                                                                                 \
         if (!configured) {                                                                                              \
-            cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<HD, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e;                                                                        \
             configured = true;                                                                                          \
         }                                                                                                               \
-        prefill_attention_kernel<HD><<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,     \
+        prefill_attention_kernel<HD, BM><<<grid, BM * 2, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,  \
             (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane, req_start, req_prior, n_requests, table,        \
             table_stride, page_tokens, n_heads, n_kv, window, scale_log2);                                              \
     }
-    if (hd == 128) LAUNCH(128) else LAUNCH(64)
+    if (hd == 128) { if (bm == 128) LAUNCH(128, 128) else LAUNCH(128, 64) }
+    else { if (bm == 128) LAUNCH(64, 128) else LAUNCH(64, 64) }
 #undef LAUNCH
     return launch_status();
 }

@@ -371,7 +371,7 @@ class DecodeScratch:
 
 def prefill_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
                       req_start: torch.Tensor, req_prior: torch.Tensor, table: torch.Tensor, page_tokens: int,
-                      n_heads: int, n_kv: int, head_dim: int, window: int, scale: float) -> None:
+                      n_heads: int, n_kv: int, head_dim: int, window: int, scale: float, block_rows: int = 0) -> None:
     """Tensor-core attention of a step's rows (request r owns rows req_start[r]..req_start[r+1]
     at positions req_prior[r] + i) over the paged cache; bfloat16, head_dim 64 or 128."""
     for n, t in (("q", q), ("out", out), ("k_plane", k_plane), ("v_plane", v_plane)):
@@ -380,5 +380,5 @@ def prefill_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor,
     st = library("attention_prefill").cj_prefill_attention(
         _ptr(q), _ptr(out), _ptr(k_plane), _ptr(v_plane), _ptr(req_start), _ptr(req_prior), _i(req_prior.numel()),
         _i(q.shape[0]), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(n_heads), _i(n_kv), _i(head_dim), _i(window),
-        _f(scale), _stream())
+        _f(scale), _i(block_rows), _stream())
     _check(st, "prefill_attention")

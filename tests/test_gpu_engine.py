@@ -219,3 +219,36 @@ def test_captured_decode_steps_give_the_same_logits_as_uncaptured_ones(model_dir
     margins = torch.cat([torch.stack([helpers.plain_margins(model_dirs["M"], t)[i] for t in seqs]) for i in range(7, 23)]
                         + [helpers.plain_margins(model_dirs["M"], seqs[0])[23:31]])
     helpers.assert_close(outs[True], want, "bfloat16", "captured decode", margins)
+
+
+def test_real_layer_sizes_match_the_plain_implementation(tmp_path):
+    """Layers of the benchmark's sizes (fewer of them): a prompt in one step, in portions
+    beside another request's decode tokens, and token by token, in float32 and bfloat16."""
+    from cajeta_llm_b200.engine.step import StepEntry
+    d = str(tmp_path)
+    helpers.write_model(d, helpers.REAL_SIZES, seed=77)
+    vocab = helpers.REAL_SIZES["vocab_size"]
+    a = helpers.random_tokens(vocab, 150, seed=1)
+    b = helpers.random_tokens(vocab, 40, seed=2)
+    want_a, want_b = helpers.plain_logits(d, a), helpers.plain_logits(d, b)
+    m_a, m_b = helpers.plain_margins(d, a), helpers.plain_margins(d, b)
+    for dtype in ("float32", "bfloat16"):
+        r = runner_for(d, dtype, page_tokens=16, max_seqs=2, max_tokens_per_seq=256)
+        sa, sb = r.admit(), r.admit()
+        got_a = [r.step([StepEntry(sa, a[:97], list(range(97)))])]                       # a long portion alone
+        got_b = [r.step([StepEntry(sb, b[:30], list(range(30)))])]
+        for i in range(30, 40):                                                            # b decodes beside a's portions
+            n = 5 if i < 39 else 8
+            lo = 97 + (i - 30) * 5
+            out = r.step([StepEntry(sb, [b[i]], [0]), StepEntry(sa, a[lo:lo + n], list(range(n)))])
+            got_b.append(out[:1])
+            got_a.append(out[1:])
+        r.release(sb)
+        assert 97 + 9 * 5 + 8 == 150
+        helpers.assert_close(torch.cat(got_b).cpu(), want_b, dtype, f"real sizes {dtype} b", m_b)
+        helpers.assert_close(torch.cat(got_a).cpu(), want_a, dtype, f"real sizes {dtype} a", m_a)
+        # and a pure decode tail (captured as a graph on the bfloat16 path)
+        sc = r.admit()
+        r.step([StepEntry(sc, b[:20], [])])
+        tail = torch.cat([r.step([StepEntry(sc, [t], [0])]) for t in b[20:]]).cpu()
+        helpers.assert_close(tail, want_b[20:], dtype, f"real sizes {dtype} decode", m_b[20:])

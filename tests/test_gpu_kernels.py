@@ -402,8 +402,9 @@ def test_decode_attention_split_kv(K, heads, n_kv, hd, page, window):
     assert torch.equal(out1[0], outs[0][3])
 
 
+@pytest.mark.parametrize("block_rows", [64, 128])
 @pytest.mark.parametrize("heads,n_kv,hd,page,window", [(4, 4, 128, 16, 0), (6, 2, 64, 16, 0), (8, 1, 128, 8, 70), (4, 2, 64, 16, 17)])
-def test_prefill_attention_tiles(K, heads, n_kv, hd, page, window):
+def test_prefill_attention_tiles(K, heads, n_kv, hd, page, window, block_rows):
     """Requests with and without earlier tokens, portions that end inside a tile, a single
     token riding along; every row against the plain attention."""
     dtype = torch.bfloat16
@@ -419,7 +420,8 @@ def test_prefill_attention_tiles(K, heads, n_kv, hd, page, window):
     out = torch.full_like(q, 5.0)
     scale = 1.0 / math.sqrt(hd)
     K.prefill_attention(q, out, kp, vp, torch.tensor(starts, dtype=torch.int32, device=DEV),
-                        torch.tensor(prior, dtype=torch.int32, device=DEV), table, page, heads, n_kv, hd, window, scale)
+                        torch.tensor(prior, dtype=torch.int32, device=DEV), table, page, heads, n_kv, hd, window, scale,
+                        block_rows=block_rows)
     for r, (T, n) in enumerate(zip(totals, new)):
         qq = torch.zeros(T, heads, hd, dtype=torch.float64)
         qq[T - n:] = q[starts[r]:starts[r + 1]].double().cpu()

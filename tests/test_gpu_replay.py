@@ -135,8 +135,8 @@ def test_replay_every_way_of_cutting_matches_the_plain_implementation(name, dtyp
         helpers.assert_close(got, want, dtype, f"{name} {dtype} step {s['step']} rows {rows[:4]}...", margins)
         worst = max(worst, float((got - want).abs().max()))
     tied = helpers.near_tie_rows
-    print(f"\n{name} {dtype}: {len(tb.steps)} steps, worst |diff| {worst:.3e}; near-tie rows so far {tied['seen']} of {tied['rows']}")
-    assert tied["seen"] <= 0.2 * max(1, tied["rows"])          # the allowance stays the exception
+    print(f"\n{name} {dtype}: {len(tb.steps)} steps, worst |diff| {worst:.3e}; rows excused as routing near-ties so far {tied['seen']} of {tied['rows']}")
+    assert tied["seen"] <= 0.02 * max(1, tied["rows"])         # the allowance stays the exception
 
 
 def test_replay_writes_nothing_when_nothing_is_wanted_and_reuses_ids(model_dirs, tmp_path):
