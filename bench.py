@@ -42,6 +42,16 @@ A27B = {
     "norm_topk_prob": False, "decoder_sparse_step": 1, "mlp_only_layers": [], "tie_word_embeddings": False,
     "use_sliding_window": False,
 }
+# BASELINE.json configs[3]: Qwen2-57B-A14B sizes (about 115 GB of bf16 weights); not the default run
+Q57B = {
+    "architectures": ["Qwen2MoeForCausalLM"], "hidden_size": 3584, "intermediate_size": 18944, "num_hidden_layers": 28,
+    "num_attention_heads": 28, "num_key_value_heads": 4, "head_dim": 128, "vocab_size": 151936,
+    "max_position_embeddings": 8192, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "num_experts": 64,
+    "num_experts_per_tok": 8, "moe_intermediate_size": 2560, "shared_expert_intermediate_size": 20480,
+    "norm_topk_prob": False, "decoder_sparse_step": 1, "mlp_only_layers": [], "tie_word_embeddings": False,
+    "use_sliding_window": False,
+}
+MODELS = {"a2.7b": ("Qwen1.5-MoE-A2.7B sizes", A27B), "57b-a14b": ("Qwen2-57B-A14B sizes", Q57B)}
 CTX, PROMPT, PAGE, BATCH, PREFILL_TOKENS = 4096, 512, 16, 8, 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
@@ -130,6 +140,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
     ap.add_argument("--quick", action="store_true", help="skip the batch-1/64 points and the end-to-end arm")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profilers)")
+    ap.add_argument("--model", default="a2.7b", choices=sorted(MODELS), help="layer sizes (default: the headline configuration)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -153,7 +164,8 @@ def main() -> int:
     from cajeta_llm_b200.engine.step import StepEntry
     from cajeta_llm_b200.sampling.params import SamplingParams
 
-    cfg = dict(A27B)
+    model_name, model_cfg = MODELS[args.model]
+    cfg = dict(model_cfg)
     full_layers = cfg["num_hidden_layers"]
     if args.layers > 0:
         cfg["num_hidden_layers"] = min(args.layers, full_layers)
@@ -275,12 +287,12 @@ def main() -> int:
         e2e = {"value": made / dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * BATCH}
 
     line = {
-        "metric": "decode tokens/s at batch 8 (Qwen1.5-MoE-A2.7B sizes, bf16, random weights)",
+        "metric": f"decode tokens/s at batch 8 ({model_name}, bf16, random weights)",
         "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
         "config": {
-            "model": "Qwen1.5-MoE-A2.7B sizes", "global_batch": BATCH, "seq_len": CTX, "prompt_len": PROMPT,
+            "model": model_name, "global_batch": BATCH, "seq_len": CTX, "prompt_len": PROMPT,
             "parallelism": "single GPU", "layers": n_layers, "layers_in_config": full_layers, "hidden": cfg["hidden_size"],
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "experts": cfg["num_experts"], "top_k": cfg["num_experts_per_tok"], "moe_inter": cfg["moe_intermediate_size"],

@@ -78,6 +78,7 @@ class StepContext:
     max_rows_per_request: int = 0
     max_context: int = 0           # longest prior + new over the step's requests
     all_single: bool = False       # every request brings exactly one token
+    decode_scratch: Optional[object] = None    # scratch of the split-KV decode attention for this step (None: the runtime's)
 
 
 @dataclass
@@ -88,6 +89,7 @@ class _CapturedStep:
     meta: torch.Tensor          # static device metadata the captured kernels read
     logits: torch.Tensor        # static output [batch, vocab]
     launches: int               # kernels the graph replays
+    scratch: object             # kernel scratch the graph's kernels point into; lives as long as the graph
 
 
 GRAPH_CONTEXT_BUCKET = 1024     # captured decode steps are keyed by the context rounded up to this
@@ -177,7 +179,10 @@ class ModelRunner:
             meta = torch.empty(host.shape, dtype=torch.int32, device=self.runtime.device)
             meta.copy_(host, non_blocking=True)
             ctx = self._context(meta, layout, all_rows, max_context=bucket)
-            logits = self._forward(ctx)                      # this step's result, uncaptured
+            # the captured kernels keep raw pointers: their scratch must belong to this graph
+            # alone and never be reallocated while the graph lives
+            ctx.decode_scratch = K.DecodeScratch()
+            logits = self._forward(ctx)                      # this step's result, uncaptured (sizes the scratch)
             torch.cuda.synchronize()
             before = K.launches
             graph = torch.cuda.CUDAGraph()
@@ -185,7 +190,7 @@ class ModelRunner:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 static_logits = self._forward(ctx)
-            self._graphs[key] = _CapturedStep(graph, meta, static_logits, K.launches - before)
+            self._graphs[key] = _CapturedStep(graph, meta, static_logits, K.launches - before, ctx.decode_scratch)
         else:
             cap.meta.copy_(host, non_blocking=True)
             cap.graph.replay()

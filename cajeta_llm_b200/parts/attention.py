@@ -104,7 +104,7 @@ class PagedAttention(Part):
             # every request brings one token: the split-KV decode kernel
             K.decode_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
                                entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale,
-                               ctx.max_context, rt.decode_scratch)
+                               ctx.max_context, getattr(ctx, "decode_scratch", None) or rt.decode_scratch)
         elif rt.fast_kernels and self.head_dim in (64, 128) and hasattr(ctx, "req_start"):
             # portions of prompts (and whatever single tokens ride along): query tiles on the tensor cores
             K.prefill_attention(q, out, entry.k_plane, entry.v_plane, ctx.req_start, ctx.req_prior, entry.block_table,

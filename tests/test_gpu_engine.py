@@ -203,7 +203,11 @@ def test_captured_decode_steps_give_the_same_logits_as_uncaptured_ones(model_dir
     for graphs in (False, True):
         r = runner_for(model_dirs["M"], "bfloat16", page_tokens=16, max_seqs=4, max_tokens_per_seq=64, cuda_graphs=graphs)
         slots = [r.admit() for _ in seqs]
-        r.step([StepEntry(s, t[:7], []) for s, t in zip(slots, seqs)])
+        r.step([StepEntry(s, t[:6], []) for s, t in zip(slots, seqs)])
+        # one step of two rows first: its graph is captured before the wider ones, whose
+        # larger scratch must not move anything the first graph points to
+        r.step([StepEntry(slots[0], [seqs[0][6]], []), StepEntry(slots[2], [seqs[2][6]], [])])
+        r.step([StepEntry(slots[1], [seqs[1][6]], [])])
         got = []
         for i in range(7, 23):                       # three rows at a time
             got.append(r.step([StepEntry(s, [t[i]], [0]) for s, t in zip(slots, seqs)]).clone())
