@@ -18,7 +18,6 @@ using namespace cj;
 
 namespace {
 
-constexpr int BN = 64;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -55,8 +54,11 @@ __device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat16* base, int row,
     return base + row * HD + chunk * 8 + (col & 7);
 }
 
-template <int HD, int BM>
-__global__ void __launch_bounds__(BM * 2) prefill_attention_kernel(
+// HD: head size; BM: query rows a block; BN: keys a tile; MT: 16-row tiles a warp owns.  A
+// warp that owns two row tiles uses every key/value fragment it reads from shared memory
+// twice, which is what the legacy tensor path needs to stay ahead of shared-memory bandwidth.
+template <int HD, int BM, int BN, int MT>
+__global__ void __launch_bounds__(BM / (16 * MT) * 32) prefill_attention_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ kplane,
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ req_start, const int* __restrict__ req_prior,
     int n_requests, const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int window,
@@ -66,7 +68,7 @@ __global__ void __launch_bounds__(BM * 2) prefill_attention_kernel(
     __nv_bfloat16* ks = qs + BM * HD;                             // [2][BN][HD]
     __nv_bfloat16* vs = ks + 2 * BN * HD;                         // [2][BN][HD]
     constexpr int CH = HD / 8;                                    // 16-byte chunks per row
-    constexpr int THREADS = BM * 2;                               // one warp per 16 query rows
+    constexpr int THREADS = BM / (16 * MT) * 32;
 
     // ---- which request and which BM-row tile of it --------------------------------------
     // the grid walks the tiles from the last to the first: in a causal prompt the late tiles
@@ -120,15 +122,18 @@ __global__ void __launch_bounds__(BM * 2) prefill_attention_kernel(
     load_kv(kt_begin, 0);
     cp_async_commit();
 
-    // ---- per-warp state: 16 query rows, output accumulator, running max and sum --------------
+    // ---- per-warp state: MT tiles of 16 query rows; output accumulators, running max and sum ----
     const int g = lane >> 2, t4 = lane & 3;
-    const int wrow = warp * 16;
-    unsigned qf[HD / 16][4];
-    float o[HD / 8][4];
+    const int wrow = warp * 16 * MT;
+    float o[MT][HD / 8][4];
+    float mrun[MT][2], lrun[MT][2];                              // rows g and g + 8 of each tile
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;      // rows g and g + 8 of the warp's 16
-    const int pos0 = p0 + wrow + g, pos1 = pos0 + 8;
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.0f;
+        mrun[mt][0] = mrun[mt][1] = -INFINITY;
+        lrun[mt][0] = lrun[mt][1] = 0.0f;
+    }
 
     for (int kt = kt_begin; kt <= kt_end; ++kt) {
         const int buf = (kt - kt_begin) & 1;
@@ -136,76 +141,84 @@ __global__ void __launch_bounds__(BM * 2) prefill_attention_kernel(
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        if (kt == kt_begin) {
-#pragma unroll
-            for (int kk = 0; kk < HD / 16; ++kk)
-                ldmatrix_x4(qf[kk], tile_ptr<HD>(qs, wrow + (lane & 15), kk * 16 + (lane >> 4) * 8));
-        }
         const __nv_bfloat16* kb = ks + buf * BN * HD;
         const __nv_bfloat16* vb = vs + buf * BN * HD;
 
-        // scores of 16 rows x 64 keys
-        float s[BN / 8][4];
+        // scores of MT x 16 rows x BN keys; the query fragments come from shared memory
+        float s[MT][BN / 8][4];
 #pragma unroll
-        for (int j = 0; j < BN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int j = 0; j < BN / 8; ++j) s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.0f;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
+            unsigned qf[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+                ldmatrix_x4(qf[mt], tile_ptr<HD>(qs, wrow + mt * 16 + (lane & 15), kk * 16 + (lane >> 4) * 8));
 #pragma unroll
             for (int jp = 0; jp < BN / 16; ++jp) {
                 unsigned b[4];
                 int mi = lane >> 3;
                 ldmatrix_x4(b, tile_ptr<HD>((__nv_bfloat16*)kb, jp * 16 + (mi >> 1) * 8 + (lane & 7), kk * 16 + (mi & 1) * 8));
-                mma_bf16(s[2 * jp], qf[kk], b[0], b[1]);
-                mma_bf16(s[2 * jp + 1], qf[kk], b[2], b[3]);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma_bf16(s[mt][2 * jp], qf[mt], b[0], b[1]);
+                    mma_bf16(s[mt][2 * jp + 1], qf[mt], b[2], b[3]);
+                }
             }
         }
         // mask and running softmax
         const int kbase = kt * BN;
-        const int from0 = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
-        const int from1 = (window > 0 && pos1 + 1 > window) ? pos1 + 1 - window : 0;
-        float mx0 = m0, mx1 = m1;
+        unsigned pf[MT][BN / 16][4];
 #pragma unroll
-        for (int j = 0; j < BN / 8; ++j) {
+        for (int mt = 0; mt < MT; ++mt) {
+            const int pos0 = p0 + wrow + mt * 16 + g, pos1 = pos0 + 8;
+            const int from0 = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+            const int from1 = (window > 0 && pos1 + 1 > window) ? pos1 + 1 - window : 0;
+            float mx0 = mrun[mt][0], mx1 = mrun[mt][1];
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                int key = kbase + j * 8 + 2 * t4 + e;
-                float a = (key <= pos0 && key >= from0) ? s[j][e] * scale_log2 : -INFINITY;
-                float b = (key <= pos1 && key >= from1) ? s[j][2 + e] * scale_log2 : -INFINITY;
-                s[j][e] = a;
-                s[j][2 + e] = b;
-                mx0 = fmaxf(mx0, a);
-                mx1 = fmaxf(mx1, b);
+            for (int j = 0; j < BN / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    int key = kbase + j * 8 + 2 * t4 + e;
+                    float a = (key <= pos0 && key >= from0) ? s[mt][j][e] * scale_log2 : -INFINITY;
+                    float b = (key <= pos1 && key >= from1) ? s[mt][j][2 + e] * scale_log2 : -INFINITY;
+                    s[mt][j][e] = a;
+                    s[mt][j][2 + e] = b;
+                    mx0 = fmaxf(mx0, a);
+                    mx1 = fmaxf(mx1, b);
+                }
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            // a row that has seen no key yet (rows past the tile's end, or keys all masked so far) keeps -inf
+            const float c0 = mx0 == -INFINITY ? 1.0f : exp2f(mrun[mt][0] - mx0);
+            const float c1 = mx1 == -INFINITY ? 1.0f : exp2f(mrun[mt][1] - mx1);
+            const float sub0 = mx0 == -INFINITY ? 0.0f : mx0, sub1 = mx1 == -INFINITY ? 0.0f : mx1;
+            float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < BN / 8; ++j) {
+                float e0 = exp2f(s[mt][j][0] - sub0), e1 = exp2f(s[mt][j][1] - sub0);
+                float e2 = exp2f(s[mt][j][2] - sub1), e3 = exp2f(s[mt][j][3] - sub1);
+                sum0 += e0 + e1;
+                sum1 += e2 + e3;
+                pf[mt][j >> 1][(j & 1) * 2] = pack_bf16(e0, e1);
+                pf[mt][j >> 1][(j & 1) * 2 + 1] = pack_bf16(e2, e3);
+            }
+            lrun[mt][0] = lrun[mt][0] * c0 + sum0;
+            lrun[mt][1] = lrun[mt][1] * c1 + sum1;
+            mrun[mt][0] = mx0;
+            mrun[mt][1] = mx1;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) {
+                o[mt][i][0] *= c0; o[mt][i][1] *= c0;
+                o[mt][i][2] *= c1; o[mt][i][3] *= c1;
             }
         }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        // a row that has seen no key yet (rows past the tile's end, or keys all masked so far) keeps -inf
-        const float c0 = mx0 == -INFINITY ? 1.0f : exp2f(m0 - mx0);
-        const float c1 = mx1 == -INFINITY ? 1.0f : exp2f(m1 - mx1);
-        const float sub0 = mx0 == -INFINITY ? 0.0f : mx0, sub1 = mx1 == -INFINITY ? 0.0f : mx1;
-        float sum0 = 0.0f, sum1 = 0.0f;
-        unsigned pf[BN / 16][4];
-#pragma unroll
-        for (int j = 0; j < BN / 8; ++j) {
-            float e0 = exp2f(s[j][0] - sub0), e1 = exp2f(s[j][1] - sub0);
-            float e2 = exp2f(s[j][2] - sub1), e3 = exp2f(s[j][3] - sub1);
-            sum0 += e0 + e1;
-            sum1 += e2 + e3;
-            pf[j >> 1][(j & 1) * 2] = pack_bf16(e0, e1);
-            pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(e2, e3);
-        }
-        l0 = l0 * c0 + sum0;
-        l1 = l1 * c1 + sum1;
-        m0 = mx0;
-        m1 = mx1;
-#pragma unroll
-        for (int i = 0; i < HD / 8; ++i) {
-            o[i][0] *= c0; o[i][1] *= c0;
-            o[i][2] *= c1; o[i][3] *= c1;
-        }
-        // weighted values: 16 rows x HD += P[16 x 64] . V[64 x HD]
+        // weighted values: MT x 16 rows x HD += P[16 x BN] . V[BN x HD]
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
 #pragma unroll
@@ -213,25 +226,32 @@ __global__ void __launch_bounds__(BM * 2) prefill_attention_kernel(
                 unsigned b[4];
                 int mi = lane >> 3;
                 ldmatrix_x4_trans(b, tile_ptr<HD>((__nv_bfloat16*)vb, kk * 16 + (mi & 1) * 8 + (lane & 7), dp * 16 + (mi >> 1) * 8));
-                mma_bf16(o[2 * dp], pf[kk], b[0], b[1]);
-                mma_bf16(o[2 * dp + 1], pf[kk], b[2], b[3]);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma_bf16(o[mt][2 * dp], pf[mt][kk], b[0], b[1]);
+                    mma_bf16(o[mt][2 * dp + 1], pf[mt][kk], b[2], b[3]);
+                }
             }
         }
         __syncthreads();                      // everyone is done with this buffer before it is refilled
     }
 
     // ---- finish: divide by the sum of the whole row (the quad holds the row) -------------------
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float i0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, i1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
-    const int r0 = wrow + g, r1 = r0 + 8;
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) {
-        int col = i * 8 + 2 * t4;
-        if (r0 < rows) *(unsigned*)(out + ((size_t)(row0 + r0) * n_heads + h) * HD + col) = pack_bf16(o[i][0] * i0, o[i][1] * i0);
-        if (r1 < rows) *(unsigned*)(out + ((size_t)(row0 + r1) * n_heads + h) * HD + col) = pack_bf16(o[i][2] * i1, o[i][3] * i1);
+    for (int mt = 0; mt < MT; ++mt) {
+        float l0 = lrun[mt][0], l1 = lrun[mt][1];
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        const float i0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, i1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+        const int r0 = wrow + mt * 16 + g, r1 = r0 + 8;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            int col = i * 8 + 2 * t4;
+            if (r0 < rows) *(unsigned*)(out + ((size_t)(row0 + r0) * n_heads + h) * HD + col) = pack_bf16(o[mt][i][0] * i0, o[mt][i][1] * i0);
+            if (r1 < rows) *(unsigned*)(out + ((size_t)(row0 + r1) * n_heads + h) * HD + col) = pack_bf16(o[mt][i][2] * i1, o[mt][i][3] * i1);
+        }
     }
 }
 
@@ -249,24 +269,24 @@ CJ_EXPORT int cj_prefill_attention(const void* q, void* out, const void* kplane,
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || page_tokens <= 0 || n_heads > 65535) return CJ_ERR_SIZE;
     if (hd != 64 && hd != 128) return CJ_ERR_SIZE;
     float scale_log2 = scale * 1.4426950408889634f;
-    // query tile: 128 rows when the step is mostly long portions, 64 otherwise
+    // long portions: 128 query rows a block, every warp two row tiles; short ones: 64 rows, one tile a warp
     const int bm = (block_rows == 128 || (block_rows == 0 && total_rows >= 128 * n_requests)) ? 128 : 64;
-#define LAUNCH(HD, BM)                                                                                                  \
+#define LAUNCH(HD, BM, BN, MT)                                                                                          \
     {                                                                                                                   \
         dim3 grid((total_rows + BM - 1) / BM + n_requests, n_heads);                                                    \
         size_t smem = (size_t)(BM + 4 * BN) * HD * sizeof(__nv_bfloat16);                                               \
         static bool configured = false;                                                                                 \
         if (!configured) {                                                                                              \
-            cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<HD, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<HD, BM, BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e;                                                                        \
             configured = true;                                                                                          \
         }                                                                                                               \
-        prefill_attention_kernel<HD, BM><<<grid, BM * 2, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,  \
-            (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane, req_start, req_prior, n_requests, table,        \
-            table_stride, page_tokens, n_heads, n_kv, window, scale_log2);                                              \
+        prefill_attention_kernel<HD, BM, BN, MT><<<grid, BM / (16 * MT) * 32, smem, stream>>>(                          \
+            (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane,   \
+            req_start, req_prior, n_requests, table, table_stride, page_tokens, n_heads, n_kv, window, scale_log2);     \
     }
-    if (hd == 128) { if (bm == 128) LAUNCH(128, 128) else LAUNCH(128, 64) }
-    else { if (bm == 128) LAUNCH(64, 128) else LAUNCH(64, 64) }
+    if (hd == 128) { if (bm == 128) LAUNCH(128, 128, 32, 2) else LAUNCH(128, 64, 64, 1) }
+    else { if (bm == 128) LAUNCH(64, 128, 64, 2) else LAUNCH(64, 64, 64, 1) }
 #undef LAUNCH
     return launch_status();
 }
