@@ -38,6 +38,7 @@ LIBRARIES: Dict[str, str] = {
     "gemm_tc": "gemm_tc.cu",
     "attention_decode": "attention_decode.cu",
     "attention_prefill": "attention_prefill.cu",
+    "attention_prefill_tc": "attention_prefill_tc.cu",
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "sampling_static.h"]
 
@@ -103,6 +104,18 @@ def _writable_dir() -> str:
 _lock = threading.Lock()
 
 
+def _drop_stale(folder: str, name: str, keep: str) -> None:
+    """Remove builds of ``name`` from other source versions; a library in use elsewhere stays
+    mapped in that process, so this cannot break a running engine."""
+    prefix = _file_name(name).rsplit("-", 1)[0] + "-"
+    try:
+        for f in os.listdir(folder):
+            if f.startswith(prefix) and f.endswith(".so") and f != keep:
+                os.remove(os.path.join(folder, f))
+    except OSError:
+        pass
+
+
 def build(name: str, verbose: bool = True) -> str:
     """Path of the built library ``name``; compiles it when no matching build exists."""
     if name not in LIBRARIES:
@@ -145,6 +158,7 @@ def build(name: str, verbose: bool = True) -> str:
                 pass
             raise BuildError(f"nvcc failed for {LIBRARIES[name]}:\n{proc.stdout}")
         os.replace(tmp, out)
+        _drop_stale(out_dir, name, os.path.basename(out))
         if verbose:
             print(f"[cajeta_llm_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
                   file=sys.stderr, flush=True)

@@ -382,3 +382,39 @@ def prefill_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor,
         _i(q.shape[0]), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(n_heads), _i(n_kv), _i(head_dim), _i(window),
         _f(scale), _i(block_rows), _stream())
     _check(st, "prefill_attention")
+
+
+def prefill_attention_tc(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+                         req_start: torch.Tensor, req_prior: torch.Tensor, table: torch.Tensor, page_tokens: int,
+                         n_heads: int, n_kv: int, head_dim: int, window: int, scale: float) -> None:
+    """The same contract as ``prefill_attention`` on the tcgen05 tensor cores: both products
+    from shared memory into tensor memory, 128 query rows a block.  Head size 128 and pages
+    of 16 tokens only; anything else is refused."""
+    for n, t in (("q", q), ("out", out), ("k_plane", k_plane), ("v_plane", v_plane)):
+        _need(t, n, torch.bfloat16)
+    _need(req_start, "req_start", torch.int32), _need(req_prior, "req_prior", torch.int32), _need(table, "table", torch.int32)
+    if head_dim != 128 or page_tokens != 16:
+        raise KernelError(f"prefill_attention_tc takes head size 128 and 16-token pages, not {head_dim} and {page_tokens}")
+    st = library("attention_prefill_tc").cj_prefill_attention_tc(
+        _ptr(q), _ptr(out), _ptr(k_plane), _ptr(v_plane), _i(k_plane.shape[0]), _ptr(req_start), _ptr(req_prior),
+        _i(req_prior.numel()), _i(q.shape[0]), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(n_heads), _i(n_kv),
+        _i(head_dim), _i(window), _f(scale), _stream())
+    _check(st, "prefill_attention_tc")
+
+
+def prefill_attention_tc_error() -> int:
+    """0, or the code of a bounded wait inside the tensor-core attention that ran out of time."""
+    return int(library("attention_prefill_tc").cj_prefill_attention_tc_error())
+
+
+def wait_errors() -> Dict[str, int]:
+    """Codes of bounded waits that ran out inside the tensor-core kernels, by library; empty
+    when all is well.  Only libraries that are already loaded are asked."""
+    found = {}
+    for name, symbol in (("gemm_tc", "cj_gemm_tc_error"), ("attention_prefill_tc", "cj_prefill_attention_tc_error")):
+        lib = _libs.get(name)
+        if lib is not None:
+            code = int(getattr(lib, symbol)())
+            if code != 0:
+                found[name] = code
+    return found

@@ -93,6 +93,7 @@ class _CapturedStep:
 
 
 GRAPH_CONTEXT_BUCKET = 1024     # captured decode steps are keyed by the context rounded up to this
+WAIT_CHECK_EVERY = 64           # steps between looks at the kernels' wait-error flags
 
 
 class ModelRunner:
@@ -137,6 +138,9 @@ class ModelRunner:
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.runtime.device)
+        self._calls = getattr(self, "_calls", 0) + 1
+        if self._calls % WAIT_CHECK_EVERY == 0:
+            self.check_waits()
         if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and not self.cache.state:
             return self._step_captured(entries)
         ctx = self._prepare(entries)
@@ -145,6 +149,15 @@ class ModelRunner:
             self.cache.commit(e.slot, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def check_waits(self) -> None:
+        """Every wait inside the tensor-core kernels is bounded; one that ran out left a code
+        behind and its step's result is not to be trusted.  Asked now and then, not every
+        step: it reads from the device."""
+        from ..csrc import kernels as K
+        bad = K.wait_errors()
+        if bad:
+            raise StepError(f"a bounded wait inside a tensor-core kernel ran out of time: {bad}")
 
     def _forward(self, ctx: StepContext) -> torch.Tensor:
         """Embedding, every schedule entry, then final norm and head on the wanted rows."""

@@ -105,8 +105,13 @@ class PagedAttention(Part):
             K.decode_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
                                entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale,
                                ctx.max_context, getattr(ctx, "decode_scratch", None) or rt.decode_scratch)
+        elif rt.fast_kernels and self.head_dim == 128 and entry.page_tokens == 16 and hasattr(ctx, "req_start"):
+            # portions of prompts (and whatever single tokens ride along): both products on tcgen05,
+            # scores and output in tensor memory
+            K.prefill_attention_tc(q, out, entry.k_plane, entry.v_plane, ctx.req_start, ctx.req_prior, entry.block_table,
+                                   entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale)
         elif rt.fast_kernels and self.head_dim in (64, 128) and hasattr(ctx, "req_start"):
-            # portions of prompts (and whatever single tokens ride along): query tiles on the tensor cores
+            # other page sizes, head size 64: query tiles on mma.sync
             K.prefill_attention(q, out, entry.k_plane, entry.v_plane, ctx.req_start, ctx.req_prior, entry.block_table,
                                 entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale)
         else:

@@ -97,3 +97,53 @@ def test_refusals(K):
     x, w = rnd(4, 64, seed=14), rnd(8, 64, seed=15)
     with pytest.raises(K.KernelError, match="size"):
         K.gemm_tc(x, w, out, K.EPI_STORE_F32, True, 24)
+
+
+@pytest.mark.parametrize("heads,n_kv,window", [(4, 4, 0), (6, 2, 0), (8, 1, 150), (4, 2, 40), (2, 2, 128)])
+def test_prefill_attention_tcgen05(K, heads, n_kv, window):
+    """Both attention products on tcgen05: requests with and without earlier tokens, portions
+    that end inside a tile, a single token riding along, several key tiles (so the running
+    maximum moves and the output is rescaled), a window that starts inside a tile; every
+    row against the plain attention.  One far key is made to stand out for the last rows."""
+    from test_gpu_kernels import paged_setup
+    import math
+    dtype, hd, page = torch.bfloat16, 128, 16
+    totals = [700, 64, 131, 300, 513]
+    new = [700, 1, 67, 130, 257]                      # rows this step brings; the rest is already cached
+    kp, vp, table, ks, vs = paged_setup(totals, n_kv, hd, page, dtype, seed=190)
+    # stale data in a page's unused tail must not reach the result
+    tail = totals[2] % page
+    kp[table[2, totals[2] // page].item(), :, tail:] = 3.0
+    vp[table[2, totals[2] // page].item(), :, tail:] = 100.0
+    starts = [0]
+    for n in new:
+        starts.append(starts[-1] + n)
+    prior = [t - n for t, n in zip(totals, new)]
+    g = torch.Generator().manual_seed(191)
+    q = torch.randn(starts[-1], heads, hd, generator=g)
+    # the last 40 rows of request 0 look hard at key 5 (far behind, in the first tile)
+    kdir = ks[0][5].to(dtype).float()                  # [n_kv, hd]
+    for h in range(heads):
+        q[starts[1] - 40:starts[1], h] = 6.0 * kdir[h // (heads // n_kv)] / kdir[h // (heads // n_kv)].norm() * math.sqrt(hd) / 4
+    q = q.to(dtype).to(DEV)
+    out = torch.full_like(q, 5.0)
+    scale = 1.0 / math.sqrt(hd)
+    for _ in range(2):
+        K.prefill_attention_tc(q, out, kp, vp, torch.tensor(starts, dtype=torch.int32, device=DEV),
+                               torch.tensor(prior, dtype=torch.int32, device=DEV), table, page, heads, n_kv, hd, window, scale)
+    torch.cuda.synchronize()
+    assert K.prefill_attention_tc_error() == 0
+    for r, (T, n) in enumerate(zip(totals, new)):
+        qq = torch.zeros(T, heads, hd, dtype=torch.float64)
+        qq[T - n:] = q[starts[r]:starts[r + 1]].double().cpu()
+        want = P.attention(qq, ks[r].to(dtype).double(), vs[r].to(dtype).double(), window, scale)[T - n:]
+        got = out[starts[r]:starts[r + 1]].double().cpu()
+        assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), (r, float((got - want).abs().max()))
+
+
+def test_prefill_attention_tcgen05_refuses(K):
+    q = torch.zeros(4, 2, 64, dtype=torch.bfloat16, device=DEV)
+    kp = torch.zeros(2, 2, 16, 64, dtype=torch.bfloat16, device=DEV)
+    z = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(K.KernelError):
+        K.prefill_attention_tc(q, q.clone(), kp, kp, z, z[:1], z.view(1, 2), 16, 2, 2, 64, 0, 1.0)
