@@ -44,7 +44,7 @@ constexpr int SMEM_Q = 0;
 constexpr int SMEM_K = SMEM_Q + TILE_BYTES;
 constexpr int SMEM_V = SMEM_K + KV_STAGES * TILE_BYTES;
 constexpr int SMEM_P = SMEM_V + KV_STAGES * TILE_BYTES;
-constexpr int SMEM_BAR = SMEM_P + TILE_BYTES;
+constexpr int SMEM_BAR = SMEM_P + 2 * TILE_BYTES;       // two P tiles: tile i + 1 is written while the product reads tile i
 constexpr int SMEM_TOTAL = SMEM_BAR + 256 + 1024;
 
 // tensor memory columns: S0 | S1 | O
@@ -77,6 +77,29 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ float ex2(float x) {       // 2^x, 0 for -inf
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// 32 consecutive 32-bit columns of this thread's lane into v[OFF .. OFF + 31]
+template <int OFF>
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[128]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[OFF + 0]), "=r"(v[OFF + 1]), "=r"(v[OFF + 2]), "=r"(v[OFF + 3]), "=r"(v[OFF + 4]), "=r"(v[OFF + 5]),
+          "=r"(v[OFF + 6]), "=r"(v[OFF + 7]), "=r"(v[OFF + 8]), "=r"(v[OFF + 9]), "=r"(v[OFF + 10]), "=r"(v[OFF + 11]),
+          "=r"(v[OFF + 12]), "=r"(v[OFF + 13]), "=r"(v[OFF + 14]), "=r"(v[OFF + 15]), "=r"(v[OFF + 16]), "=r"(v[OFF + 17]),
+          "=r"(v[OFF + 18]), "=r"(v[OFF + 19]), "=r"(v[OFF + 20]), "=r"(v[OFF + 21]), "=r"(v[OFF + 22]), "=r"(v[OFF + 23]),
+          "=r"(v[OFF + 24]), "=r"(v[OFF + 25]), "=r"(v[OFF + 26]), "=r"(v[OFF + 27]), "=r"(v[OFF + 28]), "=r"(v[OFF + 29]),
+          "=r"(v[OFF + 30]), "=r"(v[OFF + 31])
+        : "r"(taddr)
+        : "memory");
+}
 
 struct Args {
     const __nv_bfloat16* q;
@@ -118,9 +141,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + SMEM_BAR);
     uint64_t* q_full = bars;                      // Q tile landed
-    uint64_t* kv_full = bars + 1;                 // [KV_STAGES] K and V of a tile landed
-    uint64_t* kv_empty = kv_full + KV_STAGES;     // [KV_STAGES] the products of a tile have read them
-    uint64_t* s_full = kv_empty + KV_STAGES;      // [2] score tile complete
+    uint64_t* k_full = bars + 1;                  // [KV_STAGES] K of a tile landed
+    uint64_t* k_empty = k_full + KV_STAGES;       // [KV_STAGES] the score product has read it
+    uint64_t* v_full = k_empty + KV_STAGES;       // [KV_STAGES] V of a tile landed
+    uint64_t* v_empty = v_full + KV_STAGES;       // [KV_STAGES] the output product has read it
+    uint64_t* s_full = v_empty + KV_STAGES;       // [2] score tile complete
     uint64_t* s_empty = s_full + 2;               // [2] softmax has read the score tile
     uint64_t* p_full = s_empty + 2;               // P written (and O rescaled): the PV product may go
     uint64_t* pv_done = p_full + 1;               // the PV product has read P and updated O
@@ -129,7 +154,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
+        }
         for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128); }
         mbar_init(p_full, 128);
         mbar_init(pv_done, 1);
@@ -152,24 +180,30 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_expect_tx(q_full, TILE_BYTES);
             tma_load_2d(smem + SMEM_Q, &map_q, q_full, h * HD, row0);
             tma_load_2d(smem + SMEM_Q + HALF_BYTES, &map_q, q_full, h * HD + 64, row0);
-            for (int i = 0; i < n_tiles; ++i) {
+            // K runs ahead of V, in the order the products want them: K0, K1, V0, K2, V1, ...
+            auto load_tile = [&](int i, bool values) -> bool {
                 const int s = i % KV_STAGES;
-                if (!mbar_wait(&kv_empty[s], ((i / KV_STAGES) & 1) ^ 1, 11)) break;
-                mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+                uint64_t* full = values ? &v_full[s] : &k_full[s];
+                if (!mbar_wait(values ? &v_empty[s] : &k_empty[s], ((i / KV_STAGES) & 1) ^ 1, 11)) return false;
+                mbar_expect_tx(full, TILE_BYTES);
                 const int key0 = (kt_begin + i) * BN;
-                uint8_t* kd = smem + SMEM_K + s * TILE_BYTES;
-                uint8_t* vd = smem + SMEM_V + s * TILE_BYTES;
+                uint8_t* dst = smem + (values ? SMEM_V : SMEM_K) + s * TILE_BYTES;
+                const CUtensorMap* map = values ? &map_v : &map_k;
                 for (int pg = 0; pg < BN / 16; ++pg) {
                     // one cache page (16 keys) at a time; page_tokens is 16 here
                     const int key = key0 + pg * 16;
                     int page = (key <= p_last && key + 15 >= key_from) ? tab[key / 16] : -1;
                     // a page that is not there is read past the end of the plane: zeros
                     const int row = page >= 0 ? (page * p.n_kv + kvh) * 16 : p.plane_rows;
-                    tma_load_2d(kd + pg * 16 * 128, &map_k, &kv_full[s], 0, row);
-                    tma_load_2d(kd + HALF_BYTES + pg * 16 * 128, &map_k, &kv_full[s], 64, row);
-                    tma_load_2d(vd + pg * 16 * 128, &map_v, &kv_full[s], 0, row);
-                    tma_load_2d(vd + HALF_BYTES + pg * 16 * 128, &map_v, &kv_full[s], 64, row);
+                    tma_load_2d(dst + pg * 16 * 128, map, full, 0, row);
+                    tma_load_2d(dst + HALF_BYTES + pg * 16 * 128, map, full, 64, row);
                 }
+                return true;
+            };
+            bool ok = load_tile(0, false);
+            for (int i = 0; i < n_tiles && ok; ++i) {
+                if (i + 1 < n_tiles) ok = load_tile(i + 1, false);
+                if (ok) ok = load_tile(i, true);
             }
         }
     } else if (warp == 1) {
@@ -177,10 +211,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (elect_one()) {
             bool ok = mbar_wait(q_full, 0, 12);
             const uint64_t dq0 = umma_desc_sw128(smem + SMEM_Q), dq1 = umma_desc_sw128(smem + SMEM_Q + HALF_BYTES);
-            const uint64_t dp0 = umma_desc_sw128(smem + SMEM_P), dp1 = umma_desc_sw128(smem + SMEM_P + HALF_BYTES);
             auto issue_qk = [&](int i) -> bool {
                 const int s = i % KV_STAGES, sb = i & 1;
-                if (!mbar_wait(&kv_full[s], (i / KV_STAGES) & 1, 13)) return false;
+                if (!mbar_wait(&k_full[s], (i / KV_STAGES) & 1, 13)) return false;
                 if (!mbar_wait(&s_empty[sb], ((i >> 1) & 1) ^ 1, 14)) return false;
                 tcgen05_fence_after();
                 const uint64_t dk0 = umma_desc_sw128(smem + SMEM_K + s * TILE_BYTES);
@@ -190,6 +223,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int k = 0; k < 4; ++k) umma_bf16(acc, dq0 + 2 * k, dk0 + 2 * k, IDESC_QK, k > 0);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_bf16(acc, dq1 + 2 * k, dk1 + 2 * k, IDESC_QK, 1);
+                umma_commit(&k_empty[s]);        // K of this tile is free
                 umma_commit(&s_full[sb]);
                 return true;
             };
@@ -198,16 +232,18 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 // the next tile's scores first: they run while the softmax of tile i does
                 if (i + 1 < n_tiles) { ok = issue_qk(i + 1); if (!ok) break; }
                 const int s = i % KV_STAGES;
-                ok = mbar_wait(p_full, i & 1, 15);
+                ok = mbar_wait(&v_full[s], (i / KV_STAGES) & 1, 19) && mbar_wait(p_full, i & 1, 15);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint64_t dv = umma_desc_mn_sw128(smem + SMEM_V + s * TILE_BYTES);
+                const uint64_t dp0 = umma_desc_sw128(smem + SMEM_P + (i & 1) * TILE_BYTES);
+                const uint64_t dp1 = umma_desc_sw128(smem + SMEM_P + (i & 1) * TILE_BYTES + HALF_BYTES);
                 // K of this product = keys: 16 keys = two 8-row groups = 2048 bytes a step
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_bf16(tmem_base + TM_O, dp0 + 2 * k, dv + (uint64_t)(k * 2048 >> 4), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_bf16(tmem_base + TM_O, dp1 + 2 * k, dv + (uint64_t)((4 + k) * 2048 >> 4), IDESC_PV, 1);
-                umma_commit(&kv_empty[s]);       // K and V of this tile are free
+                umma_commit(&v_empty[s]);        // V of this tile is free
                 umma_commit(pv_done);            // P is free, O is updated
             }
         }
@@ -226,74 +262,80 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (i >> 1) & 1, 16));
             if (!ok) break;
             tcgen05_fence_after();
+            // the whole row of scores into registers; the buffer is free for the tile after next
+            uint32_t v[128];
             const uint32_t s_addr = tmem_base + (sb ? TM_S1 : TM_S0) + lane_off;
-            const int kbase = (kt_begin + i) * BN;
+            tmem_ld32<0>(s_addr, v);
+            tmem_ld32<32>(s_addr + 32, v);
+            tmem_ld32<64>(s_addr + 64, v);
+            tmem_ld32<96>(s_addr + 96, v);
+            tmem_ld_wait();
+            tcgen05_fence_before();
+            mbar_arrive(&s_empty[sb]);
             // columns [lo, lo + span] of this tile are keys this row may see (span < 0: none)
+            const int kbase = (kt_begin + i) * BN;
             const int lo = max(from - kbase, 0);
             const int span = min(pos - kbase, BN - 1) - lo;
-            // pass 1: the row's maximum over the tile
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(s_addr + c0, v);
-                tmem_ld_wait();
+            if (lo != 0 || span != BN - 1) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if ((unsigned)(c0 + j - lo) <= (unsigned)span && span >= 0) mx = fmaxf(mx, __uint_as_float(v[j]) * p.scale_log2);
-                }
+                for (int c = 0; c < BN; ++c)
+                    if (!((unsigned)(c - lo) <= (unsigned)span && span >= 0)) v[c] = 0xff800000u;       // -inf
             }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < BN; c += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(v[c]));
+                mx1 = fmaxf(mx1, __uint_as_float(v[c + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(v[c + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(v[c + 3]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;      // scale > 0
             // the reference maximum moves only when the tile raises it by more than the threshold
             float m_new = m_ref;
             if (mx > m_ref + RESCALE_THRESHOLD || m_ref == -INFINITY) m_new = fmaxf(m_ref, mx);
             const bool rescale = m_new != m_ref && m_ref != -INFINITY;
             const float factor = rescale ? exp2f(m_ref - m_new) : 1.0f;
-            const float sub = m_new == -INFINITY ? 0.0f : m_new;
-            // P may be overwritten and O touched only after the previous PV product is done
-            if (i > 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1, 17));
-                if (!ok) break;
-                tcgen05_fence_after();
-            }
-            // pass 2: P = exp2(S - m) to shared memory, row sum
-            float sum = 0.0f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(s_addr + c0, v);
-                tmem_ld_wait();
-                uint32_t packed[8];
+            const float neg_sub = m_new == -INFINITY ? 0.0f : -m_new;
+            // P = exp2(S * scale - m) as bf16 into this tile's P buffer (the product that read
+            // it two tiles ago finished before this tile's scores were complete)
+            uint8_t* pr = prow + sb * TILE_BYTES;
+            float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-                for (int j = 0; j < 16; j += 2) {
-                    const bool in0 = (unsigned)(c0 + j - lo) <= (unsigned)span && span >= 0;
-                    const bool in1 = (unsigned)(c0 + j + 1 - lo) <= (unsigned)span && span >= 0;
-                    float e0 = in0 ? exp2f(__uint_as_float(v[j]) * p.scale_log2 - sub) : 0.0f;
-                    float e1 = in1 ? exp2f(__uint_as_float(v[j + 1]) * p.scale_log2 - sub) : 0.0f;
-                    sum += e0 + e1;
+            for (int c0 = 0; c0 < BN; c0 += 8) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    float e0 = ex2(fmaf(__uint_as_float(v[c0 + j]), p.scale_log2, neg_sub));
+                    float e1 = ex2(fmaf(__uint_as_float(v[c0 + j + 1]), p.scale_log2, neg_sub));
+                    sum0 += e0;
+                    sum1 += e1;
                     __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
                     packed[j >> 1] = *(uint32_t*)&b;
                 }
-                // 16 keys = two 16-byte pieces of this row's 128-byte line in half (c0 / 64)
-                uint8_t* line = prow + (c0 >> 6) * HALF_BYTES;
-                int piece = (c0 & 63) >> 3;
+                // 8 keys = one 16-byte piece of this row's 128-byte line in half (c0 / 64)
+                uint8_t* line = pr + (c0 >> 6) * HALF_BYTES;
+                const int piece = (c0 & 63) >> 3;
                 *(uint4*)(line + ((piece ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                *(uint4*)(line + (((piece + 1) ^ (r & 7)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
             }
-            // the score tile may be overwritten by the product after next
-            tcgen05_fence_before();
-            mbar_arrive(&s_empty[sb]);
-            l = l * factor + sum;
+            l = l * factor + (sum0 + sum1);
             m_ref = m_new;
+            // the product of the tile before has read its P and updated O by now, as a rule; every
+            // phase of this barrier is waited for in turn, so that its parity stays unambiguous
+            if (i > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1, 17));
+                if (!ok) break;
+            }
             // rare: bring O to the new reference
             if (__any_sync(0xffffffffu, rescale)) {
+                tcgen05_fence_after();
 #pragma unroll 1
                 for (int c0 = 0; c0 < HD; c0 += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_base + TM_O + lane_off + c0, v);
+                    uint32_t o[16];
+                    tmem_ld16(tmem_base + TM_O + lane_off + c0, o);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * factor);
-                    tmem_st16(tmem_base + TM_O + lane_off + c0, v);
+                    for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
+                    tmem_st16(tmem_base + TM_O + lane_off + c0, o);
                 }
                 tmem_st_wait();
             }
