@@ -96,10 +96,11 @@ def embed_gather(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> N
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
             out_f32: Optional[torch.Tensor] = None, row_index: Optional[torch.Tensor] = None,
-            partials: Optional[torch.Tensor] = None) -> None:
+            partials: Optional[torch.Tensor] = None, out_split: Optional[torch.Tensor] = None) -> None:
     """out[r] = rmsnorm(x[row_index[r] or r]) * weight; x, weight float32; out float32 or
     bfloat16; out_f32 an optional float32 copy of the result.  ``partials`` ([S, rows, H]
-    float32): x[r] += sum_s partials[s, r] first, and x keeps the sum."""
+    float32): x[r] += sum_s partials[s, r] first, and x keeps the sum.  ``out_split``
+    (bfloat16 [rows, 3H]): the float32 result as three bfloat16 terms hi | mid | lo."""
     _need(x, "x", torch.float32), _need(weight, "weight", torch.float32), _need(out, "out")
     rows, H = out.shape
     if x.shape[-1] != H or weight.numel() != H:
@@ -108,6 +109,10 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
         _need(out_f32, "out_f32", torch.float32)
     if row_index is not None:
         _need(row_index, "row_index", torch.int32)
+    if out_split is not None:
+        _need(out_split, "out_split", torch.bfloat16)
+        if tuple(out_split.shape) != (rows, 3 * H):
+            raise KernelError(f"rmsnorm: out_split {tuple(out_split.shape)} is not [{rows}, {3 * H}]")
     n_part, part_stride = 0, 0
     if partials is not None:
         _need(partials, "partials", torch.float32)
@@ -115,7 +120,8 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
             raise KernelError(f"rmsnorm: partials {tuple(partials.shape)} do not fit {rows} rows of {H}")
         n_part, part_stride = partials.shape[0], partials.stride(0)
     st = library("rowwise").cj_rmsnorm(_ptr(x), _ptr(weight), _f(eps), _i(rows), _i(H), _ptr(out), _i(_code(out)),
-                                       _ptr(out_f32), _ptr(row_index), _ptr(partials), _i(n_part), _ll(part_stride), _stream())
+                                       _ptr(out_f32), _ptr(out_split), _ptr(row_index), _ptr(partials), _i(n_part),
+                                       _ll(part_stride), _stream())
     _check(st, "rmsnorm")
 
 
@@ -213,6 +219,25 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
     if T > 32:
         global launches
         launches += 1                  # many rows take two kernels: logits, then selection
+
+
+def router_select(partials: torch.Tensor, num_experts: int, top_k: int, norm_topk: bool, sel: torch.Tensor,
+                  weights: torch.Tensor, shared_scale: Optional[torch.Tensor]) -> None:
+    """Softmax over all experts, top-k and the shared gate's sigmoid from router logits given
+    as partial sums ``[S, T, ld]`` (float32; column ``num_experts`` holds the gate's dot when
+    ``shared_scale`` is given); the partials of a row are added in order first."""
+    _need(partials, "partials", torch.float32), _need(sel, "sel", torch.int32), _need(weights, "weights", torch.float32)
+    if partials.dim() != 3:
+        raise KernelError(f"router_select: partials {tuple(partials.shape)} are not [S, T, ld]")
+    if num_experts > 1024:
+        raise KernelError(f"router_select: {num_experts} experts; this kernel takes at most 1024")
+    S, T, ld = partials.shape
+    if shared_scale is not None:
+        _need(shared_scale, "shared_scale", torch.float32)
+    st = library("moe_route").cj_router_select(_ptr(partials), _i(S), _ll(partials.stride(0)), _i(ld), _i(T), _i(num_experts),
+                                               _i(top_k), _i(1 if norm_topk else 0), _ptr(sel), _ptr(weights),
+                                               _ptr(shared_scale), _stream())
+    _check(st, "router_select")
 
 
 def moe_group(sel: torch.Tensor, top_k: int, num_experts: int, offsets: torch.Tensor, slot_token: torch.Tensor,

@@ -210,6 +210,28 @@ __global__ void __launch_bounds__(32) router_select_kernel(
     select_row(logits + (size_t)blockIdx.x * n_cols, blockIdx.x, E, k, norm_topk, sel, w, shared_scale, probs, threadIdx.x);
 }
 
+// The selection from logits that a product split along K left as partial sums
+// [n_partials][T][ld] (column E: the shared gate's dot): a warp adds a row's partials in
+// split order and selects.  Four rows a block.
+constexpr int SELECT_ROWS = 4;
+__global__ void __launch_bounds__(SELECT_ROWS * 32) router_select_partials_kernel(
+    const float* __restrict__ partials, int n_partials, long long partial_stride, int ld, int T, int E, int k,
+    int norm_topk, int* __restrict__ sel, float* __restrict__ w, float* __restrict__ shared_scale) {
+    __shared__ float probs[SELECT_ROWS][MAX_EXPERTS];
+    __shared__ float row[SELECT_ROWS][MAX_EXPERTS + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * SELECT_ROWS + warp;
+    if (t >= T) return;
+    const int n_cols = E + (shared_scale ? 1 : 0);
+    for (int e = lane; e < n_cols; e += 32) {
+        float v = 0.0f;
+        for (int s = 0; s < n_partials; ++s) v += partials[s * partial_stride + (size_t)t * ld + e];
+        row[warp][e] = v;
+    }
+    __syncwarp();
+    select_row(row[warp], t, E, k, norm_topk, sel, w, shared_scale, probs[warp], lane);
+}
+
 // Counting sort of the picks (token t, choice j) by expert, stable.  One block per
 // expert: its warps each take a contiguous stretch of the picks, count the picks of lower
 // experts (the expert's first slot) and their own, and then place their own in pick order.  reference: model/MoeFfn.cajeta:2064-2099 (groupPicks), device
@@ -322,6 +344,17 @@ CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* share
     int st = launch_status();
     if (st) return st;
     router_select_kernel<<<T, 32, 0, stream>>>(logits, E, n_cols, k, norm_topk, sel, w, shared_gate ? shared_scale : nullptr);
+    return launch_status();
+}
+
+// partials: [n_partials][T][ld] float32 logits (column E the shared gate's dot when shared_scale is given).
+CJ_EXPORT int cj_router_select(const float* partials, int n_partials, long long partial_stride, int ld, int T, int E, int k,
+                               int norm_topk, int* sel, float* w, float* shared_scale, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (!partials || !sel || !w || n_partials < 1) return CJ_ERR_ARG;
+    if (E < 1 || E > MAX_EXPERTS || k < 1 || k > E || ld < E + (shared_scale ? 1 : 0)) return CJ_ERR_SIZE;
+    router_select_partials_kernel<<<(T + SELECT_ROWS - 1) / SELECT_ROWS, SELECT_ROWS * 32, 0, stream>>>(
+        partials, n_partials, partial_stride, ld, T, E, k, norm_topk, sel, w, shared_scale);
     return launch_status();
 }
 

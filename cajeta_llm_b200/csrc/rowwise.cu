@@ -38,13 +38,26 @@ CJ_EXPORT int cj_embed_gather(float* out, const void* table, int table_dtype, co
 // RMSNorm: ss = sum x^2; scale = 1/sqrt(ss/dim + eps); y = x * scale * w
 // reference: model/Prim.cajeta:120-151.  One block per output row; the input row may
 // be picked through row_index (the rows whose logits are wanted).  Writes the result
-// in the activation dtype and, when asked, a float32 copy (the router's input).
+// in the activation dtype and, when asked, a float32 copy (the router's input) or the
+// same float32 value cut into three bfloat16 terms [rows, 3H] = hi | mid | lo with
+// hi = bf16(y), mid = bf16(y - hi), lo = bf16(y - hi - mid): their sum is y to 2^-24, so
+// a bfloat16 tensor-core product over the widened row gives float32-grade router logits.
 // ---------------------------------------------------------------------------------
 // The row is read once into registers (with the weight, whose load is then in flight during
 // the reduction) when it fits PER elements a thread; otherwise it is read twice.
+__device__ __forceinline__ void write_split(__nv_bfloat16* dst, int H, float y) {
+    __nv_bfloat16 hi = __float2bfloat16_rn(y);
+    float r1 = y - __bfloat162float(hi);
+    __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+    __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+    dst[0] = hi;
+    dst[H] = mid;
+    dst[2 * H] = lo;
+}
+
 template <typename TO, int PER>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ w, float eps, int H,
-                               TO* __restrict__ out, float* __restrict__ out_f32,
+                               TO* __restrict__ out, float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_split,
                                const int* __restrict__ row_index, const float* __restrict__ partials, int n_partials,
                                long long partial_stride) {
     __shared__ float partial[32];
@@ -105,6 +118,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
                 float y = xv[q] * scale * wv[q];
                 out[(size_t)r * H + i] = from_f32<TO>(y);
                 if (out_f32) out_f32[(size_t)r * H + i] = y;
+                if (out_split) write_split(out_split + (size_t)r * 3 * H + i, H, y);
             }
         }
     } else {
@@ -112,22 +126,24 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
             float y = src[i] * scale * w[i];
             out[(size_t)r * H + i] = from_f32<TO>(y);
             if (out_f32) out_f32[(size_t)r * H + i] = y;
+            if (out_split) write_split(out_split + (size_t)r * 3 * H + i, H, y);
         }
     }
 }
 
 // partials (optional): [n_partials][rows][H] float32 with partial_stride elements between
 // them; x[r] += sum of its partials first (the residual add of a product that was split
-// along K), and x keeps the sum.  Not combined with row_index.
+// along K), and x keeps the sum.  Not combined with row_index.  out_split (optional):
+// bfloat16 [rows, 3H], the three-term form of the float32 result.
 CJ_EXPORT int cj_rmsnorm(float* x, const float* w, float eps, int rows, int H, void* out, int out_dtype,
-                         float* out_f32, const int* row_index, const float* partials, int n_partials,
+                         float* out_f32, void* out_split, const int* row_index, const float* partials, int n_partials,
                          long long partial_stride, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (!x || !w || !out || H <= 0) return CJ_ERR_ARG;
     if (partials && (row_index || n_partials < 1)) return CJ_ERR_ARG;
     int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     int per = (H + threads - 1) / threads;
-#define LAUNCH(TO, PER) rmsnorm_kernel<TO, PER><<<rows, threads, 0, stream>>>(x, w, eps, H, (TO*)out, out_f32, row_index, partials, n_partials, partial_stride)
+#define LAUNCH(TO, PER) rmsnorm_kernel<TO, PER><<<rows, threads, 0, stream>>>(x, w, eps, H, (TO*)out, out_f32, (__nv_bfloat16*)out_split, row_index, partials, n_partials, partial_stride)
 #define PICK(TO)                                   \
     if (per <= 4) LAUNCH(TO, 4);                   \
     else if (per <= 8) LAUNCH(TO, 8);              \

@@ -43,6 +43,11 @@ class PreNormBlock(Part):
         # a mixer may return partial sums it still owes the residual stream ([S, rows, H]
         # float32, from a product split along K); the next norm adds them as it reads hs
         pending = self.mixer.forward(x, hs, ctx, entry)
-        x, x_f32 = self.feed_forward_norm.forward(hs, want_f32=getattr(self.feed_forward, "needs_f32_input", False),
-                                                  pending=pending)
-        self.feed_forward.forward(x, x_f32, hs, ctx)
+        # the feed-forward may want its input once more in float32 (a router), or, for many
+        # rows, as three bfloat16 terms that a tensor-core product can sum to the same grade
+        ff = self.feed_forward
+        wants_split = getattr(ff, "wants_split_input", None)
+        split = bool(wants_split and wants_split(hs.shape[0]))
+        x, x_exact = self.feed_forward_norm.forward(hs, want_f32=getattr(ff, "needs_f32_input", False) and not split,
+                                                    pending=pending, want_split=split)
+        ff.forward(x, x_exact, hs, ctx)

@@ -87,6 +87,7 @@ class SparseMoE(Part):
         self.w_gate = self.w_up = self.w_down = None
         self.ws_gate = self.ws_up = self.ws_down = None
         self.shared_gate_w = None
+        self.router_split = None        # [cols, 3 hidden] bfloat16: router rows (and the gate's) three times over
         self.last_offsets = None
         # chunks of the shared expert that run as extra groups of the grouped products
         self.shared_chunks = 0
@@ -136,7 +137,54 @@ class SparseMoE(Part):
             if self.shared_gate:
                 self.shared_gate_w = self.fetch(source, self.name("shared_expert_gate.weight")).reshape(-1).contiguous()
 
-    def forward(self, x: torch.Tensor, x_f32: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+        self._prepare_split_router()
+
+    # Router logits on the tensor cores, float32-grade.  The normed row arrives as three
+    # bfloat16 terms hi | mid | lo (their sum is the float32 value to 2^-24); the router's
+    # weights, when they are exactly representable in bfloat16 (a bfloat16 checkpoint), are
+    # laid three times side by side, so one bfloat16 product over K = 3 hidden, accumulated in
+    # float32 and cut along K into partial sums, gives sum_j w[e, j] (hi + mid + lo)[j] with
+    # every product exact.  Used for many rows; few rows take the fused float32 kernel.
+    SPLIT_ROUTER_MIN_ROWS = 64
+
+    def _prepare_split_router(self) -> None:
+        rt = self.runtime
+        self.router_split = None
+        if not rt.fast_kernels or self.hidden % 8 != 0 or self.hidden < 128:
+            return
+        rows = [self.router]
+        if self.shared_gate:
+            rows.append(self.shared_gate_w.view(1, -1))
+        w = torch.cat(rows, dim=0)
+        wb = w.to(torch.bfloat16)
+        if not torch.equal(wb.to(torch.float32), w):
+            return                              # weights with more than 8 bits of mantissa: the float32 kernel
+        cols = -(-w.shape[0] // 16) * 16
+        padded = torch.zeros((cols, self.hidden), dtype=torch.bfloat16, device=w.device)
+        padded[:w.shape[0]] = wb
+        self.router_split = torch.cat([padded, padded, padded], dim=1).contiguous()
+
+    def wants_split_input(self, rows: int) -> bool:
+        return self.router_split is not None and rows >= self.SPLIT_ROUTER_MIN_ROWS
+
+    def _route(self, x_exact: torch.Tensor, sel, wts, shared_scale) -> None:
+        k = self.top_k
+        if x_exact.dtype == torch.bfloat16:
+            # the three-term form: one tensor-core product, cut along K so that the machine is
+            # occupied and the float32 sums stay short
+            T = x_exact.shape[0]
+            cols, Kd = self.router_split.shape
+            k_blocks = Kd // 64
+            tiles = -(-T // 128) * -(-cols // 128)
+            splits = max(1, min(8, k_blocks // 8, -(-148 // tiles)))
+            logits = torch.empty((splits, T, cols), dtype=torch.float32, device=x_exact.device)
+            K.gemm_tc(x_exact, self.router_split, logits if splits > 1 else logits[0], K.EPI_STORE_F32, False, 128,
+                      k_splits=splits)
+            K.router_select(logits, self.num_experts, k, self.norm_topk, sel, wts, shared_scale)
+        else:
+            K.router_topk(x_exact, self.router, self.shared_gate_w, k, self.norm_topk, sel, wts, shared_scale)
+
+    def forward(self, x: torch.Tensor, x_exact: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         rt = self.runtime
         dev = x.device
         T = x.shape[0]
@@ -144,7 +192,7 @@ class SparseMoE(Part):
         sel = torch.empty((T, k), dtype=torch.int32, device=dev)
         wts = torch.empty((T, k), dtype=torch.float32, device=dev)
         shared_scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.shared_gate else None
-        K.router_topk(x_f32, self.router, self.shared_gate_w, k, self.norm_topk, sel, wts, shared_scale)
+        self._route(x_exact, sel, wts, shared_scale)
 
         C = self.shared_chunks
         n_slots = T * k + C * T

@@ -30,20 +30,27 @@ class RMSNorm(Part):
         self.weight = self.fetch(source, self.name("weight"))
 
     def forward(self, x: torch.Tensor, want_f32: bool = False, row_index: Optional[torch.Tensor] = None,
-                out_dtype: Optional[torch.dtype] = None, pending: Optional[torch.Tensor] = None
-                ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+                out_dtype: Optional[torch.dtype] = None, pending: Optional[torch.Tensor] = None,
+                want_split: bool = False) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """Normalise rows of the float32 residual stream.
 
         Returns the result in the activation dtype and, when ``want_f32``, also in
         float32 (the same tensor on the 32-bit path).  ``row_index`` (int32) picks the
         rows to normalise.  ``pending`` ([S, rows, dim] float32) are partial sums still
         owed to the residual stream by the part before: they are added to ``x`` (in
-        order, ``x`` keeps the sum) in the same pass."""
+        order, ``x`` keeps the sum) in the same pass.  ``want_split`` (instead of
+        ``want_f32``): the second result is bfloat16 ``[rows, 3 * dim]``, the float32 value
+        as three bfloat16 terms hi | mid | lo whose sum is the value to 2^-24 - the form a
+        tensor-core product needs to give float32-grade sums."""
         rt = self.runtime
         rows = x.shape[0] if row_index is None else row_index.numel()
         dtype = out_dtype or rt.act_dtype
         out = torch.empty((rows, self.dim), dtype=dtype, device=x.device)
         out_f32 = None
+        if want_split:
+            split = torch.empty((rows, 3 * self.dim), dtype=torch.bfloat16, device=x.device)
+            K.rmsnorm(x, self.weight, self.eps, out, None, row_index, pending, out_split=split)
+            return out, split
         if want_f32:
             out_f32 = out if dtype == torch.float32 else torch.empty((rows, self.dim), dtype=torch.float32, device=x.device)
         K.rmsnorm(x, self.weight, self.eps, out, out_f32 if out_f32 is not out else None, row_index, pending)

@@ -194,3 +194,43 @@ def test_block_part(dtype):
     x = x + P.swiglu_mlp(P.rmsnorm(x, w["L.n2.weight"], 1e-6), w["L.ff.gate_proj.weight"], w["L.ff.up_proj.weight"],
                          w["L.ff.down_proj.weight"])
     assert torch.allclose(hs.cpu().double(), x, **tol(dtype))
+
+
+@pytest.mark.parametrize("E,k,gate,norm,T", [(60, 4, True, False, 150), (7, 2, False, True, 64), (130, 3, True, True, 300)])
+def test_router_on_tensor_cores_is_float32_grade(E, k, gate, norm, T):
+    """Many rows route through a bfloat16 tensor-core product over the three-term form of the
+    float32 normed row.  The norm's three terms add up to its float32 result, and the
+    selection and weights equal those of the float32 router kernel (and the plain router)."""
+    from cajeta_llm_b200.parts.plan import PartSpec
+    from cajeta_llm_b200.csrc import kernels as K
+    H = 264
+    norm_part, nw = make("norm", PartSpec("rmsnorm", {"dim": H, "eps": 1e-5}), "n", "bfloat16", 21)
+    hs = (torch.randn(T, H, generator=torch.Generator().manual_seed(22)) * 3).to(DEV)
+    out, split = norm_part.forward(hs, want_split=True)
+    out2, x32 = norm_part.forward(hs, want_f32=True)
+    assert torch.equal(out, out2) and split.shape == (T, 3 * H) and split.dtype == torch.bfloat16
+    assert torch.equal(split[:, :H], out)
+    back = split[:, :H].double() + split[:, H:2 * H].double() + split[:, 2 * H:].double()
+    assert float((back - x32.double()).abs().max()) <= 2.0 ** -23 * float(x32.abs().max())
+
+    spec = PartSpec("sparse_moe", {"hidden_size": H, "num_experts": E, "top_k": k, "expert_intermediate_size": 32,
+                                   "shared_intermediate_size": 64 if gate else 0, "shared_gate": gate, "norm_topk_prob": norm})
+    part, w = make("feed_forward", spec, "m", "bfloat16", 23)
+    assert part.wants_split_input(T) and not part.wants_split_input(8)
+    sel = [torch.empty((T, k), dtype=torch.int32, device=DEV) for _ in range(2)]
+    wts = [torch.empty((T, k), dtype=torch.float32, device=DEV) for _ in range(2)]
+    sc = [torch.empty((T,), dtype=torch.float32, device=DEV) if gate else None for _ in range(2)]
+    part._route(split, sel[0], wts[0], sc[0])
+    part._route(x32, sel[1], wts[1], sc[1])
+    assert K.gemm_tc_error() == 0
+    same = (sel[0] == sel[1]).all(dim=1)
+    assert int((~same).sum()) <= 1                     # an exact near-tie may fall either way
+    assert torch.allclose(wts[0][same], wts[1][same], atol=1e-6, rtol=1e-5)
+    if gate:
+        assert torch.allclose(sc[0], sc[1], atol=1e-6, rtol=1e-5)
+    # and against the plain router on a few rows
+    for t in (0, T // 2, T - 1):
+        logits = x32[t].double().cpu() @ w["m.gate.weight"].t()
+        psel, pw = P.route(logits, k, norm)
+        assert sel[0][t].tolist() == psel
+        assert torch.allclose(wts[0][t].double().cpu(), pw, atol=1e-6, rtol=1e-5)
