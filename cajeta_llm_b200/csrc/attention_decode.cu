@@ -1,8 +1,8 @@
 // Decode attention for the bfloat16 path: few query rows, each over a long stretch of
-// cached keys.  The keys of a row are cut into fixed chunks of 128 ("split-KV"); one
+// cached keys.  The keys of a row are cut into fixed chunks of 64 or 128 ("split-KV"); one
 // block takes one (row, kv head, chunk), stages the chunk's keys and values in shared
-// memory, and then each thread takes one key for the scores and eight output dims of a
-// key phase for the weighted sum of values, for every query head of the kv head's group.  A chunk leaves a partial (max, sum, unnormalised accumulator); the
+// memory, and then four lanes share a key for the scores and each thread takes eight output
+// dims of a key phase for the weighted sum of values, for every query head of the kv head's group.  A chunk leaves a partial (max, sum, unnormalised accumulator); the
 // block that finishes a (row, head) last merges the partials in chunk order, so the
 // result does not depend on which block arrived when, nor - the chunking being a function
 // of the row's own [from, p] - on what else is in the batch.
@@ -16,7 +16,7 @@ using namespace cj;
 
 namespace {
 
-constexpr int CHUNK = 128;       // keys per block = threads per block
+constexpr int THREADS = 256;     // threads per block; a block takes CHUNK (64 or 128) keys
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -29,22 +29,21 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // is in flight at once) into shared memory, 16-byte pieces XOR-swizzled by row so that both
 // the per-key reads of the scores and the per-column reads of the value sum are free of
 // bank conflicts; all query heads of the kv head's group then work from shared memory.
-template <int HD>
-__global__ void __launch_bounds__(CHUNK) decode_attention_kernel(
+template <int HD, int CHUNK>
+__global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ kplane,
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ positions, const int* __restrict__ row_req,
     const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int window, float scale,
     float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters, int max_splits) {
     constexpr int VEC = 8;                        // dims one thread owns in the value sum (one 16-byte piece)
     constexpr int COLS = HD / VEC;                // pieces of a row
-    constexpr int KPAR = CHUNK / COLS;            // key phases working side by side in the value sum
+    constexpr int KPAR = THREADS / COLS;          // key phases working side by side in the value sum
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;             // [CHUNK][HD], pieces swizzled
     __nv_bfloat16* vs = ks + CHUNK * HD;                      // [CHUNK][HD], pieces swizzled
-    __shared__ __align__(16) float qs[HD];
     __shared__ float es[CHUNK];
     __shared__ long long bases[CHUNK];
-    __shared__ float red[CHUNK / 32];
+    __shared__ float red[THREADS / 32];
     __shared__ float vsum[KPAR][HD + 4];
     __shared__ int is_last;
 
@@ -68,53 +67,90 @@ __global__ void __launch_bounds__(CHUNK) decode_attention_kernel(
     }
     __syncthreads();
     // all keys, then all values, on their way to shared memory
-    for (int i = tid; i < count * COLS; i += CHUNK) {
+    for (int i = tid; i < count * COLS; i += THREADS) {
         int r = i / COLS, c = i % COLS;
         cp_async16(ks + r * HD + ((c ^ (r & 7)) * VEC), kplane + bases[r] + c * VEC);
     }
     cp_async_commit();
-    for (int i = tid; i < count * COLS; i += CHUNK) {
+    for (int i = tid; i < count * COLS; i += THREADS) {
         int r = i / COLS, c = i % COLS;
         cp_async16(vs + r * HD + ((c ^ (r & 7)) * VEC), vplane + bases[r] + c * VEC);
     }
     cp_async_commit();
 
+    // scores: four lanes share a key, each with a quarter of the head's dims (its part of q in
+    // registers); lane = quarter * 8 + key, so that the eight lanes of a shared-memory
+    // wavefront read eight different rows at eight different swizzled pieces
+    constexpr int QD = HD / 4;                     // dims a lane owns in the score
+    constexpr int KEYS_PER_PASS = THREADS / 4;     // keys the block scores side by side
+    const int quarter = lane >> 3;
     for (int hg = 0; hg < group; ++hg) {
         const int h = kvh * group + hg;
-        __syncthreads();                                        // previous head done with qs / es / vsum
-        if (tid < HD) qs[tid] = __bfloat162float(q[((size_t)t * n_heads + h) * HD + tid]);
-        if (hg == 0) cp_async_wait<1>();                        // this thread's key pieces have landed
-        __syncthreads();                                        // everyone's
-
-        // scores: one key per thread
-        float s = -INFINITY;
-        if (tid < count) {
-            float dot = 0.0f;
+        float qr[QD];
+        {
+            const __nv_bfloat16* qp = q + ((size_t)t * n_heads + h) * HD + quarter * QD;
 #pragma unroll
-            for (int c = 0; c < COLS; ++c) {
-                uint4 u = *(const uint4*)(ks + tid * HD + ((c ^ (tid & 7)) * VEC));
+            for (int c = 0; c < QD / 8; ++c) {
+                uint4 u = *(const uint4*)(qp + c * 8);
                 const __nv_bfloat162* b2 = (const __nv_bfloat162*)&u;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     float2 f = __bfloat1622float2(b2[j]);
-                    dot = fmaf(qs[c * 8 + 2 * j], f.x, dot);
-                    dot = fmaf(qs[c * 8 + 2 * j + 1], f.y, dot);
+                    qr[c * 8 + 2 * j] = f.x;
+                    qr[c * 8 + 2 * j + 1] = f.y;
                 }
             }
-            s = dot * scale;
         }
-        float m = warp_max(s);
+        if (hg == 0) cp_async_wait<1>();                        // this thread's key pieces have landed
+        __syncthreads();                                        // everyone's; the previous head is done with es / vsum
+
+        float sc[CHUNK / KEYS_PER_PASS];
+        float m = -INFINITY;
+#pragma unroll
+        for (int pass = 0; pass < CHUNK / KEYS_PER_PASS; ++pass) {
+            const int key = pass * KEYS_PER_PASS + warp * 8 + (lane & 7);
+            float dot = 0.0f;
+#pragma unroll
+            for (int c = 0; c < QD / 8; ++c) {
+                const int piece = quarter * (QD / 8) + c;
+                uint4 u = *(const uint4*)(ks + key * HD + ((piece ^ (key & 7)) * VEC));
+                const __nv_bfloat162* b2 = (const __nv_bfloat162*)&u;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float2 f = __bfloat1622float2(b2[j]);
+                    dot = fmaf(qr[c * 8 + 2 * j], f.x, dot);
+                    dot = fmaf(qr[c * 8 + 2 * j + 1], f.y, dot);
+                }
+            }
+            dot += __shfl_xor_sync(0xffffffffu, dot, 8);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 16);
+            sc[pass] = key < count ? dot * scale : -INFINITY;     // rows past the chunk's end hold nothing
+            m = fmaxf(m, sc[pass]);
+        }
+        m = warp_max(m);
         if (lane == 0) red[warp] = m;
         __syncthreads();
-        m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-        float e = tid < count ? expf(s - m) : 0.0f;
-        es[tid] = e;
-        float l = warp_sum(e);
+        m = red[0];
+#pragma unroll
+        for (int w = 1; w < THREADS / 32; ++w) m = fmaxf(m, red[w]);
+        float l = 0.0f;
+#pragma unroll
+        for (int pass = 0; pass < CHUNK / KEYS_PER_PASS; ++pass) {
+            const int key = pass * KEYS_PER_PASS + warp * 8 + (lane & 7);
+            float e = key < count ? expf(sc[pass] - m) : 0.0f;
+            if (quarter == 0) {
+                es[key] = e;
+                l += e;
+            }
+        }
+        l = warp_sum(l);
         if (hg == 0) cp_async_wait<0>();                        // this thread's value pieces have landed
         __syncthreads();                                        // everyone has read red; es and values visible
         if (lane == 0) red[warp] = l;
         __syncthreads();
-        l = (red[0] + red[1]) + (red[2] + red[3]);
+        l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < THREADS / 32; ++w) l += red[w];
 
         // values: thread = (8 dims, key phase); the keys of its phase in order
         const int col = tid % COLS, phase = tid / COLS;
@@ -155,17 +191,21 @@ __global__ void __launch_bounds__(CHUNK) decode_attention_kernel(
     }
     if (n_splits == 1) return;
 
-    // the last chunk of this (row, kv head) to finish merges all chunks, in chunk order
-    __threadfence();
+    // the last chunk of this (row, kv head) to finish merges all chunks, in chunk order.  The
+    // barrier orders the block's partial stores before thread 0, whose fence (cumulative)
+    // orders them before its ticket.
     __syncthreads();
     if (tid == 0) {
+        __threadfence();
         int done = atomicAdd(&counters[t * n_kv + kvh], 1);
         is_last = done == n_splits - 1;
-        if (is_last) counters[t * n_kv + kvh] = 0;             // ready for the next launch
+        if (is_last) {
+            counters[t * n_kv + kvh] = 0;                       // ready for the next launch
+            __threadfence();                                    // the other chunks' partials, published before their tickets
+        }
     }
     __syncthreads();
     if (!is_last) return;
-    __threadfence();
     for (int hg = 0; hg < group; ++hg) {
         const int h = kvh * group + hg;
         size_t slot0 = ((size_t)t * n_heads + h) * max_splits;
@@ -190,36 +230,41 @@ __global__ void __launch_bounds__(CHUNK) decode_attention_kernel(
 }  // namespace
 
 // q, out: [T, n_heads, hd] bf16; planes [pages, n_kv, page_tokens, hd] bf16.  max_context
-// bounds position + 1 over the rows.  part_acc: scratch float32 [T, n_heads, max_splits, hd],
+// bounds position + 1 over the rows.  chunk: keys a block takes, 64 or 128.  part_acc: scratch float32 [T, n_heads, max_splits, hd],
 // part_ml: [T, n_heads, max_splits, 2], counters: int32 [T * n_kv], zero before the first use
 // (the kernel leaves them zero).  hd must be 64 or 128.
 CJ_EXPORT int cj_decode_attention(const void* q, void* out, const void* kplane, const void* vplane, const int* positions,
                                   const int* row_req, const int* table, int table_stride, int page_tokens, int T,
                                   int n_heads, int n_kv, int hd, int window, float scale, int max_context,
-                                  float* part_acc, float* part_ml, int* counters, int max_splits, cudaStream_t stream) {
+                                  float* part_acc, float* part_ml, int* counters, int max_splits, int chunk,
+                                  cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!q || !out || !kplane || !vplane || !positions || !row_req || !table || !part_acc || !part_ml || !counters) return CJ_ERR_ARG;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || page_tokens <= 0) return CJ_ERR_SIZE;
     if (hd != 64 && hd != 128) return CJ_ERR_SIZE;
+    if (chunk != 64 && chunk != 128) return CJ_ERR_SIZE;
     int span = window > 0 ? min(window, max_context) : max_context;
-    int splits = (span + CHUNK - 1) / CHUNK;
+    int splits = (span + chunk - 1) / chunk;
     if (splits < 1) splits = 1;
     if (splits > max_splits || splits > 65535 || n_kv > 65535) return CJ_ERR_SIZE;
     dim3 grid(T, n_kv, splits);
-#define LAUNCH(HD)                                                                                                     \
+#define LAUNCH(HD, CH)                                                                                                 \
     {                                                                                                                  \
-        constexpr int smem = 2 * CHUNK * HD * (int)sizeof(__nv_bfloat16);                                              \
+        constexpr int smem = 2 * CH * HD * (int)sizeof(__nv_bfloat16);                                                 \
         static bool configured = false;                                                                                \
         if (!configured) {                                                                                             \
-            cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+            cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<HD, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
             if (e != cudaSuccess) return (int)e;                                                                       \
             configured = true;                                                                                         \
         }                                                                                                              \
-        decode_attention_kernel<HD><<<grid, CHUNK, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,       \
+        decode_attention_kernel<HD, CH><<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, \
             (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane, positions, row_req, table, table_stride,       \
             page_tokens, n_heads, n_kv, window, scale, part_acc, part_ml, counters, max_splits);                       \
     }
-    if (hd == 128) LAUNCH(128) else LAUNCH(64)
+    if (hd == 128 && chunk == 128) LAUNCH(128, 128)
+    else if (hd == 128) LAUNCH(128, 64)
+    else if (chunk == 128) LAUNCH(64, 128)
+    else LAUNCH(64, 64)
 #undef LAUNCH
     return launch_status();
 }

@@ -354,25 +354,29 @@ def gather_rows(x: torch.Tensor, index: torch.Tensor, out: torch.Tensor) -> None
     _check(st, "gather_rows")
 
 
-DECODE_CHUNK = 128
+def decode_chunk(span: int) -> int:
+    """Keys a block of the split-KV decode kernel takes.  The kernel also takes 64; measured on
+    a B200 it gains nothing for a handful of rows and loses 10 % for many, so 128 it is."""
+    return 128
 
 
 def decode_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
                      positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int,
                      n_heads: int, n_kv: int, head_dim: int, window: int, scale: float, max_context: int,
-                     scratch: "DecodeScratch") -> None:
+                     scratch: "DecodeScratch", chunk: int = 0) -> None:
     """Split-KV attention of few bfloat16 query rows over their cached keys (head_dim 64 or 128)."""
     for n, t in (("q", q), ("out", out), ("k_plane", k_plane), ("v_plane", v_plane)):
         _need(t, n, torch.bfloat16)
     _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
     T = q.shape[0]
     span = min(window, max_context) if window > 0 else max_context
-    splits = max(1, -(-span // DECODE_CHUNK))
+    chunk = chunk or decode_chunk(span)
+    splits = max(1, -(-span // chunk))
     scratch.ensure(T, n_heads, n_kv, head_dim, splits, q.device)
     st = library("attention_decode").cj_decode_attention(
         _ptr(q), _ptr(out), _ptr(k_plane), _ptr(v_plane), _ptr(positions), _ptr(row_req), _ptr(table), _i(table.stride(0)),
         _i(page_tokens), _i(T), _i(n_heads), _i(n_kv), _i(head_dim), _i(window), _f(scale), _i(max_context),
-        _ptr(scratch.acc), _ptr(scratch.ml), _ptr(scratch.counters), _i(scratch.splits), _stream())
+        _ptr(scratch.acc), _ptr(scratch.ml), _ptr(scratch.counters), _i(scratch.splits), _i(chunk), _stream())
     _check(st, "decode_attention")
 
 

@@ -370,10 +370,11 @@ def test_sampler_distribution_and_draws_follow_the_plain_sampler(K, V):
 
 @pytest.mark.parametrize("heads,n_kv,hd,page,window", [(16, 16, 128, 16, 0), (14, 2, 128, 16, 0), (6, 3, 64, 8, 0),
                                                          (8, 4, 64, 16, 200), (4, 1, 128, 16, 130)])
-def test_decode_attention_split_kv(K, heads, n_kv, hd, page, window):
+@pytest.mark.parametrize("chunk", [64, 128])
+def test_decode_attention_split_kv(K, heads, n_kv, hd, page, window, chunk):
     """Rows of very different lengths (1 key, exactly one chunk, several chunks and a
     remainder) against the plain attention; run twice to see the arrival counters reset."""
-    lengths = [1, 128, 129, 700, 300, 17]
+    lengths = [1, 128, 129, 700, 300, 17, 64, 65]
     dtype = torch.bfloat16
     kp, vp, table, ks, vs = paged_setup(lengths, n_kv, hd, page, dtype, seed=70)
     rows = [(r, L - 1) for r, L in enumerate(lengths)]
@@ -386,7 +387,8 @@ def test_decode_attention_split_kv(K, heads, n_kv, hd, page, window):
     outs = []
     for _ in range(2):
         out = torch.full_like(q, 7.0)
-        K.decode_attention(q, out, kp, vp, pos, req, table, page, heads, n_kv, hd, window, scale, max(lengths), scratch)
+        K.decode_attention(q, out, kp, vp, pos, req, table, page, heads, n_kv, hd, window, scale, max(lengths), scratch,
+                           chunk=chunk)
         outs.append(out)
     assert torch.equal(outs[0], outs[1])
     assert int(scratch.counters.abs().sum()) == 0
@@ -398,7 +400,7 @@ def test_decode_attention_split_kv(K, heads, n_kv, hd, page, window):
     # the same row alone gives the same bits: the chunking depends on the row only
     out1 = torch.empty_like(q[3:4])
     K.decode_attention(q[3:4].contiguous(), out1, kp, vp, pos[3:4].contiguous(), req[3:4].contiguous(), table, page, heads,
-                       n_kv, hd, window, scale, lengths[3], K.DecodeScratch())
+                       n_kv, hd, window, scale, lengths[3], K.DecodeScratch(), chunk=chunk)
     assert torch.equal(out1[0], outs[0][3])
 
 
