@@ -36,6 +36,7 @@ LIBRARIES: Dict[str, str] = {
     "moe_route": "moe_route.cu",
     "sampling": "sampling.cu",
     "gemm_tc": "gemm_tc.cu",
+    "gemm_tc2": "gemm_tc2.cu",
     "attention_decode": "attention_decode.cu",
     "attention_prefill": "attention_prefill.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",

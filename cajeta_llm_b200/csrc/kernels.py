@@ -342,6 +342,34 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     _check(st, "gemm_tc")
 
 
+def gemm_tc2(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, n_tok: int,
+             bias: Optional[torch.Tensor] = None, w_up: Optional[torch.Tensor] = None,
+             group_offsets: Optional[torch.Tensor] = None, tokens: Optional[int] = None) -> None:
+    """The same product as ``gemm_tc`` on pairs of SMs (tcgen05 cta_group::2): tiles of 256
+    features x ``n_tok`` (128 or 256) tokens, each SM of a pair loading its own 128 weight rows
+    and half of the token rows.  For steps with many rows."""
+    _need(x, "x", torch.bfloat16), _need(w, "w", torch.bfloat16), _need(out, "out")
+    features, K = w.shape[-2], w.shape[-1]
+    T = tokens if tokens is not None else x.shape[0]
+    if x.shape[-1] != K or out.shape[-1] != features:
+        raise KernelError(f"gemm_tc2: shapes x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)} do not agree")
+    want = torch.bfloat16 if epilogue in (EPI_SWIGLU_BF16, EPI_STORE_BF16) else torch.float32
+    if out.dtype != want:
+        raise KernelError(f"gemm_tc2: epilogue {epilogue} writes {want}, out is {out.dtype}")
+    if w_up is not None:
+        _need(w_up, "w_up", torch.bfloat16)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    G = 0
+    if group_offsets is not None:
+        _need(group_offsets, "group_offsets", torch.int32)
+        G = w.shape[0]
+    st = library("gemm_tc2").cj_gemm_tc2(
+        _ptr(x), _ll(x.stride(0)), _ptr(w), _ptr(w_up), _ptr(bias), _ptr(out), _ll(out.stride(-2)), _i(T), _i(features), _i(K),
+        _i(epilogue), _i(n_tok), _ptr(group_offsets), _i(G), _stream())
+    _check(st, "gemm_tc2")
+
+
 def gemm_tc_error() -> int:
     """0, or the code of a bounded wait inside a tensor-core kernel that ran out of time."""
     return int(library("gemm_tc").cj_gemm_tc_error())
@@ -440,7 +468,8 @@ def wait_errors() -> Dict[str, int]:
     """Codes of bounded waits that ran out inside the tensor-core kernels, by library; empty
     when all is well.  Only libraries that are already loaded are asked."""
     found = {}
-    for name, symbol in (("gemm_tc", "cj_gemm_tc_error"), ("attention_prefill_tc", "cj_prefill_attention_tc_error")):
+    for name, symbol in (("gemm_tc", "cj_gemm_tc_error"), ("gemm_tc2", "cj_gemm_tc2_error"),
+                         ("attention_prefill_tc", "cj_prefill_attention_tc_error")):
         lib = _libs.get(name)
         if lib is not None:
             code = int(getattr(lib, symbol)())

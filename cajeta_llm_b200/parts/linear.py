@@ -50,6 +50,31 @@ def _group_tile(total_rows: int, groups: int) -> int:
     return TOKEN_TILES[-1]
 
 
+PAIR_MIN_ROWS = 512          # dense products with at least this many rows run on pairs of SMs
+PAIR_MIN_GROUP_ROWS = 96     # grouped products whose groups average at least this many rows do
+
+
+def _pair_tile(rows: int, w: torch.Tensor, swiglu: bool, grouped: bool) -> int:
+    """Token tile (128 or 256) of the two-SM product when the shape calls for it, else 0."""
+    features = w.shape[-2]
+    if features < 256:
+        return 0
+    if swiglu:
+        # the two-SM SwiGLU puts 256 tokens on the product's rows: right for a dense layer with
+        # many rows, wasteful for ragged groups (an expert with 136 rows pays for 256), which
+        # stay on the one-SM kernel with the tokens on the product's N
+        return 256 if not grouped and rows >= PAIR_MIN_ROWS else 0
+    if grouped:
+        mean = rows / max(1, w.shape[0])
+        if mean < PAIR_MIN_GROUP_ROWS:
+            return 0
+        return 256 if mean + 2.0 * mean ** 0.5 > 128 else 128
+    if rows < PAIR_MIN_ROWS:
+        return 0
+    feature_tiles = -(-features // 256)
+    return 256 if feature_tiles * -(-rows // 256) >= 74 else 128
+
+
 def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
             accumulate: bool = False, w_up: Optional[torch.Tensor] = None, group_offsets: Optional[torch.Tensor] = None,
             a_row_index: Optional[torch.Tensor] = None, max_group_rows: Optional[int] = None) -> None:
@@ -81,7 +106,11 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
         # (the SwiGLU form keeps two accumulators per stage: beyond 128 tokens tensor memory
         # holds one stage only and the epilogue no longer overlaps the next tile)
         tile = min(128, _group_tile(rows, w.shape[0])) if w_up is not None else _group_tile(rows, w.shape[0])
-    if tile:
+    pair_tile = 0 if tile and group_offsets is None else _pair_tile(rows, w, w_up is not None, group_offsets is not None)
+    if pair_tile:
+        # many rows: tiles of 256 features on pairs of SMs, each loading half of the token rows
+        K.gemm_tc2(x, w, out, epi, pair_tile, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows)
+    elif tile:
         K.gemm_tc(x, w, out, epi, True, tile, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows)
     else:
         n_mma = 256 if (w_up is None and w.shape[-2] >= 512) else 128

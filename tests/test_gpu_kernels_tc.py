@@ -147,3 +147,63 @@ def test_prefill_attention_tcgen05_refuses(K):
     z = torch.zeros(2, dtype=torch.int32, device=DEV)
     with pytest.raises(K.KernelError):
         K.prefill_attention_tc(q, q.clone(), kp, kp, z, z[:1], z.view(1, 2), 16, 2, 2, 64, 0, 1.0)
+
+
+@pytest.mark.parametrize("n_tok", [128, 256])
+def test_pair_product_dense(K, n_tok):
+    """The two-SM product (tcgen05 cta_group::2): every epilogue, partial tiles in every
+    dimension (300 tokens, 384 features = one and a half pairs of 128 rows, K = 520)."""
+    T, N, Kd = 300, 384, 520
+    x, w, wu = rnd(T, Kd, seed=1), rnd(N, Kd, seed=2, scale=0.1), rnd(N, Kd, seed=7, scale=0.1)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(3)).to(DEV)
+    want = x.double() @ w.double().t()
+    out = torch.full((T, N), 7.0, device=DEV)
+    K.gemm_tc2(x, w, out, K.EPI_STORE_F32, n_tok, bias=bias)
+    close(out, want + bias.double())
+    base = torch.randn(T, N, generator=torch.Generator().manual_seed(4)).to(DEV)
+    acc = base.clone()
+    K.gemm_tc2(x, w, acc, K.EPI_ACC_F32, n_tok)
+    close(acc, want + base.double())
+    ob = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tc2(x, w, ob, K.EPI_STORE_BF16, n_tok)
+    close(ob, want, atol=2e-2, rtol=1e-2)
+    os_ = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tc2(x, w, os_, K.EPI_SWIGLU_BF16, n_tok, w_up=wu)
+    close(os_, P.silu(want) * (x.double() @ wu.double().t()), atol=2e-2, rtol=1e-2)
+    torch.cuda.synchronize()
+    assert K.wait_errors() == {}
+
+
+@pytest.mark.parametrize("n_tok", [128, 256])
+def test_pair_product_grouped(K, n_tok):
+    """Ragged groups (empty, 1 row, exactly a tile, a tile and one) through the two-SM product."""
+    G, N, Kd = 7, 320, 264
+    counts = [0, 5, 130, 300, 1, 257, 64]
+    offs = [0]
+    for c in counts:
+        offs.append(offs[-1] + c)
+    Tt = offs[-1]
+    x, w, wu = rnd(Tt, Kd, seed=11), rnd(G, N, Kd, seed=12, scale=0.1), rnd(G, N, Kd, seed=13, scale=0.1)
+    go = torch.tensor(offs, dtype=torch.int32, device=DEV)
+    want = torch.zeros(Tt, N, dtype=torch.float64, device=DEV)
+    wantu = torch.zeros_like(want)
+    for g in range(G):
+        want[offs[g]:offs[g + 1]] = x[offs[g]:offs[g + 1]].double() @ w[g].double().t()
+        wantu[offs[g]:offs[g + 1]] = x[offs[g]:offs[g + 1]].double() @ wu[g].double().t()
+    out = torch.full((Tt, N), 7.0, device=DEV)
+    K.gemm_tc2(x, w, out, K.EPI_STORE_F32, n_tok, group_offsets=go)
+    close(out, want)
+    os_ = torch.full((Tt, N), 3.0, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tc2(x, w, os_, K.EPI_SWIGLU_BF16, n_tok, w_up=wu, group_offsets=go)
+    close(os_, P.silu(want) * wantu, atol=2e-2, rtol=1e-2)
+    torch.cuda.synchronize()
+    assert K.wait_errors() == {}
+
+
+def test_pair_product_refuses(K):
+    x, w = rnd(64, 128, seed=1), rnd(200, 128, seed=2)
+    out = torch.empty(64, 200, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(K.KernelError):
+        K.gemm_tc2(x, w, torch.empty(64, 200, device=DEV), K.EPI_STORE_F32, 64)          # token tiles of 128 or 256
+    with pytest.raises(K.KernelError):
+        K.gemm_tc2(x, w, out, K.EPI_STORE_F32, 128)                                     # float32 epilogue, bf16 out
