@@ -35,6 +35,8 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ positions, const int* __restrict__ row_req,
     const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int window, float scale,
     float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters, int max_splits) {
+    cj::after_predecessor();
+    cj::release_successor();
     constexpr int VEC = 8;                        // dims one thread owns in the value sum (one 16-byte piece)
     constexpr int COLS = HD / VEC;                // pieces of a row
     constexpr int KPAR = THREADS / COLS;          // key phases working side by side in the value sum
@@ -257,7 +259,7 @@ CJ_EXPORT int cj_decode_attention(const void* q, void* out, const void* kplane, 
             if (e != cudaSuccess) return (int)e;                                                                       \
             configured = true;                                                                                         \
         }                                                                                                              \
-        decode_attention_kernel<HD, CH><<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, \
+        cj::launch(decode_attention_kernel<HD, CH>, dim3(grid), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, \
             (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane, positions, row_req, table, table_stride,       \
             page_tokens, n_heads, n_kv, window, scale, part_acc, part_ml, counters, max_splits);                       \
     }

@@ -25,6 +25,8 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
     const TQ* __restrict__ q, TO* __restrict__ out, const TC* __restrict__ kplane, const TC* __restrict__ vplane,
     const int* __restrict__ positions, const int* __restrict__ row_req, const int* __restrict__ table,
     int table_stride, int page_tokens, int n_heads, int n_kv, int hd, int window, float scale) {
+    cj::after_predecessor();
+    cj::release_successor();
     extern __shared__ float smem[];
     float* qs = smem;                       // [hd]
     float* acc_s = smem + hd;               // [WARPS][hd]
@@ -124,7 +126,7 @@ CJ_EXPORT int cj_paged_attention(const void* q, void* out, int act_dtype, const 
     dim3 grid(T, n_heads);
     size_t smem = (size_t)(hd + WARPS * hd + 2 * WARPS) * sizeof(float);
 #define LAUNCH(TQ, TC)                                                                                             \
-    paged_attention_kernel<TQ, TC, TQ><<<grid, WARPS * 32, smem, stream>>>((const TQ*)q, (TQ*)out, (const TC*)kplane, \
+    cj::launch(paged_attention_kernel<TQ, TC, TQ>, dim3(grid), dim3(WARPS * 32), smem, stream, (const TQ*)q, (TQ*)out, (const TC*)kplane, \
         (const TC*)vplane, positions, row_req, table, table_stride, page_tokens, n_heads, n_kv, hd, window, scale)
     if (act_dtype == CJ_F32 && cache_dtype == CJ_F32) LAUNCH(float, float);
     else if (act_dtype == CJ_BF16 && cache_dtype == CJ_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(BM / (16 * MT) * 32) prefill_attention_kernel(
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ req_start, const int* __restrict__ req_prior,
     int n_requests, const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int window,
     float scale_log2) {
+    cj::after_predecessor();
+    cj::release_successor();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [BM][HD]
     __nv_bfloat16* ks = qs + BM * HD;                             // [2][BN][HD]
@@ -281,7 +283,7 @@ CJ_EXPORT int cj_prefill_attention(const void* q, void* out, const void* kplane,
             if (e != cudaSuccess) return (int)e;                                                                        \
             configured = true;                                                                                          \
         }                                                                                                               \
-        prefill_attention_kernel<HD, BM, BN, MT><<<grid, BM / (16 * MT) * 32, smem, stream>>>(                          \
+        cj::launch(prefill_attention_kernel<HD, BM, BN, MT>, dim3(grid), dim3(BM / (16 * MT) * 32), smem, stream,                           \
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane,   \
             req_start, req_prior, n_requests, table, table_stride, page_tokens, n_heads, n_kv, window, scale_log2);     \
     }

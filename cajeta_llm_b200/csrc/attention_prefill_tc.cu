@@ -115,6 +115,7 @@ struct Args {
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, Args p) {
+    cj::after_predecessor();
     // ---- which request and which 128-row tile of it (last tiles first) --------------------
     int tile = (int)gridDim.x - 1 - (int)blockIdx.x, req = -1, row0 = 0, rows = 0, first = 0;
     for (int r = 0; r < p.n_requests; ++r) {
@@ -167,6 +168,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
+    // only now may a following kernel's blocks be scheduled beside this one: a block that took
+    // tensor memory first and then waited for this kernel to end would starve this block's own
+    // allocation
+    cj::release_successor();
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
@@ -411,7 +416,7 @@ CJ_EXPORT int cj_prefill_attention_tc(const void* q, void* out, const void* kpla
     Args a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, req_start, req_prior, table, n_requests, table_stride, page_tokens,
            n_heads, n_kv, window, scale * 1.4426950408889634f, (int)plane_rows};
     dim3 grid((total_rows + BM - 1) / BM + n_requests, n_heads);
-    prefill_attention_tc_kernel<<<grid, THREADS, SMEM_TOTAL, stream>>>(mq, mk, mv, a);
+    cj::launch(prefill_attention_tc_kernel, dim3(grid), dim3(THREADS), SMEM_TOTAL, stream, mq, mk, mv, a);
     return cj::launch_status();
 }
 

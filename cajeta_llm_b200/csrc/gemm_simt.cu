@@ -36,6 +36,8 @@ struct GemmArgs {
 
 template <typename TA, typename TW, typename TC, bool SWIGLU>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmArgs p) {
+    cj::after_predecessor();
+    cj::release_successor();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     __shared__ float W2s[SWIGLU ? BK : 1][BN + 4];
@@ -152,8 +154,8 @@ int launch(const GemmArgs& p, bool swiglu, cudaStream_t stream) {
     int row_tiles = p.group_offsets ? (p.M + BM - 1) / BM + p.num_groups : (p.M + BM - 1) / BM;
     dim3 grid((p.N + BN - 1) / BN, row_tiles);
     if (grid.y > 65535) return CJ_ERR_SIZE;
-    if (swiglu) gemm_simt_kernel<TA, TW, TC, true><<<grid, 256, 0, stream>>>(p);
-    else gemm_simt_kernel<TA, TW, TC, false><<<grid, 256, 0, stream>>>(p);
+    if (swiglu) cj::launch(gemm_simt_kernel<TA, TW, TC, true>, dim3(grid), dim3(256), 0, stream, p);
+    else cj::launch(gemm_simt_kernel<TA, TW, TC, false>, dim3(grid), dim3(256), 0, stream, p);
     return launch_status();
 }
 

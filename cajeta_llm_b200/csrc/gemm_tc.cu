@@ -159,6 +159,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         fence_barrier_init();
     }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    // everything above touched only this block's own shared and tensor memory; from here on
+    // the kernel reads what earlier kernels wrote
+    cj::after_predecessor();
     if (p.group_offsets && warp == 2) {
         // token tiles before each group (a warp scan over the groups, 32 at a time)
         int carry = 0;
@@ -176,10 +180,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         if (lane == 0) tiles_before[p.groups] = carry;
     }
-    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
+    // tensor memory is held: a following kernel's blocks may now be scheduled beside this one
+    // (one that took tensor memory first and then waited for this kernel would starve it)
+    cj::release_successor();
     const uint32_t tmem_base = *tmem_slot;
     // a grouped launch knows its number of tiles only now (it depends on the routing)
     if (p.group_offsets) total_tiles = tiles_before[p.groups] * feat_tiles * p.k_splits;
@@ -389,7 +395,7 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2,
     long long total = (long long)feat_tiles * tok_tiles * a.k_splits;
     if (total > 0x7fffffffLL) return CJ_ERR_SIZE;
     int grid = (int)(total < sm_count() ? total : sm_count());
-    kern<<<grid, THREADS, S::TOTAL, stream>>>(mx, mw, mw2, a, feat_tiles, tok_tiles, (int)total);
+    cj::launch(kern, dim3(grid), dim3(THREADS), S::TOTAL, stream, mx, mw, mw2, a, feat_tiles, tok_tiles, (int)total);
     return cj::launch_status();
 }
 

@@ -137,6 +137,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
         fence_barrier_init();
     }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    cj::after_predecessor();          // from here on the kernel reads what earlier kernels wrote
     if (p.group_offsets && warp == 2) {
         int carry = 0;
         for (int g0 = 0; g0 < p.groups; g0 += 32) {
@@ -153,10 +155,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
         if (lane == 0) tiles_before[p.groups] = carry;
     }
-    if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
     tcgen05_fence_before();
     __syncthreads();
     cluster_sync_all();                           // both blocks' barriers are initialised before either is signalled
+    cj::release_successor();                      // tensor memory is held: a following kernel may be scheduled beside
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     if (p.group_offsets) total_tiles = tiles_before[p.groups] * feat_tiles;
@@ -328,6 +330,8 @@ swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         }
         fence_barrier_init();
     }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    cj::after_predecessor();          // from here on the kernel reads what earlier kernels wrote
     if (p.group_offsets && warp == 2) {
         int carry = 0;
         for (int g0 = 0; g0 < p.groups; g0 += 32) {
@@ -344,10 +348,10 @@ swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         }
         if (lane == 0) tiles_before[p.groups] = carry;
     }
-    if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
     tcgen05_fence_before();
     __syncthreads();
     cluster_sync_all();
+    cj::release_successor();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     if (p.group_offsets) total_tiles = tiles_before[p.groups] * feat_tiles;
@@ -488,13 +492,15 @@ int launch_pairs(Kern kern, int smem, long long total, cudaStream_t stream, cons
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = cj::overlap_launches() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mx, mw, mw2, a, feat_tiles, tok_tiles, (int)total);
     if (e != cudaSuccess) return (int)e;
     return cj::launch_status();

@@ -26,6 +26,8 @@ template <int TOKB>
 __global__ void __launch_bounds__(ROUTER_THREADS) router_logits_kernel(
     const float* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ shared_gate, int T, int H,
     int E, int experts_per_block, float* __restrict__ logits) {
+    cj::after_predecessor();
+    cj::release_successor();
     extern __shared__ __align__(16) float xs[];         // [TOKB][H]
     const int t0 = blockIdx.x * TOKB;
     const int n_tok = min(TOKB, T - t0);
@@ -154,6 +156,8 @@ __global__ void __launch_bounds__(SMALL_ROWS * 32) router_small_kernel(
     const float* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ shared_gate, int T, int H,
     int E, int k, int norm_topk, float* __restrict__ logits, int* __restrict__ sel, float* __restrict__ w,
     float* __restrict__ shared_scale, int* __restrict__ tickets) {
+    cj::after_predecessor();
+    cj::release_successor();
     __shared__ float probs[SMALL_ROWS][MAX_EXPERTS];
     __shared__ int is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -206,6 +210,8 @@ __global__ void __launch_bounds__(SMALL_ROWS * 32) router_small_kernel(
 __global__ void __launch_bounds__(32) router_select_kernel(
     const float* __restrict__ logits, int E, int n_cols, int k, int norm_topk, int* __restrict__ sel,
     float* __restrict__ w, float* __restrict__ shared_scale) {
+    cj::after_predecessor();
+    cj::release_successor();
     __shared__ float probs[MAX_EXPERTS];
     select_row(logits + (size_t)blockIdx.x * n_cols, blockIdx.x, E, k, norm_topk, sel, w, shared_scale, probs, threadIdx.x);
 }
@@ -217,6 +223,8 @@ constexpr int SELECT_ROWS = 4;
 __global__ void __launch_bounds__(SELECT_ROWS * 32) router_select_partials_kernel(
     const float* __restrict__ partials, int n_partials, long long partial_stride, int ld, int T, int E, int k,
     int norm_topk, int* __restrict__ sel, float* __restrict__ w, float* __restrict__ shared_scale) {
+    cj::after_predecessor();
+    cj::release_successor();
     __shared__ float probs[SELECT_ROWS][MAX_EXPERTS];
     __shared__ float row[SELECT_ROWS][MAX_EXPERTS + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -244,6 +252,8 @@ constexpr int GROUP_WARPS = 8;
 __global__ void __launch_bounds__(GROUP_WARPS * 32) moe_group_kernel(
     const int* __restrict__ sel, int n, int k, int E, int extra, int* __restrict__ offsets,
     int* __restrict__ slot_token, int* __restrict__ slot_of_pick) {
+    cj::after_predecessor();
+    cj::release_successor();
     __shared__ int lt_s[GROUP_WARPS], eq_s[GROUP_WARPS];
     const int e = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -316,7 +326,7 @@ CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* share
     const int n_cols = E + (shared_gate ? 1 : 0);
     if (T <= 32 && tickets) {
         dim3 grid_small(n_cols, (T + SMALL_ROWS - 1) / SMALL_ROWS);
-        router_small_kernel<<<grid_small, SMALL_ROWS * 32, 0, stream>>>(x, Wr, shared_gate, T, H, E, k, norm_topk, logits, sel, w,
+        cj::launch(router_small_kernel, dim3(grid_small), dim3(SMALL_ROWS * 32), 0, stream, x, Wr, shared_gate, T, H, E, k, norm_topk, logits, sel, w,
                                                                          shared_gate ? shared_scale : nullptr, tickets);
         return launch_status();
     }
@@ -337,13 +347,13 @@ CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* share
             if (e != cudaSuccess) return (int)e;                                                                     \
             configured = true;                                                                                       \
         }                                                                                                            \
-        router_logits_kernel<TB><<<grid, ROUTER_THREADS, smem, stream>>>(x, Wr, shared_gate, T, H, E, per_block, logits); \
+        cj::launch(router_logits_kernel<TB>, dim3(grid), dim3(ROUTER_THREADS), smem, stream, x, Wr, shared_gate, T, H, E, per_block, logits); \
     }
     if (tokb == 8) LAUNCH(8) else if (tokb == 4) LAUNCH(4) else if (tokb == 2) LAUNCH(2) else LAUNCH(1)
 #undef LAUNCH
     int st = launch_status();
     if (st) return st;
-    router_select_kernel<<<T, 32, 0, stream>>>(logits, E, n_cols, k, norm_topk, sel, w, shared_gate ? shared_scale : nullptr);
+    cj::launch(router_select_kernel, dim3(T), dim3(32), 0, stream, logits, E, n_cols, k, norm_topk, sel, w, shared_gate ? shared_scale : nullptr);
     return launch_status();
 }
 
@@ -353,7 +363,7 @@ CJ_EXPORT int cj_router_select(const float* partials, int n_partials, long long 
     if (T <= 0) return 0;
     if (!partials || !sel || !w || n_partials < 1) return CJ_ERR_ARG;
     if (E < 1 || E > MAX_EXPERTS || k < 1 || k > E || ld < E + (shared_scale ? 1 : 0)) return CJ_ERR_SIZE;
-    router_select_partials_kernel<<<(T + SELECT_ROWS - 1) / SELECT_ROWS, SELECT_ROWS * 32, 0, stream>>>(
+    cj::launch(router_select_partials_kernel, dim3((T + SELECT_ROWS - 1) / SELECT_ROWS), dim3(SELECT_ROWS * 32), 0, stream, 
         partials, n_partials, partial_stride, ld, T, E, k, norm_topk, sel, w, shared_scale);
     return launch_status();
 }
@@ -364,6 +374,6 @@ CJ_EXPORT int cj_moe_group(const int* sel, int n_picks, int k, int E, int extra,
                            int* slot_of_pick, cudaStream_t stream) {
     if (E < 1 || k < 1 || n_picks < 0 || extra < 0) return CJ_ERR_SIZE;
     if (!sel || !offsets || !slot_token || !slot_of_pick) return CJ_ERR_ARG;
-    moe_group_kernel<<<E + extra, GROUP_WARPS * 32, 0, stream>>>(sel, n_picks, k, E, extra, offsets, slot_token, slot_of_pick);
+    cj::launch(moe_group_kernel, dim3(E + extra), dim3(GROUP_WARPS * 32), 0, stream, sel, n_picks, k, E, extra, offsets, slot_token, slot_of_pick);
     return launch_status();
 }

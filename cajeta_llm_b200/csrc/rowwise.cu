@@ -12,6 +12,8 @@ using namespace cj;
 template <typename TW>
 __global__ void embed_gather_kernel(float* __restrict__ out, const TW* __restrict__ table,
                                     const int* __restrict__ ids, int H, int V) {
+    cj::after_predecessor();
+    cj::release_successor();
     int t = blockIdx.x;
     int id = ids[t];
     bool ok = id >= 0 && id < V;   // the host checks ids; an id out of range reads nothing
@@ -26,9 +28,9 @@ CJ_EXPORT int cj_embed_gather(float* out, const void* table, int table_dtype, co
     if (!out || !table || !ids || H <= 0 || V <= 0) return CJ_ERR_ARG;
     int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == CJ_F32)
-        embed_gather_kernel<float><<<T, threads, 0, stream>>>(out, (const float*)table, ids, H, V);
+        cj::launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, out, (const float*)table, ids, H, V);
     else if (table_dtype == CJ_BF16)
-        embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, H, V);
+        cj::launch(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, out, (const __nv_bfloat16*)table, ids, H, V);
     else
         return CJ_ERR_DTYPE;
     return launch_status();
@@ -60,6 +62,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
                                TO* __restrict__ out, float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_split,
                                const int* __restrict__ row_index, const float* __restrict__ partials, int n_partials,
                                long long partial_stride) {
+    cj::after_predecessor();
+    cj::release_successor();
     __shared__ float partial[32];
     __shared__ float scale_s;
     int r = blockIdx.x;
@@ -143,7 +147,7 @@ CJ_EXPORT int cj_rmsnorm(float* x, const float* w, float eps, int rows, int H, v
     if (partials && (row_index || n_partials < 1)) return CJ_ERR_ARG;
     int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     int per = (H + threads - 1) / threads;
-#define LAUNCH(TO, PER) rmsnorm_kernel<TO, PER><<<rows, threads, 0, stream>>>(x, w, eps, H, (TO*)out, out_f32, (__nv_bfloat16*)out_split, row_index, partials, n_partials, partial_stride)
+#define LAUNCH(TO, PER) cj::launch(rmsnorm_kernel<TO, PER>, dim3(rows), dim3(threads), 0, stream, x, w, eps, H, (TO*)out, out_f32, (__nv_bfloat16*)out_split, row_index, partials, n_partials, partial_stride)
 #define PICK(TO)                                   \
     if (per <= 4) LAUNCH(TO, 4);                   \
     else if (per <= 8) LAUNCH(TO, 8);              \
@@ -182,6 +186,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int 
                                      const int* __restrict__ table, int table_stride, int page_tokens,
                                      int n_heads, int n_kv, int hd, int rot, const float* __restrict__ inv_freq,
                                      int write_kv) {
+    cj::after_predecessor();
+    cj::release_successor();
     extern __shared__ float cs[];                 // cos[half] then sin[half]
     const int t = blockIdx.x;
     // with few rows the units of a row are shared out over gridDim.y blocks
@@ -290,7 +296,7 @@ CJ_EXPORT int cj_rope_kv_write(const float* qkv, int ld, int q_off, int k_off, i
     if (parts > 16) parts = 16;
     dim3 grid(T, parts);
 #define LAUNCH(TQ, TC)                                                                                          \
-    rope_kv_write_kernel<TQ, TC><<<grid, threads, smem, stream>>>(qkv, ld, q_off, k_off, v_off, (TQ*)q_out,     \
+    cj::launch(rope_kv_write_kernel<TQ, TC>, dim3(grid), dim3(threads), smem, stream, qkv, ld, q_off, k_off, v_off, (TQ*)q_out,     \
         (TC*)kplane, (TC*)vplane, positions, row_req, table, table_stride, page_tokens, n_heads, n_kv, hd,      \
         rotary_dim, inv_freq, write_kv)
     if (q_dtype == CJ_F32 && cache_dtype == CJ_F32) LAUNCH(float, float);
@@ -313,6 +319,8 @@ template <int VEC>
 __global__ void moe_combine_kernel(float* __restrict__ hs, const float* __restrict__ y, const int* __restrict__ slot_of_pick,
                                    const float* __restrict__ w, int k, const float* __restrict__ shared, int chunks,
                                    long long chunk_stride, const float* __restrict__ shared_scale, int H) {
+    cj::after_predecessor();
+    cj::release_successor();
     int t = blockIdx.x;
     int i = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
     if (i >= H) return;
@@ -368,8 +376,8 @@ CJ_EXPORT int cj_moe_combine(float* hs, const float* y, const int* slot_of_pick,
     int threads = H / per >= 256 ? 256 : 128;
     dim3 grid(T, (H / per + threads - 1) / threads + (H % per ? 1 : 0));
     if (grid.y > 65535) return CJ_ERR_SIZE;
-    if (vec) moe_combine_kernel<4><<<grid, threads, 0, stream>>>(hs, y, slot_of_pick, w, k, shared, chunks, chunk_stride, shared_scale, H);
-    else moe_combine_kernel<1><<<grid, threads, 0, stream>>>(hs, y, slot_of_pick, w, k, shared, chunks, chunk_stride, shared_scale, H);
+    if (vec) cj::launch(moe_combine_kernel<4>, dim3(grid), dim3(threads), 0, stream, hs, y, slot_of_pick, w, k, shared, chunks, chunk_stride, shared_scale, H);
+    else cj::launch(moe_combine_kernel<1>, dim3(grid), dim3(threads), 0, stream, hs, y, slot_of_pick, w, k, shared, chunks, chunk_stride, shared_scale, H);
     return launch_status();
 }
 
@@ -380,6 +388,8 @@ CJ_EXPORT int cj_moe_combine(float* hs, const float* y, const int* slot_of_pick,
 // ---------------------------------------------------------------------------------
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ index, int H) {
+    cj::after_predecessor();
+    cj::release_successor();
     int s = blockIdx.x;
     const T* src = x + (size_t)index[s] * H;
     T* dst = out + (size_t)s * H;
@@ -397,8 +407,8 @@ CJ_EXPORT int cj_gather_rows(void* out, const void* x, int dtype, const int* ind
     if (rows <= 0) return 0;
     if (!out || !x || !index || H <= 0) return CJ_ERR_ARG;
     int threads = H >= 1024 ? 256 : 128;
-    if (dtype == CJ_F32) gather_rows_kernel<float><<<rows, threads, 0, stream>>>((float*)out, (const float*)x, index, H);
-    else if (dtype == CJ_BF16) gather_rows_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, index, H);
+    if (dtype == CJ_F32) cj::launch(gather_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, (float*)out, (const float*)x, index, H);
+    else if (dtype == CJ_BF16) cj::launch(gather_rows_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, index, H);
     else return CJ_ERR_DTYPE;
     return launch_status();
 }
