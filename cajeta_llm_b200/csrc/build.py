@@ -214,6 +214,7 @@ def _compile_unlocked(name: str, verbose: bool) -> None:
             pass
         raise BuildError(f"nvcc failed for {LIBRARIES[name]}:\n{proc.stdout}")
     os.replace(tmp, out)
+    _drop_stale(out_dir, name, os.path.basename(out))
     if verbose:
         print(f"[cajeta_llm_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
 
