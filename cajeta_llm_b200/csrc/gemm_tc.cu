@@ -160,9 +160,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         fence_barrier_init();
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
-    // everything above touched only this block's own shared and tensor memory; from here on
-    // the kernel reads what earlier kernels wrote
-    cj::after_predecessor();
+    // Everything above touched only this block's own shared and tensor memory.  A grouped
+    // launch now reads the groups' offsets, which an earlier kernel wrote; a dense one defers
+    // the wait into its roles, so that its first weight tiles - which no kernel writes - are
+    // on their way while the kernel before is still draining.
+    const bool dense = p.group_offsets == nullptr;
+    if (!dense) cj::after_predecessor();
     if (p.group_offsets && warp == 2) {
         // token tiles before each group (a warp scan over the groups, 32 at a time)
         int carry = 0;
@@ -196,6 +199,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             tma_prefetch_descriptor(&map_x);
             tma_prefetch_descriptor(&map_w);
             if (DUAL) tma_prefetch_descriptor(&map_w2);
+            uint32_t early = 0;               // stages whose weight tiles left before the wait
+            if (dense) {
+                for (int tile = blockIdx.x; tile < total_tiles && early < STAGES; tile += gridDim.x) {
+                    TileCoord c = decode_tile<TOK_TILE, FEAT_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before);
+                    if (!c.valid) continue;
+                    for (int i = 0; i < c.n_kb && early < STAGES; ++i, ++early) {
+                        uint8_t* st = tiles + (size_t)early * S::STAGE_BYTES;
+                        mbar_expect_tx(&full_bar[early], S::STAGE_BYTES);
+                        int k0 = (c.kb_begin + i) * BK;
+                        tma_load_2d(st + S::X_BYTES, &map_w, &full_bar[early], k0, c.w_row0);
+                        if (DUAL) tma_load_2d(st + S::X_BYTES + S::W_BYTES, &map_w2, &full_bar[early], k0, c.w_row0);
+                    }
+                }
+                cj::after_predecessor();
+            }
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -203,11 +221,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (!c.valid) continue;
                 for (int i = 0; i < c.n_kb; ++i, ++it) {
                     int s = it % STAGES;
+                    uint8_t* st = tiles + (size_t)s * S::STAGE_BYTES;
+                    int k0 = (c.kb_begin + i) * BK;
+                    if (it < early) {
+                        // the stage's weights are under way and its bytes announced: only the activations are missing
+                        tma_load_2d(st, &map_x, &full_bar[s], k0, c.tok0);
+                        continue;
+                    }
                     ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, 1);
                     if (!ok) break;
-                    uint8_t* st = tiles + (size_t)s * S::STAGE_BYTES;
                     mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
-                    int k0 = (c.kb_begin + i) * BK;
                     tma_load_2d(st, &map_x, &full_bar[s], k0, c.tok0);
                     tma_load_2d(st + S::X_BYTES, &map_w, &full_bar[s], k0, c.w_row0);
                     if (DUAL) tma_load_2d(st + S::X_BYTES + S::W_BYTES, &map_w2, &full_bar[s], k0, c.w_row0);
@@ -216,6 +239,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
     } else if (warp == 1) {
         // ---- product issue -----------------------------------------------------------------
+        if (dense) cj::after_predecessor();
         if (elect_one()) {
             uint32_t it = 0, acc_it = 0;
             bool ok = true;
@@ -260,6 +284,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
     } else {
         // ---- epilogue: warps 2..5, each its own quarter of the 128 lanes --------------------
+        if (dense) cj::after_predecessor();
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;           // accumulator row of this thread
         uint32_t acc_it = 0;
