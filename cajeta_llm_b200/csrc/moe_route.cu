@@ -156,7 +156,6 @@ __global__ void __launch_bounds__(SMALL_ROWS * 32) router_small_kernel(
     const float* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ shared_gate, int T, int H,
     int E, int k, int norm_topk, float* __restrict__ logits, int* __restrict__ sel, float* __restrict__ w,
     float* __restrict__ shared_scale, int* __restrict__ tickets) {
-    cj::after_predecessor();
     cj::release_successor();
     __shared__ float probs[SMALL_ROWS][MAX_EXPERTS];
     __shared__ int is_last;
@@ -164,27 +163,46 @@ __global__ void __launch_bounds__(SMALL_ROWS * 32) router_small_kernel(
     const int n_cols = E + (shared_gate ? 1 : 0);
     const int e = blockIdx.x;
     const int t = blockIdx.y * SMALL_ROWS + warp;
+    const float* wr = e < E ? Wr + (size_t)e * H : shared_gate;
+    const bool vec = (H % 4) == 0;
+    // the weight row is written by no kernel: its loads (cold, from memory) go out before this
+    // kernel waits for the one before it
+    constexpr int PRE = 16;                       // float4 pieces of the row a lane holds ahead
+    float4 wv[PRE];
+    if (vec && t < T) {
+#pragma unroll
+        for (int u = 0; u < PRE; ++u) {
+            int j = lane * 4 + 128 * u;
+            wv[u] = j < H ? __ldg((const float4*)(wr + j)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    cj::after_predecessor();
     if (t < T) {
-        const float* wr = e < E ? Wr + (size_t)e * H : shared_gate;
         const float* xr = x + (size_t)t * H;
         float acc = 0.0f;
-        if ((H % 4) == 0) {
-            for (int j0 = lane * 4; j0 < H; j0 += 128 * 8) {
-                float4 wv[8], xv[8];
+        if (vec) {
+            float4 xv[PRE];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    int j = j0 + 128 * u;
-                    wv[u] = j < H ? __ldg((const float4*)(wr + j)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    xv[u] = j < H ? *(const float4*)(xr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
+            for (int u = 0; u < PRE; ++u) {
+                int j = lane * 4 + 128 * u;
+                xv[u] = j < H ? *(const float4*)(xr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    if (j0 + 128 * u >= H) break;
-                    acc = fmaf(wv[u].x, xv[u].x, acc);
-                    acc = fmaf(wv[u].y, xv[u].y, acc);
-                    acc = fmaf(wv[u].z, xv[u].z, acc);
-                    acc = fmaf(wv[u].w, xv[u].w, acc);
-                }
+            for (int u = 0; u < PRE; ++u) {
+                if (lane * 4 + 128 * u >= H) break;
+                acc = fmaf(wv[u].x, xv[u].x, acc);
+                acc = fmaf(wv[u].y, xv[u].y, acc);
+                acc = fmaf(wv[u].z, xv[u].z, acc);
+                acc = fmaf(wv[u].w, xv[u].w, acc);
+            }
+            // rows wider than the pieces held ahead
+            for (int j = lane * 4 + 128 * PRE; j < H; j += 128) {
+                float4 w4 = __ldg((const float4*)(wr + j));
+                float4 x4 = *(const float4*)(xr + j);
+                acc = fmaf(w4.x, x4.x, acc);
+                acc = fmaf(w4.y, x4.y, acc);
+                acc = fmaf(w4.z, x4.z, acc);
+                acc = fmaf(w4.w, x4.w, acc);
             }
         } else {
             for (int j = lane; j < H; j += 32) acc = fmaf(wr[j], xr[j], acc);
