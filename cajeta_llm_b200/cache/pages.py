@@ -217,6 +217,47 @@ class CacheBooks:
             g.grow(slot, L, n_new, pages)
         return True
 
+    # -- one token for each of several requests (a decode step), the books' hot path -------------
+    def reserve_one_each(self, slots: Sequence[int]) -> Optional[np.ndarray]:
+        """``reserve(slot, 1)`` for every slot, all or nothing over the whole list.  Returns the
+        requests' lengths (before the new token) or None when the pages are not there."""
+        idx = np.asarray(slots, dtype=np.int64)
+        if idx.size == 0:
+            return np.zeros(0, dtype=np.int64)
+        if idx.min() < 0 or idx.max() >= self.max_seqs or not self.live[idx].all():
+            bad = [int(s) for s in idx if not (0 <= s < self.max_seqs) or not self.live[s]]
+            raise CacheError(f"slot {bad[0]} holds no request")
+        L = self.length[idx]
+        if int(L.max()) + 1 > self.max_tokens_per_seq:
+            s = int(idx[int(L.argmax())])
+            raise CacheError(f"request in slot {s} would reach {int(L.max()) + 1} tokens; the limit is {self.max_tokens_per_seq}")
+        wanting = []
+        for g in self.groups:
+            short = np.nonzero(-(-(L + 1) // self.page_tokens) > g.next_page[idx])[0]
+            if short.size > g.allocator.free_count:
+                return None
+            wanting.append(short)
+        for g, short in zip(self.groups, wanting):
+            for i in short:
+                pages = g.allocator.take(1)
+                assert pages is not None
+                g.grow(int(idx[i]), int(L[i]), 1, pages)
+        return L
+
+    def commit_one_each(self, slots: Sequence[int]) -> None:
+        """``commit(slot, 1)`` for every slot."""
+        idx = np.asarray(slots, dtype=np.int64)
+        if idx.size == 0:
+            return
+        self.length[idx] += 1
+        L = self.length[idx]
+        for g in self.groups:
+            if (-(-L // self.page_tokens) > g.next_page[idx]).any():
+                raise CacheError("a token was committed without reserved pages")
+            if g.spec.window > 0:
+                for s, n in zip(idx, L):
+                    g.trim_window(int(s), int(n))
+
     def commit(self, slot: int, n_new: int) -> None:
         """The step that wrote ``n_new`` tokens is launched: advance the length and give
         back pages that have passed behind a window."""

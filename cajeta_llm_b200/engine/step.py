@@ -121,6 +121,8 @@ class ModelRunner:
         self.cuda_graphs = cuda_graphs and self.runtime.fast_kernels and self.runtime.device.type == "cuda"
         self._graphs: Dict[Tuple[int, int], _CapturedStep] = {}
         self._graph_pool = None
+        self._decode_host: Dict[Tuple[int, int], tuple] = {}   # pinned metadata of decode steps by (rows, width), reused
+        self._meta_copied = None                               # event: the last copy out of the buffer in use is over
         self.graph_replays = 0
 
     # -- requests --------------------------------------------------------------------
@@ -181,14 +183,14 @@ class ModelRunner:
         for e in entries:
             if any(w != 0 for w in e.want):
                 raise StepError(f"want index {list(e.want)} is outside the 1 tokens of the entry")
-        longest = max(self.cache.length(e.slot) + 1 for e in entries)
-        bucket = min(-(-longest // GRAPH_CONTEXT_BUCKET) * GRAPH_CONTEXT_BUCKET, self.max_tokens_per_seq)
         width = self.cache.books.max_pages_per_seq
-        all_rows = [StepEntry(e.slot, e.tokens, [0]) for e in entries]
-        host, layout = self._build_meta(all_rows, width)
+        host, layout = self._build_meta_decode(entries, width)
+        longest = max(layout[5]) + 1
+        bucket = min(-(-longest // GRAPH_CONTEXT_BUCKET) * GRAPH_CONTEXT_BUCKET, self.max_tokens_per_seq)
         key = (B, bucket)
         cap = self._graphs.get(key)
         if cap is None:
+            all_rows = [StepEntry(e.slot, e.tokens, [0]) for e in entries]
             meta = torch.empty(host.shape, dtype=torch.int32, device=self.runtime.device)
             meta.copy_(host, non_blocking=True)
             ctx = self._context(meta, layout, all_rows, max_context=bucket)
@@ -206,12 +208,12 @@ class ModelRunner:
             self._graphs[key] = _CapturedStep(graph, meta, static_logits, K.launches - before, ctx.decode_scratch)
         else:
             cap.meta.copy_(host, non_blocking=True)
+            self._meta_copied.record()         # the pinned buffer may be rewritten once this copy is over
             cap.graph.replay()
             K.launches += cap.launches
             self.graph_replays += 1
             logits = cap.logits.clone()        # the static buffer is overwritten by the next replay
-        for e in entries:
-            self.cache.commit(e.slot, 1)
+        self.cache.books.commit_one_each([e.slot for e in entries])
         self.steps_run += 1
         rows = [i for i, e in enumerate(entries) for _ in e.want]
         if rows == list(range(B)):
@@ -239,6 +241,48 @@ class ModelRunner:
             max_rows_per_request=max(len(e.tokens) for e in entries),
             max_context=max_context if max_context is not None else max(p + len(e.tokens) for p, e in zip(req_prior, entries)),
             all_single=all(len(e.tokens) == 1 for e in entries))
+
+    def _build_meta_decode(self, entries: Sequence[StepEntry], width: int):
+        """``_build_meta`` for a step in which every request brings one token and wants its
+        logits: the same checks, the same layout, without a Python loop per row, into a pinned
+        buffer that is kept (a decode step is short: what the host spends here the device
+        waits for)."""
+        cache = self.cache
+        R = len(entries)
+        slots = [e.slot for e in entries]
+        if len(set(slots)) != R:
+            raise StepError("a request appears twice in one step")
+        toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=R)
+        if toks.min() < 0 or toks.max() >= self.model.vocab:
+            bad = int(toks[(toks < 0) | (toks >= self.model.vocab)][0])
+            raise StepError(f"token id {bad} is outside the vocabulary [0, {self.model.vocab})")
+        prior = cache.books.reserve_one_each(slots)
+        if prior is None:
+            raise OutOfPages(f"step needs a new page for some of its {R} requests; free: {cache.free_pages()}")
+        G = cache.num_groups
+        kept = self._decode_host.get((R, width))
+        if kept is None:
+            sizes = [R, R, R, R + 1, R, R, R] + [R * width] * G
+            offs = [0]
+            for n in sizes:
+                offs.append(offs[-1] + n)
+            host = torch.empty((offs[-1],), dtype=torch.int32, pin_memory=True)
+            h = host.numpy()
+            rows = np.arange(R + 1, dtype=np.int32)
+            h[offs[2]:offs[3]] = rows[:R]          # row -> request, request starts and wanted rows never change
+            h[offs[3]:offs[4]] = rows
+            h[offs[6]:offs[7]] = rows[:R]
+            kept = self._decode_host[(R, width)] = (host, h, offs, rows.tolist(), torch.cuda.Event())
+        else:
+            kept[4].synchronize()              # the copy that last read this buffer is over
+        host, h, offs, rows, self._meta_copied = kept
+        h[offs[0]:offs[1]] = toks
+        h[offs[1]:offs[2]] = prior
+        h[offs[4]:offs[5]] = prior
+        h[offs[5]:offs[6]] = slots
+        for g in range(G):
+            h[offs[7 + g]:offs[8 + g]] = cache.table_rows(g, slots, width).reshape(-1)
+        return host, (offs, R, width, G, rows, prior.tolist(), slots)
 
     def _build_meta(self, entries: Sequence[StepEntry], width: Optional[int]):
         """Checks the step, reserves its pages and lays its metadata into one pinned int32

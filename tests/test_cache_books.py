@@ -124,6 +124,57 @@ def test_random_orders_lose_no_page(seed, window, page_tokens):
     assert all(f == 12 for f in b.free_pages())
 
 
+@settings(max_examples=40, deadline=None)
+@given(st.integers(0, 2 ** 31), st.sampled_from([0, 6]), st.sampled_from([2, 4]))
+def test_one_token_each_equals_one_by_one(seed, window, page_tokens):
+    """The decode step's batch calls leave the books exactly as the one-by-one calls do,
+    and refuse (changing nothing) exactly when the pages for all of them are not there."""
+    rng = random.Random(seed)
+    a = books(pages=9, window=window, page_tokens=page_tokens, max_seqs=4, ctx=30)
+    b = books(pages=9, window=window, page_tokens=page_tokens, max_seqs=4, ctx=30)
+    live = []
+    for _ in range(80):
+        op = rng.random()
+        if op < 0.2 and a.free_slots:
+            s = a.admit()
+            assert b.admit() == s
+            n = rng.randint(0, 5)
+            if n and a.reserve(s, n):
+                a.commit(s, n)
+                assert b.reserve(s, n)
+                b.commit(s, n)
+            live.append(s)
+        elif op < 0.9 and live:
+            slots = rng.sample(live, rng.randint(1, len(live)))
+            if any(int(a.length[s]) + 1 > 30 for s in slots):
+                continue
+            needs = [a.pages_needed(s, 1) for s in slots]
+            fits = a.fits(needs)
+            before = (a.free_pages(), [g.table.copy() for g in a.groups])
+            got = a.reserve_one_each(slots)
+            assert (got is not None) == fits
+            if got is None:
+                assert a.free_pages() == before[0] and all((g.table == t).all() for g, t in zip(a.groups, before[1]))
+                continue
+            assert [int(x) for x in got] == [int(b.length[s]) for s in slots]
+            a.commit_one_each(slots)
+            for s in slots:
+                assert b.reserve(s, 1)
+                b.commit(s, 1)
+        elif live:
+            s = live.pop(rng.randrange(len(live)))
+            a.release(s)
+            b.release(s)
+        a.check()
+        assert (a.length == b.length).all() and a.free_pages() == b.free_pages()
+        for ga, gb in zip(a.groups, b.groups):
+            assert (ga.first_live == gb.first_live).all() and (ga.next_page == gb.next_page).all()
+            # which page ids are drawn depends on the order of takes and returns; how many each holds does not
+            assert [len(ga.held_pages(s)) for s in live] == [len(gb.held_pages(s)) for s in live]
+    with pytest.raises(CacheError):
+        a.reserve_one_each([3] if 3 not in live else [7])
+
+
 def test_manager_groups_layers_by_their_needs():
     full, win = KvNeed(2, 16, 0), KvNeed(2, 16, 8)
     m = CacheManager([full, win, full, win, None], [None, None, None, None, StateNeed((3,))], [None, None, None, 1, None],
