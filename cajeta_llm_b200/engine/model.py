@@ -43,6 +43,16 @@ class Model:
             out[self.plan.lm_head_name] = ParamSpec((self.vocab, self.hidden))
         return out
 
+    def libraries(self) -> set:
+        """The kernel libraries this model's steps will call (embedding, norms and head included)."""
+        out = {"rowwise", "gemm_simt", "sampling"}
+        for b in self.blocks:
+            out |= b.libraries()
+        out |= self.final_norm.libraries()
+        if self.runtime.fast_kernels and self.hidden >= 128:
+            out.add("gemm_tc")
+        return out
+
     def load(self, source) -> None:
         schema = self.params()
         source.check(schema)

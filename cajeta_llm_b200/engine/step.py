@@ -119,6 +119,11 @@ class ModelRunner:
         self.max_tokens_per_seq = max_tokens_per_seq
         self.steps_run = 0
         self.cuda_graphs = cuda_graphs and self.runtime.fast_kernels and self.runtime.device.type == "cuda"
+        # what this model needs is compiled now, side by side (a library not named here is still
+        # compiled when it is first wanted)
+        if self.runtime.device.startswith("cuda"):
+            from ..csrc import build as _build
+            _build.build_all(sorted(n for n in model.libraries() if n in _build.LIBRARIES))
         self._graphs: Dict[Tuple[int, int], _CapturedStep] = {}
         self._graph_pool = None
         self._decode_host: Dict[Tuple[int, int], tuple] = {}   # pinned metadata of decode steps by (rows, width), reused

@@ -77,6 +77,16 @@ class PagedAttention(Part):
             p[self.name("o_proj.bias")] = ParamSpec((self.hidden,), role="vector")
         return p
 
+    def libraries(self) -> set:
+        libs = {"rowwise", "gemm_simt"}
+        if self.runtime.fast_kernels and self.head_dim in (64, 128):
+            libs |= {"attention_decode", "attention_prefill_tc" if self.head_dim == 128 else "attention_prefill"}
+        else:
+            libs.add("attention_paged")
+        if self.runtime.fast_kernels and self.hidden >= 128:
+            libs |= {"gemm_tc", "gemm_tc2"}
+        return libs
+
     def load(self, source) -> None:
         # q, k and v rows are stacked so that one product yields all three
         self.w_qkv = torch.cat([self.fetch(source, self.name(f"{n}_proj.weight")) for n in ("q", "k", "v")], dim=0).contiguous()

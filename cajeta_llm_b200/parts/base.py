@@ -116,6 +116,12 @@ class Part:
         """Tensor name -> what the weight file must hold under it."""
         return {}
 
+    def libraries(self) -> set:
+        """Names of the kernel libraries (``csrc/build.py``) this part's steps will call: a hint,
+        so that a model's libraries can be compiled side by side before its first step instead
+        of one after the other as they are first wanted.  Nothing breaks if a part names none."""
+        return set()
+
     def load(self, source: Any) -> None:
         """Fetch the declared tensors from ``source.get(name, spec)`` onto the device."""
         return None

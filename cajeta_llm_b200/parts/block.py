@@ -34,6 +34,12 @@ class PreNormBlock(Part):
             out.update(p.params())
         return out
 
+    def libraries(self) -> set:
+        out = set()
+        for p in self.parts():
+            out |= p.libraries()
+        return out
+
     def load(self, source) -> None:
         for p in self.parts():
             p.load(source)

@@ -54,6 +54,12 @@ class DenseSwiGLU(Part):
             self.name("down_proj.weight"): ParamSpec((self.hidden, self.inter)),
         }
 
+    def libraries(self) -> set:
+        libs = {"gemm_simt"}
+        if self.runtime.fast_kernels and self.hidden >= 128:
+            libs |= {"gemm_tc", "gemm_tc2"}
+        return libs
+
     def load(self, source) -> None:
         self.w_gate = self.fetch(source, self.name("gate_proj.weight"))
         self.w_up = self.fetch(source, self.name("up_proj.weight"))
@@ -107,6 +113,12 @@ class SparseMoE(Part):
             if self.shared_gate:
                 p[self.name("shared_expert_gate.weight")] = ParamSpec((1, self.hidden), role="vector")
         return p
+
+    def libraries(self) -> set:
+        libs = {"rowwise", "moe_route", "gemm_simt"}
+        if self.runtime.fast_kernels and self.hidden >= 128:
+            libs |= {"gemm_tc", "gemm_tc2"}
+        return libs
 
     def load(self, source) -> None:
         rt = self.runtime

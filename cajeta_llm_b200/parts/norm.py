@@ -26,6 +26,9 @@ class RMSNorm(Part):
     def params(self) -> Dict[str, ParamSpec]:
         return {self.name("weight"): ParamSpec((self.dim,), role="vector", init="ones")}
 
+    def libraries(self) -> set:
+        return {"rowwise"}
+
     def load(self, source) -> None:
         self.weight = self.fetch(source, self.name("weight"))
 
