@@ -121,7 +121,7 @@ class ModelRunner:
         self.cuda_graphs = cuda_graphs and self.runtime.fast_kernels and self.runtime.device.type == "cuda"
         # what this model needs is compiled now, side by side (a library not named here is still
         # compiled when it is first wanted)
-        if self.runtime.device.startswith("cuda"):
+        if str(self.runtime.device).startswith("cuda"):
             from ..csrc import build as _build
             _build.build_all(sorted(n for n in model.libraries() if n in _build.LIBRARIES))
         self._graphs: Dict[Tuple[int, int], _CapturedStep] = {}
