@@ -39,7 +39,7 @@ class LlmEngine:
                                   cuda_graphs=options.cuda_graphs)
         self.sampler = BatchSampler(model.runtime.device, model.vocab)
         self._scheduler = Scheduler(self.runner, self.sampler, max_batch_tokens=options.max_batch_tokens,
-                                    chunk=options.chunk, eog_token_ids=self._eog)
+                                    chunk=options.chunk, eog_token_ids=self._eog, lookahead=options.lookahead)
         self._closed = False
 
     # -- loading ---------------------------------------------------------------------

@@ -31,6 +31,7 @@ class EngineOptions:
     config: Optional[object] = None    # a ModelConfig (or config.json dict) for random weights without a folder
     verbose: bool = False
     cuda_graphs: bool = True           # replay pure decode steps of the bfloat16 path from CUDA graphs
+    lookahead: bool = True             # while all requests decode, launch the next step before the host has seen this step's tokens
 
     def validate(self) -> None:
         if self.ctx < 1:

@@ -33,7 +33,7 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Xorshift64
-from .step import StepEntry
+from .step import OutOfPages, StepEntry
 
 
 class RequestState(enum.Enum):
@@ -99,7 +99,7 @@ class Counters:
 
 class Scheduler:
     def __init__(self, runner, sampler, max_batch_tokens: int = 2048, chunk: int = 0,
-                 eog_token_ids: Sequence[int] = ()):
+                 eog_token_ids: Sequence[int] = (), lookahead: bool = True):
         """``runner`` offers admit / release / step and a ``cache`` with pages_needed,
         free_pages and length; ``sampler.sample(logits, params, rngs, histories)`` returns
         one token per row."""
@@ -110,6 +110,7 @@ class Scheduler:
         self.max_batch_tokens = max_batch_tokens
         self.chunk = chunk
         self.eog_token_ids = tuple(eog_token_ids)
+        self.lookahead = lookahead
         self.requests: Dict[int, Request] = {}
         self.waiting: List[Request] = []
         self.preempted: List[Request] = []
@@ -311,6 +312,92 @@ class Scheduler:
         """Iterate until nothing is left (or ``max_steps`` iterations, 0 = no limit)."""
         steps = 0
         while self.has_work and (max_steps <= 0 or steps < max_steps):
-            self.step_once()
-            steps += 1
+            if self._can_run_ahead():
+                steps += self._run_ahead(max_steps - steps if max_steps > 0 else 0)
+            else:
+                self.step_once()
+                steps += 1
         return steps
+
+    # -- decoding one step ahead of the host -------------------------------------------------
+    # While every running request is decoding and nothing waits, the host has nothing to decide
+    # between two steps except whether a request has ended.  The next step is then launched
+    # BEFORE the host has seen the tokens of the one in flight: the sampler leaves them on the
+    # device and the next step reads them there, so the device never waits for the host's
+    # bookkeeping.  A request that turns out to have ended (a stop token) has ridden along for
+    # one step too many; its row of that step is dropped.  Ends that can be foreseen (the
+    # budget) are: a request is only taken along while it has two tokens of budget left.
+    # Not used while a sink wants every token before the next step, nor with a repetition
+    # penalty (the sampler would need the token the host has not seen).
+    def _can_run_ahead(self) -> bool:
+        if not self.lookahead or self.sink is not None or self.waiting or self.preempted or not self.running:
+            return False
+        if not hasattr(self.runner, "step_chained") or not hasattr(self.sampler, "sample_device"):
+            return False
+        if len(self.running) > self.max_batch_tokens:
+            return False
+        for r in self.running:
+            if r.total_len - r.cached_len != 1 or r.params.repeat_penalty != 1.0:
+                return False
+            if len(r.generated) + 2 > r.params.max_new_tokens:
+                return False
+        return True
+
+    def _run_ahead(self, max_steps: int = 0) -> int:
+        """Steps while the condition above holds; returns how many it ran (at least one)."""
+        import torch
+        reqs = sorted(self.running, key=lambda r: r.admit_stamp)
+        slots = [r.slot for r in reqs]
+        params, rngs = [r.params for r in reqs], [r.rng for r in reqs]
+        n = len(reqs)
+        try:
+            logits = self.runner.step([StepEntry(slot=r.slot, tokens=[r.tokens[-1]], want=[0]) for r in reqs])
+        except OutOfPages:
+            self.step_once()               # the ordinary iteration decides whom to preempt
+            return 1
+        steps = 1
+        for r in reqs:
+            r.cached_len += 1
+        self.counters.steps += 1
+        self.counters.decode_rows += n
+        dev = self.sampler.sample_device(logits, params, rngs, [r.generated for r in reqs])
+        bufs = [torch.empty((n,), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        events = [torch.cuda.Event(), torch.cuda.Event()]
+        cur = 0
+        bufs[cur].copy_(dev, non_blocking=True)
+        events[cur].record()
+        while True:
+            # the step after the one in flight, launched before its tokens are known here
+            ahead = None
+            surely = all(len(r.generated) + 2 <= r.params.max_new_tokens for r in reqs)
+            if surely and (max_steps <= 0 or steps < max_steps):
+                try:
+                    ahead = self.runner.step_chained(slots, dev)
+                except OutOfPages:
+                    ahead = None
+            if ahead is not None:
+                dev = self.sampler.sample_device(ahead, params, rngs, [r.generated for r in reqs])
+                bufs[cur ^ 1].copy_(dev, non_blocking=True)
+                events[cur ^ 1].record()
+            # now the tokens of the step in flight
+            events[cur].synchronize()
+            tokens = bufs[cur].tolist()
+            for r, tok in zip(reqs, tokens):
+                self._consume(r, int(tok))
+            ended = [r.state == RequestState.DONE for r in reqs]
+            if ahead is None:
+                return steps
+            steps += 1
+            self.counters.steps += 1
+            self.counters.decode_rows += n - sum(ended)
+            for r, e in zip(reqs, ended):
+                if not e:
+                    r.cached_len += 1
+            cur ^= 1
+            if any(ended):
+                # the step ahead carried rows of requests that had ended: drop those rows, take the rest
+                events[cur].synchronize()
+                for r, e, tok in zip(reqs, ended, bufs[cur].tolist()):
+                    if not e:
+                        self._consume(r, int(tok))
+                return steps

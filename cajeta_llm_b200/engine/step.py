@@ -179,7 +179,19 @@ class ModelRunner:
             return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.runtime.device)
         return self.model.logits(hs, ctx.want_rows)
 
-    def _step_captured(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step_chained(self, slots: Sequence[int], device_tokens: torch.Tensor) -> Optional[torch.Tensor]:
+        """One decode step for the requests in ``slots`` whose next tokens are still on the
+        device (``device_tokens``, int32 [len(slots)], what a sampler left there for the step
+        before): the host never sees them before the launch.  Returns the logits of every row,
+        or None when this shape has no captured graph yet (the caller then takes the ordinary
+        ``step`` once).  Raises :class:`OutOfPages` like ``step``."""
+        if not self.cuda_graphs or self.cache.state:
+            return None
+        entries = [StepEntry(s, [0], [0]) for s in slots]
+        return self._step_captured(entries, device_tokens=device_tokens)
+
+    def _step_captured(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None
+                       ) -> Optional[torch.Tensor]:
         """Pure decode: logits of every row are computed by a captured graph; the wanted
         ones are returned.  The first step of a (batch, bucket) runs uncaptured and is
         then captured for the steps after it."""
@@ -194,6 +206,10 @@ class ModelRunner:
         bucket = min(-(-longest // GRAPH_CONTEXT_BUCKET) * GRAPH_CONTEXT_BUCKET, self.max_tokens_per_seq)
         key = (B, bucket)
         cap = self._graphs.get(key)
+        if cap is None and device_tokens is not None:
+            # no graph for this shape yet: hand the reserved pages' step back to the ordinary path
+            # (the pages stay reserved; the ordinary step finds them there)
+            return None
         if cap is None:
             all_rows = [StepEntry(e.slot, e.tokens, [0]) for e in entries]
             meta = torch.empty(host.shape, dtype=torch.int32, device=self.runtime.device)
@@ -214,6 +230,8 @@ class ModelRunner:
         else:
             cap.meta.copy_(host, non_blocking=True)
             self._meta_copied.record()         # the pinned buffer may be rewritten once this copy is over
+            if device_tokens is not None:
+                cap.meta[:B].copy_(device_tokens, non_blocking=True)
             cap.graph.replay()
             K.launches += cap.launches
             self.graph_replays += 1

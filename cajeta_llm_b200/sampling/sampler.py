@@ -53,13 +53,20 @@ class BatchSampler:
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[Xorshift64],
                histories: Sequence[Sequence[int]]) -> List[int]:
         """``logits``: float32 [n, vocab]; one params / stream / emitted-token history per row."""
-        n = logits.shape[0]
-        if n == 0:
+        if logits.shape[0] == 0:
             return []
+        return self.sample_device(logits, params, rngs, histories).cpu().tolist()
+
+    def sample_device(self, logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[Xorshift64],
+                      histories: Sequence[Sequence[int]]) -> torch.Tensor:
+        """The same draw, left on the device (int32 [n]): nothing waits for it here."""
+        n = logits.shape[0]
         out = torch.empty((n,), dtype=torch.int32, device=self.device)
+        if n == 0:
+            return out
         if all(p.is_greedy for p in params):
             K.argmax(logits, out)
-            return out.cpu().tolist()
+            return out
         # one sampler launch for all rows; greedy rows ride along with temperature 0
         temp = np.array([p.temperature for p in params], dtype=np.float32)
         top_k = np.array([p.top_k for p in params], dtype=np.int32)
@@ -83,7 +90,7 @@ class BatchSampler:
         history = up(np.array(flat if flat else [0], dtype=np.int32))
         K.sample(logits, up(temp), up(u), self._scratch, out, top_k=up(top_k), top_p=up(top_p), repeat_penalty=up(pen),
                  history=history, history_offsets=up(hist_off))
-        return out.cpu().tolist()
+        return out
 
     def prepared_distribution(self, n_rows: int) -> torch.Tensor:
         """The post-filter distribution of the last ``sample`` call by token id (what the

@@ -256,3 +256,36 @@ def test_real_layer_sizes_match_the_plain_implementation(tmp_path):
         r.step([StepEntry(sc, b[:20], [])])
         tail = torch.cat([r.step([StepEntry(sc, [t], [0])]) for t in b[20:]]).cpu()
         helpers.assert_close(tail, want_b[20:], dtype, f"real sizes {dtype} decode", m_b[20:])
+
+
+@pytest.mark.parametrize("name", ["A", "M"])
+def test_decoding_one_step_ahead_of_the_host_changes_no_token(name, model_dirs):
+    """While all requests decode the scheduler launches the next step before it has seen the
+    tokens of the one in flight.  Budgets that end at different steps, a stop token that ends a
+    request in the middle (its row rides along for one step and is dropped), greedy and sampled
+    rows: every request's tokens equal those of the scheduler that waits for each step."""
+    from cajeta_llm_b200.sampling.params import SamplingParams
+    cfg = helpers.CONFIGS[name]
+    vocab = cfg["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, seed=60 + n) for n in (6, 11, 19, 4)]
+
+    def run(lookahead, stop_for_second=()):
+        eng = engine_for(model_dirs[name], "bfloat16", ctx=96, max_seqs=4, lookahead=lookahead)
+        params = [SamplingParams(max_new_tokens=14, stop_token_ids=()),
+                  SamplingParams(max_new_tokens=20, stop_token_ids=tuple(stop_for_second)),
+                  SamplingParams(max_new_tokens=9, stop_token_ids=(), temperature=0.7, top_k=20, seed=5),
+                  SamplingParams(max_new_tokens=3, stop_token_ids=())]
+        ids = [eng.submit_tokens(p, sp.max_new_tokens, sp) for p, sp in zip(prompts, params)]
+        eng.run_all()
+        out = [(list(eng.request(i).generated), eng.request(i).finish_reason.value) for i in ids]
+        steps = eng.scheduler().counters.steps
+        eng.close()
+        return out, steps
+
+    base, _ = run(False)
+    stop = base[1][0][7]                         # the second request will end on this token, in the middle
+    want, steps_wait = run(False, (stop,))
+    got, steps_ahead = run(True, (stop,))
+    assert got == want
+    assert want[1][1] == "eos" and len(want[1][0]) <= 8 and [r[1] for r in want[:1] + want[2:]] == ["budget"] * 3
+    assert steps_ahead <= steps_wait + 1         # at most the one step a stopped request rode along
