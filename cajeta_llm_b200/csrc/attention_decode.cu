@@ -25,6 +25,30 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Two float32 multiply-adds in one instruction (sm_100 f32x2): the kernel is bound by the
+// number of instructions it issues, and the dot products are half of them.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 bf16x2_to_f32x2(uint32_t u) {       // the two bfloat16 halves widened
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(u << 16), "r"(u & 0xffff0000u));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ float2 unpack2(f32x2 v) {
+    float2 r;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+    return r;
+}
+
 // The chunk's keys and values are fetched with cp.async in one go (every load of the block
 // is in flight at once) into shared memory, 16-byte pieces XOR-swizzled by row so that both
 // the per-key reads of the scores and the per-column reads of the value sum are free of
@@ -47,6 +71,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     __shared__ long long bases[CHUNK];
     __shared__ float red[THREADS / 32];
     __shared__ float vsum[KPAR][HD + 4];
+    __shared__ float lsum[KPAR];
     __shared__ int is_last;
 
     const int t = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -68,17 +93,27 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
         bases[tid] = (((long long)page * n_kv + kvh) * page_tokens + key % page_tokens) * HD;
     }
     __syncthreads();
-    // all keys, then all values, on their way to shared memory
-    for (int i = tid; i < count * COLS; i += THREADS) {
-        int r = i / COLS, c = i % COLS;
-        cp_async16(ks + r * HD + ((c ^ (r & 7)) * VEC), kplane + bases[r] + c * VEC);
+    // all keys, then all values, on their way to shared memory: a thread fetches piece c of
+    // rows r0, r0 + ROWS_STEP, ... (the swizzle of a row depends on r mod 8 only, which a step
+    // of a multiple of 8 rows leaves alone, so the piece's place in the row is computed once)
+    {
+        constexpr int ROWS_STEP = THREADS / COLS;
+        static_assert(ROWS_STEP % 8 == 0, "rows a pass apart must share their swizzle");
+        const int c = tid % COLS, r0 = tid / COLS;
+        const int in_row = (c ^ (r0 & 7)) * VEC;
+#pragma unroll
+        for (int j = 0; j < CHUNK / ROWS_STEP; ++j) {
+            int r = r0 + j * ROWS_STEP;
+            if (r < count) cp_async16(ks + r * HD + in_row, kplane + bases[r] + c * VEC);
+        }
+        cp_async_commit();
+#pragma unroll
+        for (int j = 0; j < CHUNK / ROWS_STEP; ++j) {
+            int r = r0 + j * ROWS_STEP;
+            if (r < count) cp_async16(vs + r * HD + in_row, vplane + bases[r] + c * VEC);
+        }
+        cp_async_commit();
     }
-    cp_async_commit();
-    for (int i = tid; i < count * COLS; i += THREADS) {
-        int r = i / COLS, c = i % COLS;
-        cp_async16(vs + r * HD + ((c ^ (r & 7)) * VEC), vplane + bases[r] + c * VEC);
-    }
-    cp_async_commit();
 
     // scores: four lanes share a key, each with a quarter of the head's dims (its part of q in
     // registers); lane = quarter * 8 + key, so that the eight lanes of a shared-memory
@@ -88,19 +123,16 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     const int quarter = lane >> 3;
     for (int hg = 0; hg < group; ++hg) {
         const int h = kvh * group + hg;
-        float qr[QD];
+        f32x2 qr[QD / 2];                            // this lane's quarter of q, in pairs of dims
         {
             const __nv_bfloat16* qp = q + ((size_t)t * n_heads + h) * HD + quarter * QD;
 #pragma unroll
             for (int c = 0; c < QD / 8; ++c) {
                 uint4 u = *(const uint4*)(qp + c * 8);
-                const __nv_bfloat162* b2 = (const __nv_bfloat162*)&u;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float2 f = __bfloat1622float2(b2[j]);
-                    qr[c * 8 + 2 * j] = f.x;
-                    qr[c * 8 + 2 * j + 1] = f.y;
-                }
+                qr[c * 4 + 0] = bf16x2_to_f32x2(u.x);
+                qr[c * 4 + 1] = bf16x2_to_f32x2(u.y);
+                qr[c * 4 + 2] = bf16x2_to_f32x2(u.z);
+                qr[c * 4 + 3] = bf16x2_to_f32x2(u.w);
             }
         }
         if (hg == 0) cp_async_wait<1>();                        // this thread's key pieces have landed
@@ -108,22 +140,25 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
 
         float sc[CHUNK / KEYS_PER_PASS];
         float m = -INFINITY;
+        // a lane's keys are KEYS_PER_PASS apart (a multiple of 8): one swizzle for all of them
+        const __nv_bfloat16* krow = ks + (warp * 8 + (lane & 7)) * HD;
+        int in_row[QD / 8];
+#pragma unroll
+        for (int c = 0; c < QD / 8; ++c) in_row[c] = ((quarter * (QD / 8) + c) ^ (lane & 7)) * VEC;
 #pragma unroll
         for (int pass = 0; pass < CHUNK / KEYS_PER_PASS; ++pass) {
             const int key = pass * KEYS_PER_PASS + warp * 8 + (lane & 7);
-            float dot = 0.0f;
+            f32x2 d0 = 0, d1 = 0;                                   // (even dims, odd dims) sums, two chains
 #pragma unroll
             for (int c = 0; c < QD / 8; ++c) {
-                const int piece = quarter * (QD / 8) + c;
-                uint4 u = *(const uint4*)(ks + key * HD + ((piece ^ (key & 7)) * VEC));
-                const __nv_bfloat162* b2 = (const __nv_bfloat162*)&u;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float2 f = __bfloat1622float2(b2[j]);
-                    dot = fmaf(qr[c * 8 + 2 * j], f.x, dot);
-                    dot = fmaf(qr[c * 8 + 2 * j + 1], f.y, dot);
-                }
+                uint4 u = *(const uint4*)(krow + pass * KEYS_PER_PASS * HD + in_row[c]);
+                d0 = fma2(qr[c * 4 + 0], bf16x2_to_f32x2(u.x), d0);
+                d1 = fma2(qr[c * 4 + 1], bf16x2_to_f32x2(u.y), d1);
+                d0 = fma2(qr[c * 4 + 2], bf16x2_to_f32x2(u.z), d0);
+                d1 = fma2(qr[c * 4 + 3], bf16x2_to_f32x2(u.w), d1);
             }
+            float2 s0 = unpack2(d0), s1 = unpack2(d1);
+            float dot = (s0.x + s1.x) + (s0.y + s1.y);
             dot += __shfl_xor_sync(0xffffffffu, dot, 8);
             dot += __shfl_xor_sync(0xffffffffu, dot, 16);
             sc[pass] = key < count ? dot * scale : -INFINITY;     // rows past the chunk's end hold nothing
@@ -135,51 +170,45 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
         m = red[0];
 #pragma unroll
         for (int w = 1; w < THREADS / 32; ++w) m = fmaxf(m, red[w]);
-        float l = 0.0f;
 #pragma unroll
         for (int pass = 0; pass < CHUNK / KEYS_PER_PASS; ++pass) {
             const int key = pass * KEYS_PER_PASS + warp * 8 + (lane & 7);
             float e = key < count ? expf(sc[pass] - m) : 0.0f;
-            if (quarter == 0) {
-                es[key] = e;
-                l += e;
-            }
+            if (quarter == 0) es[key] = e;
         }
-        l = warp_sum(l);
         if (hg == 0) cp_async_wait<0>();                        // this thread's value pieces have landed
         __syncthreads();                                        // everyone has read red; es and values visible
-        if (lane == 0) red[warp] = l;
-        __syncthreads();
-        l = 0.0f;
-#pragma unroll
-        for (int w = 0; w < THREADS / 32; ++w) l += red[w];
 
-        // values: thread = (8 dims, key phase); the keys of its phase in order
+        // values: thread = (8 dims, key phase); the keys of its phase in order (KPAR apart, a
+        // multiple of 8: one swizzle), and with them the phase's share of the sum of e
         const int col = tid % COLS, phase = tid / COLS;
-        float acc[VEC];
-#pragma unroll
-        for (int d = 0; d < VEC; ++d) acc[d] = 0.0f;
+        static_assert(KPAR % 8 == 0, "keys of a phase must share their swizzle");
+        const __nv_bfloat16* vcol = vs + ((col ^ (phase & 7)) * VEC);
+        f32x2 acc2[VEC / 2] = {0, 0, 0, 0};
+        float lpart = 0.0f;
 #pragma unroll 4
         for (int j = phase; j < count; j += KPAR) {
             float ej = es[j];
-            uint4 u = *(const uint4*)(vs + j * HD + ((col ^ (j & 7)) * VEC));
-            const __nv_bfloat162* b2 = (const __nv_bfloat162*)&u;
-#pragma unroll
-            for (int d = 0; d < VEC / 2; ++d) {
-                float2 f = __bfloat1622float2(b2[d]);
-                acc[2 * d] = fmaf(ej, f.x, acc[2 * d]);
-                acc[2 * d + 1] = fmaf(ej, f.y, acc[2 * d + 1]);
-            }
+            lpart += ej;
+            const f32x2 e2 = pack2(ej, ej);
+            uint4 u = *(const uint4*)(vcol + j * HD);
+            acc2[0] = fma2(e2, bf16x2_to_f32x2(u.x), acc2[0]);
+            acc2[1] = fma2(e2, bf16x2_to_f32x2(u.y), acc2[1]);
+            acc2[2] = fma2(e2, bf16x2_to_f32x2(u.z), acc2[2]);
+            acc2[3] = fma2(e2, bf16x2_to_f32x2(u.w), acc2[3]);
         }
 #pragma unroll
-        for (int d = 0; d < VEC; ++d) vsum[phase][VEC * col + d] = acc[d];
+        for (int d = 0; d < VEC / 2; ++d) *(float2*)&vsum[phase][VEC * col + 2 * d] = unpack2(acc2[d]);
+        if (col == 0) lsum[phase] = lpart;
         __syncthreads();
         if (tid < HD / 2) {
             float2 a = make_float2(0.0f, 0.0f);
+            float l = 0.0f;
 #pragma unroll
             for (int ph = 0; ph < KPAR; ++ph) {
                 a.x += vsum[ph][2 * tid];
                 a.y += vsum[ph][2 * tid + 1];
+                l += lsum[ph];
             }
             if (n_splits == 1) {
                 float inv = 1.0f / l;
