@@ -258,6 +258,257 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The same chunk on the tensor cores (mma.sync m16n8k16, bf16 in, f32 out): a chunk's scores
+// and weighted values are 256 tensor instructions and a few dozen fragment loads instead of
+// thousands of multiply-adds, and ALL query heads of a kv head's group (up to 8 at a time) share
+// them - the product's 16 rows are those heads (the rest zero), its columns the chunk's 128
+// keys.  Warp w takes keys [16 w, 16 w + 16) for both products; the warps exchange row maxima
+// through shared memory and add their partial outputs there in warp order.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool valid) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(n) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *(unsigned*)&v;
+}
+// element (row, col) of a [rows][HD] bf16 tile whose 16-byte pieces are XOR-swizzled by row
+template <int HD>
+__device__ __forceinline__ const __nv_bfloat16* tile_at(const __nv_bfloat16* base, int row, int col) {
+    return base + row * HD + (((col >> 3) ^ (row & 7)) << 3) + (col & 7);
+}
+
+constexpr int TC_CHUNK = 128;
+constexpr int TC_THREADS = 256;      // 8 warps, 16 keys each
+constexpr int TC_HEADS = 8;          // query heads of a kv head a block takes at a time
+
+template <int HD>
+__global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
+    const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ kplane,
+    const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ positions, const int* __restrict__ row_req,
+    const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int head_batches,
+    int window, float scale, float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters,
+    int max_splits) {
+    cj::after_predecessor();
+    cj::release_successor();
+    constexpr int COLS = HD / 8;
+    constexpr int WARPS = TC_THREADS / 32;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;             // [128][HD] swizzled; later the warps' partial outputs
+    __nv_bfloat16* vs = ks + TC_CHUNK * HD;                   // [128][HD] swizzled
+    __nv_bfloat16* qs = vs + TC_CHUNK * HD;                   // [16][HD] swizzled: the group's heads, zero rows below
+    __shared__ long long bases[TC_CHUNK];
+    __shared__ float smax[WARPS][16];
+    __shared__ float ssum[WARPS][16];
+    __shared__ int is_last;
+
+    const int t = blockIdx.x, split = blockIdx.z;
+    const int kvh = blockIdx.y / head_batches, hb = blockIdx.y % head_batches;
+    const int group = n_heads / n_kv;
+    const int h0 = kvh * group + hb * TC_HEADS;
+    const int n_h = min(TC_HEADS, group - hb * TC_HEADS);
+    const int p = positions[t];
+    const int from = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
+    const int n_keys = p - from + 1;
+    const int n_splits = (n_keys + TC_CHUNK - 1) / TC_CHUNK;
+    if (split >= n_splits) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int key0 = from + split * TC_CHUNK;
+    const int count = min(TC_CHUNK, p - key0 + 1);
+    const int* tab = table + (size_t)row_req[t] * table_stride;
+
+    if (tid < TC_CHUNK) {
+        long long b = 0;
+        if (tid < count) {
+            int key = key0 + tid;
+            int page = tab[key / page_tokens];
+            b = (((long long)page * n_kv + kvh) * page_tokens + key % page_tokens) * HD;
+        }
+        bases[tid] = b;
+    }
+    __syncthreads();
+    {
+        // q rows (zero below the heads taken), all keys, then all values; rows past the chunk's
+        // end are filled with zeros (a stale value row times a zero weight could still be NaN)
+        constexpr int ROWS_STEP = TC_THREADS / COLS;
+        const int c = tid % COLS, r0 = tid / COLS;
+        const int in_row = (c ^ (r0 & 7)) * 8;
+        if (r0 < 16) {
+            const bool live = r0 < n_h;
+            cp_async16_zfill(qs + r0 * HD + in_row, q + ((size_t)t * n_heads + h0 + (live ? r0 : 0)) * HD + c * 8, live);
+        }
+#pragma unroll
+        for (int j = 0; j < TC_CHUNK / ROWS_STEP; ++j) {
+            int r = r0 + j * ROWS_STEP;
+            cp_async16_zfill(ks + r * HD + in_row, kplane + bases[r] + c * 8, r < count);
+        }
+        cp_async_commit();
+#pragma unroll
+        for (int j = 0; j < TC_CHUNK / ROWS_STEP; ++j) {
+            int r = r0 + j * ROWS_STEP;
+            cp_async16_zfill(vs + r * HD + in_row, vplane + bases[r] + c * 8, r < count);
+        }
+        cp_async_commit();
+    }
+    cp_async_wait<1>();
+    __syncthreads();
+
+    // ---- scores of this warp's 16 keys for the 16 rows -------------------------------------------
+    const int g = lane >> 2, t4 = lane & 3, mi = lane >> 3;
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+        unsigned qf[4], b[4];
+        ldmatrix_x4(qf, tile_at<HD>(qs, lane & 15, kk * 16 + (lane >> 4) * 8));
+        ldmatrix_x4(b, tile_at<HD>(ks, warp * 16 + (mi >> 1) * 8 + (lane & 7), kk * 16 + (mi & 1) * 8));
+        mma_bf16(s[0], qf, b[0], b[1]);
+        mma_bf16(s[1], qf, b[2], b[3]);
+    }
+    // s[j][e]: row g (e < 2) or g + 8, key warp * 16 + j * 8 + 2 t4 + (e & 1)
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const bool in = warp * 16 + j * 8 + 2 * t4 + e < count;
+            s[j][e] = in ? s[j][e] * scale : -INFINITY;
+            s[j][2 + e] = in ? s[j][2 + e] * scale : -INFINITY;
+            mx0 = fmaxf(mx0, s[j][e]);
+            mx1 = fmaxf(mx1, s[j][2 + e]);
+        }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    if (t4 == 0) { smax[warp][g] = mx0; smax[warp][g + 8] = mx1; }
+    __syncthreads();                                            // every warp is done with the keys, too
+    float m0 = smax[0][g], m1 = smax[0][g + 8];
+#pragma unroll
+    for (int w = 1; w < WARPS; ++w) { m0 = fmaxf(m0, smax[w][g]); m1 = fmaxf(m1, smax[w][g + 8]); }
+    // the chunk has at least one key, so the maxima are finite
+    unsigned pf[4];
+    float sum0, sum1;
+    {
+        float e00 = expf(s[0][0] - m0), e01 = expf(s[0][1] - m0), e02 = expf(s[0][2] - m1), e03 = expf(s[0][3] - m1);
+        float e10 = expf(s[1][0] - m0), e11 = expf(s[1][1] - m0), e12 = expf(s[1][2] - m1), e13 = expf(s[1][3] - m1);
+        sum0 = (e00 + e01) + (e10 + e11);
+        sum1 = (e02 + e03) + (e12 + e13);
+        pf[0] = pack_bf16(e00, e01);
+        pf[1] = pack_bf16(e02, e03);
+        pf[2] = pack_bf16(e10, e11);
+        pf[3] = pack_bf16(e12, e13);
+    }
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+    if (t4 == 0) { ssum[warp][g] = sum0; ssum[warp][g + 8] = sum1; }
+    cp_async_wait<0>();
+    __syncthreads();                                            // everyone's value pieces have landed
+
+    // ---- this warp's keys' share of the weighted values -----------------------------------------------
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+        unsigned b[4];
+        ldmatrix_x4_trans(b, tile_at<HD>(vs, warp * 16 + (mi & 1) * 8 + (lane & 7), dp * 16 + (mi >> 1) * 8));
+        mma_bf16(o[2 * dp], pf, b[0], b[1]);
+        mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
+    }
+    // rows below the heads taken are zero work; the first n_h rows go to shared memory (the keys'
+    // tile is free: every warp passed the barrier after its scores): [warp][row][HD] float32
+    float* osum = (float*)ks;
+    if (g < n_h) {
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i)
+            *(float2*)(osum + ((size_t)warp * TC_HEADS + g) * HD + i * 8 + 2 * t4) = make_float2(o[i][0], o[i][1]);
+    }
+    __syncthreads();
+    // ---- the chunk's result per head: warps added in order ---------------------------------------------
+    for (int i = tid; i < n_h * (HD / 2); i += TC_THREADS) {
+        const int row = i / (HD / 2), d2 = i % (HD / 2);
+        float2 a = make_float2(0.0f, 0.0f);
+        float l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            float2 v = *(const float2*)(osum + ((size_t)w * TC_HEADS + row) * HD + 2 * d2);
+            a.x += v.x;
+            a.y += v.y;
+            l += ssum[w][row];
+        }
+        const int h = h0 + row;
+        if (n_splits == 1) {
+            float inv = 1.0f / l;
+            *(__nv_bfloat162*)(out + ((size_t)t * n_heads + h) * HD + 2 * d2) = __floats2bfloat162_rn(a.x * inv, a.y * inv);
+        } else {
+            size_t slot = ((size_t)t * n_heads + h) * max_splits + split;
+            *(float2*)(part_acc + slot * HD + 2 * d2) = a;
+            if (d2 == 0) {
+                float m = smax[0][row];
+#pragma unroll
+                for (int w = 1; w < WARPS; ++w) m = fmaxf(m, smax[w][row]);
+                part_ml[slot * 2] = m;
+                part_ml[slot * 2 + 1] = l;
+            }
+        }
+    }
+    if (n_splits == 1) return;
+
+    // the last chunk of this (row, kv head, head batch) to finish merges all chunks, in chunk order
+    __syncthreads();
+    int* counter = counters + ((size_t)t * n_kv + kvh) * head_batches + hb;
+    if (tid == 0) {
+        __threadfence();
+        int done = atomicAdd(counter, 1);
+        is_last = done == n_splits - 1;
+        if (is_last) {
+            *counter = 0;
+            __threadfence();
+        }
+    }
+    __syncthreads();
+    if (!is_last) return;
+    for (int i = tid; i < n_h * (HD / 2); i += TC_THREADS) {
+        const int row = i / (HD / 2), d2 = i % (HD / 2);
+        const int h = h0 + row;
+        size_t slot0 = ((size_t)t * n_heads + h) * max_splits;
+        float M = -INFINITY;
+        for (int sidx = 0; sidx < n_splits; ++sidx) M = fmaxf(M, part_ml[(slot0 + sidx) * 2]);
+        float L = 0.0f;
+        float2 a = make_float2(0.0f, 0.0f);
+        for (int sidx = 0; sidx < n_splits; ++sidx) {
+            float f = expf(part_ml[(slot0 + sidx) * 2] - M);
+            L += part_ml[(slot0 + sidx) * 2 + 1] * f;
+            float2 v = *(const float2*)(part_acc + (slot0 + sidx) * HD + 2 * d2);
+            a.x = fmaf(v.x, f, a.x);
+            a.y = fmaf(v.y, f, a.y);
+        }
+        float inv = 1.0f / L;
+        *(__nv_bfloat162*)(out + ((size_t)t * n_heads + h) * HD + 2 * d2) = __floats2bfloat162_rn(a.x * inv, a.y * inv);
+    }
+}
+
 }  // namespace
 
 // q, out: [T, n_heads, hd] bf16; planes [pages, n_kv, page_tokens, hd] bf16.  max_context
@@ -296,6 +547,43 @@ CJ_EXPORT int cj_decode_attention(const void* q, void* out, const void* kplane, 
     else if (hd == 128) LAUNCH(128, 64)
     else if (chunk == 128) LAUNCH(64, 128)
     else LAUNCH(64, 64)
+#undef LAUNCH
+    return launch_status();
+}
+
+// The same on the tensor cores (chunks of 128 keys; up to 8 query heads of a kv head a block).
+// counters: int32 [T * n_heads] here (one per row, kv head and batch of 8 heads).
+CJ_EXPORT int cj_decode_attention_tc(const void* q, void* out, const void* kplane, const void* vplane, const int* positions,
+                                     const int* row_req, const int* table, int table_stride, int page_tokens, int T,
+                                     int n_heads, int n_kv, int hd, int window, float scale, int max_context,
+                                     float* part_acc, float* part_ml, int* counters, int max_splits, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (!q || !out || !kplane || !vplane || !positions || !row_req || !table || !part_acc || !part_ml || !counters) return CJ_ERR_ARG;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || page_tokens <= 0) return CJ_ERR_SIZE;
+    if (hd != 64 && hd != 128) return CJ_ERR_SIZE;
+    int span = window > 0 ? min(window, max_context) : max_context;
+    int splits = (span + TC_CHUNK - 1) / TC_CHUNK;
+    if (splits < 1) splits = 1;
+    const int group = n_heads / n_kv;
+    const int head_batches = (group + TC_HEADS - 1) / TC_HEADS;
+    if (splits > max_splits || splits > 65535 || (long long)n_kv * head_batches > 65535) return CJ_ERR_SIZE;
+    dim3 grid(T, n_kv * head_batches, splits);
+#define LAUNCH(HD)                                                                                                     \
+    {                                                                                                                  \
+        constexpr int smem = (2 * TC_CHUNK + 16) * HD * (int)sizeof(__nv_bfloat16);                                    \
+        static_assert(8 * TC_HEADS * HD * 4 <= TC_CHUNK * HD * 2, "the warps' partial outputs must fit the keys' tile"); \
+        static bool configured = false;                                                                                \
+        if (!configured) {                                                                                             \
+            cudaError_t e = cudaFuncSetAttribute(decode_attention_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+            if (e != cudaSuccess) return (int)e;                                                                       \
+            configured = true;                                                                                         \
+        }                                                                                                              \
+        cj::launch(decode_attention_tc_kernel<HD>, dim3(grid), dim3(TC_THREADS), smem, stream, (const __nv_bfloat16*)q, \
+            (__nv_bfloat16*)out, (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane, positions, row_req, table, \
+            table_stride, page_tokens, n_heads, n_kv, head_batches, window, scale, part_acc, part_ml, counters,        \
+            max_splits);                                                                                               \
+    }
+    if (hd == 128) LAUNCH(128) else LAUNCH(64)
 #undef LAUNCH
     return launch_status();
 }

@@ -7,6 +7,7 @@ no fallback: without a CUDA device and the built libraries these functions raise
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional
 
 import torch
@@ -382,6 +383,10 @@ def gather_rows(x: torch.Tensor, index: torch.Tensor, out: torch.Tensor) -> None
     _check(st, "gather_rows")
 
 
+# CAJETA_B200_DECODE_FMA=1: decode attention on the FMA pipe instead of the tensor cores (for comparison)
+DECODE_TENSOR_CORES = os.environ.get("CAJETA_B200_DECODE_FMA", "0") != "1"
+
+
 def decode_chunk(span: int) -> int:
     """Keys a block of the split-KV decode kernel takes.  The kernel also takes 64; measured on
     a B200 it gains nothing for a handful of rows and loses 10 % for many, so 128 it is."""
@@ -391,13 +396,26 @@ def decode_chunk(span: int) -> int:
 def decode_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
                      positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int,
                      n_heads: int, n_kv: int, head_dim: int, window: int, scale: float, max_context: int,
-                     scratch: "DecodeScratch", chunk: int = 0) -> None:
-    """Split-KV attention of few bfloat16 query rows over their cached keys (head_dim 64 or 128)."""
+                     scratch: "DecodeScratch", chunk: int = 0, tensor_cores: Optional[bool] = None) -> None:
+    """Split-KV attention of few bfloat16 query rows over their cached keys (head_dim 64 or 128).
+    ``tensor_cores``: scores and weighted values of a chunk by mma.sync (the default) or on the
+    FMA pipe (``chunk`` 64 or 128 applies to that form only)."""
     for n, t in (("q", q), ("out", out), ("k_plane", k_plane), ("v_plane", v_plane)):
         _need(t, n, torch.bfloat16)
     _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
     T = q.shape[0]
     span = min(window, max_context) if window > 0 else max_context
+    if tensor_cores is None:
+        tensor_cores = DECODE_TENSOR_CORES and chunk == 0
+    if tensor_cores:
+        splits = max(1, -(-span // 128))
+        scratch.ensure(T, n_heads, n_kv, head_dim, splits, q.device)
+        st = library("attention_decode").cj_decode_attention_tc(
+            _ptr(q), _ptr(out), _ptr(k_plane), _ptr(v_plane), _ptr(positions), _ptr(row_req), _ptr(table),
+            _i(table.stride(0)), _i(page_tokens), _i(T), _i(n_heads), _i(n_kv), _i(head_dim), _i(window), _f(scale),
+            _i(max_context), _ptr(scratch.acc), _ptr(scratch.ml), _ptr(scratch.counters), _i(scratch.splits), _stream())
+        _check(st, "decode_attention")
+        return
     chunk = chunk or decode_chunk(span)
     splits = max(1, -(-span // chunk))
     scratch.ensure(T, n_heads, n_kv, head_dim, splits, q.device)
@@ -423,7 +441,7 @@ class DecodeScratch:
             self.splits = max(splits, self.splits)
             self.acc = torch.empty((self.rows, heads, self.splits, hd), dtype=torch.float32, device=device)
             self.ml = torch.empty((self.rows, heads, self.splits, 2), dtype=torch.float32, device=device)
-            self.counters = torch.zeros((self.rows * kv,), dtype=torch.int32, device=device)
+            self.counters = torch.zeros((self.rows * heads,), dtype=torch.int32, device=device)
 
 
 def prefill_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,

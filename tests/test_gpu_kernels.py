@@ -369,11 +369,12 @@ def test_sampler_distribution_and_draws_follow_the_plain_sampler(K, V):
 
 
 @pytest.mark.parametrize("heads,n_kv,hd,page,window", [(16, 16, 128, 16, 0), (14, 2, 128, 16, 0), (6, 3, 64, 8, 0),
-                                                         (8, 4, 64, 16, 200), (4, 1, 128, 16, 130)])
-@pytest.mark.parametrize("chunk", [64, 128])
+                                                         (8, 4, 64, 16, 200), (4, 1, 128, 16, 130), (24, 2, 64, 16, 0)])
+@pytest.mark.parametrize("chunk", [64, 128, 0])
 def test_decode_attention_split_kv(K, heads, n_kv, hd, page, window, chunk):
     """Rows of very different lengths (1 key, exactly one chunk, several chunks and a
-    remainder) against the plain attention; run twice to see the arrival counters reset."""
+    remainder) against the plain attention, on the FMA pipe (chunks of 64 or 128) and on the
+    tensor cores (chunk 0); run twice to see the arrival counters reset."""
     lengths = [1, 128, 129, 700, 300, 17, 64, 65]
     dtype = torch.bfloat16
     kp, vp, table, ks, vs = paged_setup(lengths, n_kv, hd, page, dtype, seed=70)
