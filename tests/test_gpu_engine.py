@@ -289,3 +289,46 @@ def test_decoding_one_step_ahead_of_the_host_changes_no_token(name, model_dirs):
     assert got == want
     assert want[1][1] == "eos" and len(want[1][0]) <= 8 and [r[1] for r in want[:1] + want[2:]] == ["budget"] * 3
     assert steps_ahead <= steps_wait + 1         # at most the one step a stopped request rode along
+
+
+def test_full_size_float32_path_gives_the_same_logits_however_the_work_is_cut():
+    """The whole model at Qwen1.5-MoE-A2.7B sizes (24 layers, 60 experts, vocabulary 151,936,
+    ~64 GB) on the true 32-bit path: a mixed workload of 8 requests with prompts of 64 to 1,024
+    tokens, prefill portions of 256 beside decode tokens, runs through the scheduler; one
+    request's logits are the same to the bit whole, in portions and token by token (the 32-bit
+    kernels sum in an order that does not depend on the batch), and its greedy tokens inside
+    the mixed batch equal those it gives alone."""
+    from cajeta_llm_b200.engine.llm_engine import LlmEngine
+    from cajeta_llm_b200.engine.options import EngineOptions
+    from cajeta_llm_b200.engine.step import StepEntry
+    from cajeta_llm_b200.sampling.params import SamplingParams
+    if torch.cuda.mem_get_info()[0] < 80e9:
+        pytest.skip("needs 80 GB of free device memory")
+    cfg = dict(helpers.REAL_SIZES, num_hidden_layers=24, num_experts=60, vocab_size=151936)
+    eng = LlmEngine.load(EngineOptions(config=cfg, random_weights=True, seed=1, dtype="float32", ctx=1280, max_seqs=8,
+                                       block_tokens=16, max_batch_tokens=2048, chunk=256))
+    vocab = cfg["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, seed=200 + n) for n in (64, 1024, 300, 517, 129, 800, 256, 999)]
+    new = 24
+    ids = [eng.submit_tokens(p, new, SamplingParams(max_new_tokens=new, stop_token_ids=())) for p in prompts]
+    eng.run_all()
+    mixed = [list(eng.request(i).generated) for i in ids]
+    assert all(len(g) == new for g in mixed)
+    r = eng.runner
+
+    def last_logits(cuts):
+        s, pos, lg = r.admit(), 0, None
+        for n in cuts:
+            lg = r.step([StepEntry(s, prompts[1][pos:pos + n], [n - 1])])
+            pos += n
+        r.release(s)
+        return lg[-1].clone()
+
+    whole = last_logits([1024])
+    assert torch.isfinite(whole).all() and float(whole.abs().max()) > 0.1
+    assert torch.equal(whole, last_logits([256, 256, 256, 256]))
+    assert torch.equal(whole, last_logits([1000] + [1] * 24))
+    rid = eng.submit_tokens(prompts[1], new, SamplingParams(max_new_tokens=new, stop_token_ids=()))
+    eng.run_all()
+    assert list(eng.request(rid).generated) == mixed[1]
+    eng.close()
