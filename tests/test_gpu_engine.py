@@ -332,3 +332,41 @@ def test_full_size_float32_path_gives_the_same_logits_however_the_work_is_cut():
     eng.run_all()
     assert list(eng.request(rid).generated) == mixed[1]
     eng.close()
+
+
+def test_full_size_bfloat16_path_agrees_with_itself_however_the_work_is_cut():
+    """The same at serving precision (tensor-core kernels at the benchmark's shapes): all 1,024
+    positions of a prompt, whole, in portions of 256 and with the last tokens one by one (captured
+    decode steps).  Different cuts take different kernels and tile shapes, so rounding differs; a
+    row may also sit on a routing near-tie.  As everywhere in these tests, rows outside the
+    element-wise bound must stay under 2 % and still point the same way."""
+    from cajeta_llm_b200.engine.llm_engine import LlmEngine
+    from cajeta_llm_b200.engine.options import EngineOptions
+    from cajeta_llm_b200.engine.step import StepEntry
+    if torch.cuda.mem_get_info()[0] < 50e9:
+        pytest.skip("needs 50 GB of free device memory")
+    cfg = dict(helpers.REAL_SIZES, num_hidden_layers=24, num_experts=60, vocab_size=151936)
+    eng = LlmEngine.load(EngineOptions(config=cfg, random_weights=True, seed=1, dtype="bfloat16", ctx=1280, max_seqs=4,
+                                       block_tokens=16, max_batch_tokens=2048))
+    r = eng.runner
+    prompt = helpers.random_tokens(cfg["vocab_size"], 1024, seed=1224)
+
+    def all_logits(cuts):
+        s, pos, outs = r.admit(), 0, []
+        for n in cuts:
+            outs.append(r.step([StepEntry(s, prompt[pos:pos + n], list(range(n)))]).clone())
+            pos += n
+        r.release(s)
+        return torch.cat(outs)
+
+    whole = all_logits([1024])
+    assert torch.isfinite(whole).all() and float(whole.abs().max()) > 0.1
+    tol = helpers.TOL["bfloat16"]
+    for cuts in ([256, 256, 256, 256], [700, 2, 61, 237] + [1] * 24):
+        other = all_logits(cuts)
+        out_of_bound = ((whole - other).abs() > tol["atol"] + tol["rtol"] * whole.abs()).any(dim=1)
+        cosine = torch.nn.functional.cosine_similarity(whole, other, dim=1)
+        assert int(out_of_bound.sum()) <= 0.02 * whole.shape[0], (cuts[:4], int(out_of_bound.sum()))
+        assert float(cosine.min()) >= helpers.TIE_COSINE, (cuts[:4], float(cosine.min()))
+    r.check_waits()
+    eng.close()
