@@ -1,23 +1,29 @@
 // Attention for prompt portions on the 5th-generation tensor cores (tcgen05), head size 128.
 //
-// A block takes 128 query rows of one request and one query head.  Per tile of 128 keys:
+// A block takes 256 query rows of one request and one query head, as two tiles of 128 rows
+// that share every tile of 128 keys and values the block loads.  Per key tile and query tile:
 //     S = Q . K^T        tcgen05.mma, Q and K tiles in 128-byte-swizzled shared memory (TMA),
-//                        the score tile [128 x 128] float32 in tensor memory (two of them,
-//                        so that the next tile's scores are computed while this one's
-//                        softmax runs)
-//     P = exp2(S - m)    four warps, one query row per thread: the row comes out of tensor
-//                        memory with tcgen05.ld, mask / running max / sum in float32
-//                        registers, P goes to shared memory as bf16 in the K-major
-//                        swizzled layout the next product reads
-//     O += P . V         tcgen05.mma with V as an MN-major operand (V rows are keys, the
-//                        head's dims are contiguous), O [128 x 128] float32 in tensor memory
+//                        the score tile [128 x 128] float32 in tensor memory
+//     P = exp2(S - m)    four warps a query tile, one row per thread: the row comes out of
+//                        tensor memory with tcgen05.ld, mask / running max / sum in float32
+//                        registers, P goes back as bf16 into the columns its scores came from
+//     O += P . V         tcgen05.mma with P read from tensor memory and V as an MN-major
+//                        operand from shared memory (V rows are keys, the head's dims are
+//                        contiguous), O [128 x 128] float32 in tensor memory
+// The two query tiles take turns: while the four warps of one compute exponentials (16 a clock
+// on an SM, as long as both products of a tile take on the tensor core), the tensor core runs
+// the other tile's products.  A key tile is worked on as two halves of 64 keys, each a step of
+// the running softmax of its own, so that the output product over the first half runs while the
+// second half's exponentials are computed.  A half is one pass over the scores in registers
+// with the reference maximum the row has so far; its own maximum is found in the same pass, on
+// units the exponentials leave idle, and only if it moves the reference is the pass repeated.
 // The running maximum is only moved (and O rescaled, through tcgen05.ld / st) when a tile
 // raises it by more than 2^8; otherwise the old reference stays, which keeps P <= 256 and
 // the rescale rare.  Keys and values come from the cache pages by TMA, one box of
 // [16 keys x 64 dims] per page and half; a page that does not exist (a stretch before the
 // window, or past the end) is fetched at an out-of-range coordinate, which TMA fills with
-// zeros.  Roles: warp 0 TMA, warp 1 products and tensor-memory allocation, warps 2..5
-// softmax, rescale and the final normalisation.
+// zeros.  Roles: warp 0 TMA, warp 1 products and tensor-memory allocation, warps 2..5 the
+// first query tile's softmax, rescale and final normalisation, warps 6..9 the second's.
 //
 // Formula: model/PagedKvCache.cajeta:374-470 (keys [from, p], from = p + 1 - w under a
 // window; softmax with the maximum subtracted; o = sum e v / sum e).  The reference's
@@ -31,24 +37,25 @@ using namespace tc;
 namespace {
 
 constexpr int HD = 128;            // head size this kernel is written for
-constexpr int BM = 128;            // query rows a block
+constexpr int BM = 128;            // query rows a tile
+constexpr int QT = 2;              // query tiles a block
 constexpr int BN = 128;            // keys a tile
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;       // TMA warp, product warp, four softmax warps for each query tile
 constexpr int HALF_BYTES = 128 * 64 * 2;          // a [128 x 64] bf16 swizzled half tile: 16 KB
 constexpr int TILE_BYTES = 2 * HALF_BYTES;        // a [128 x 128] bf16 tile: 32 KB
 constexpr float RESCALE_THRESHOLD = 8.0f;         // in log2 units
 
-// shared memory: Q | K ring | V ring | P | barriers
+// shared memory: Q (two tiles) | K ring | V ring | barriers
 constexpr int SMEM_Q = 0;
-constexpr int SMEM_K = SMEM_Q + TILE_BYTES;
+constexpr int SMEM_K = SMEM_Q + QT * TILE_BYTES;
 constexpr int SMEM_V = SMEM_K + KV_STAGES * TILE_BYTES;
-constexpr int SMEM_P = SMEM_V + KV_STAGES * TILE_BYTES;
-constexpr int SMEM_BAR = SMEM_P + 2 * TILE_BYTES;       // two P tiles: tile i + 1 is written while the product reads tile i
+constexpr int SMEM_BAR = SMEM_V + KV_STAGES * TILE_BYTES;
 constexpr int SMEM_TOTAL = SMEM_BAR + 256 + 1024;
 
-// tensor memory columns: S0 | S1 | O
-constexpr uint32_t TM_S0 = 0, TM_S1 = 128, TM_O = 256, TM_COLS = 512;
+// tensor memory columns: scores of the two query tiles (P over the first 64 columns of its
+// scores: 128 bf16 a row), then their outputs
+constexpr uint32_t TM_S = 0, TM_O = 256, TM_COLS = 512;
 
 // instruction descriptors (kind::f16, bf16 x bf16 -> f32, M = 128, N = 128): both operands
 // K-major for S = Q K^T; B MN-major (bit 16) for O = P V
@@ -75,8 +82,59 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
           "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
 }
+// 32 consecutive 32-bit columns of this thread's lane from v[OFF .. OFF + 31]
+template <int OFF, int N>
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[N]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[OFF + 0]), "r"(v[OFF + 1]), "r"(v[OFF + 2]), "r"(v[OFF + 3]), "r"(v[OFF + 4]), "r"(v[OFF + 5]),
+          "r"(v[OFF + 6]), "r"(v[OFF + 7]), "r"(v[OFF + 8]), "r"(v[OFF + 9]), "r"(v[OFF + 10]), "r"(v[OFF + 11]),
+          "r"(v[OFF + 12]), "r"(v[OFF + 13]), "r"(v[OFF + 14]), "r"(v[OFF + 15]), "r"(v[OFF + 16]), "r"(v[OFF + 17]),
+          "r"(v[OFF + 18]), "r"(v[OFF + 19]), "r"(v[OFF + 20]), "r"(v[OFF + 21]), "r"(v[OFF + 22]), "r"(v[OFF + 23]),
+          "r"(v[OFF + 24]), "r"(v[OFF + 25]), "r"(v[OFF + 26]), "r"(v[OFF + 27]), "r"(v[OFF + 28]), "r"(v[OFF + 29]),
+          "r"(v[OFF + 30]), "r"(v[OFF + 31])
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]: A's rows are the lanes, two bf16 of consecutive k per column
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// two float32 operations in one instruction (sm_100 f32x2), and the maximum of three
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ float2 unpack2(f32x2 v) {
+    float2 r;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 
 __device__ __forceinline__ float ex2(float x) {       // 2^x, 0 for -inf
     float y;
@@ -85,8 +143,8 @@ __device__ __forceinline__ float ex2(float x) {       // 2^x, 0 for -inf
 }
 
 // 32 consecutive 32-bit columns of this thread's lane into v[OFF .. OFF + 31]
-template <int OFF>
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[128]) {
+template <int OFF, int N>
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[N]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -112,45 +170,72 @@ struct Args {
     int plane_rows;            // rows of the [pages * n_kv * page_tokens, 128] view of a cache plane
 };
 
+// What a query tile of the block covers: its rows, positions and the key tiles it needs.
+struct QueryTile {
+    int rows;          // rows of the step in this tile (0: the tile is empty)
+    int p0;            // position of its first row in the request
+    int begin, end;    // key tiles [begin, end] it needs, counted from the block's first key tile (begin > end: none)
+};
+
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, Args p) {
     cj::after_predecessor();
-    // ---- which request and which 128-row tile of it (last tiles first) --------------------
-    int tile = (int)gridDim.x - 1 - (int)blockIdx.x, req = -1, row0 = 0, rows = 0, first = 0;
-    for (int r = 0; r < p.n_requests; ++r) {
-        int lo = p.req_start[r], hi = p.req_start[r + 1];
-        int tiles = (hi - lo + BM - 1) / BM;
-        if (tile < first + tiles) {
-            req = r;
-            row0 = lo + (tile - first) * BM;
-            rows = min(BM, hi - row0);
-            break;
+    // ---- which request and which 256 rows of it -----------------------------------------------
+    // Blocks start in the order of blockIdx.y; the last rows of a request see the most keys, so
+    // the last 256 rows of every request come first, then the 256 before them, and so on: the
+    // longest blocks start first and the short ones fill the gaps at the end.
+    constexpr int BLOCK_ROWS = QT * BM;
+    int req = -1, row0 = 0, rows = 0;
+    {
+        int b = (int)blockIdx.y;
+        for (int level = 0; req < 0; ++level) {
+            bool any = false;
+            for (int r = 0; r < p.n_requests; ++r) {
+                const int lo = p.req_start[r], n = p.req_start[r + 1] - lo;
+                const int tiles = (n + BLOCK_ROWS - 1) / BLOCK_ROWS;
+                if (tiles <= level) continue;
+                any = true;
+                if (b-- == 0) {
+                    req = r;
+                    row0 = lo + (tiles - 1 - level) * BLOCK_ROWS;
+                    rows = min(BLOCK_ROWS, lo + n - row0);
+                    break;
+                }
+            }
+            if (!any) return;            // the grid has a few blocks more than there are tiles
         }
-        first += tiles;
     }
-    if (req < 0) return;
-    const int h = blockIdx.y, kvh = h / (p.n_heads / p.n_kv);
+    const int h = blockIdx.x, kvh = h / (p.n_heads / p.n_kv);
     const int p0 = p.req_prior[req] + (row0 - p.req_start[req]);
     const int p_last = p0 + rows - 1;
     const int key_from = (p.window > 0 && p0 + 1 > p.window) ? p0 + 1 - p.window : 0;
-    const int kt_begin = key_from / BN, kt_end = p_last / BN;
-    const int n_tiles = kt_end - kt_begin + 1;
+    const int kt_begin = key_from / BN;
+    QueryTile qt[QT];
+#pragma unroll
+    for (int g = 0; g < QT; ++g) {
+        qt[g].rows = max(0, min(BM, rows - g * BM));
+        qt[g].p0 = p0 + g * BM;
+        const int from = (p.window > 0 && qt[g].p0 + 1 > p.window) ? qt[g].p0 + 1 - p.window : 0;
+        qt[g].begin = from / BN - kt_begin;
+        qt[g].end = qt[g].rows > 0 ? (qt[g].p0 + qt[g].rows - 1) / BN - kt_begin : qt[g].begin - 1;
+    }
+    const int n_tiles = max(qt[0].end, qt[1].end) + 1;        // the first tile is never empty
     const int* tab = p.table + (size_t)req * p.table_stride;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + SMEM_BAR);
-    uint64_t* q_full = bars;                      // Q tile landed
+    uint64_t* q_full = bars;                      // both Q tiles landed
     uint64_t* k_full = bars + 1;                  // [KV_STAGES] K of a tile landed
-    uint64_t* k_empty = k_full + KV_STAGES;       // [KV_STAGES] the score product has read it
+    uint64_t* k_empty = k_full + KV_STAGES;       // [KV_STAGES] the score products have read it
     uint64_t* v_full = k_empty + KV_STAGES;       // [KV_STAGES] V of a tile landed
-    uint64_t* v_empty = v_full + KV_STAGES;       // [KV_STAGES] the output product has read it
-    uint64_t* s_full = v_empty + KV_STAGES;       // [2] score tile complete
-    uint64_t* s_empty = s_full + 2;               // [2] softmax has read the score tile
-    uint64_t* p_full = s_empty + 2;               // P written (and O rescaled): the PV product may go
-    uint64_t* pv_done = p_full + 1;               // the PV product has read P and updated O
-    uint32_t* tmem_slot = (uint32_t*)(pv_done + 1);
+    uint64_t* v_empty = v_full + KV_STAGES;       // [KV_STAGES] the output products have read it
+    uint64_t* s_full = v_empty + KV_STAGES;       // [QT] a query tile's scores are complete (and every product before them)
+    uint64_t* p_full = s_full + QT;               // [QT][2] P of the tile's first / last 64 keys is written (and O rescaled): that half of the output product may go
+    uint64_t* half_done = p_full + 2 * QT;        // [QT] the output product over a tile's first 64 keys is done
+    uint64_t* o_done = half_done + QT;            // [QT] its last output product is done
+    uint32_t* tmem_slot = (uint32_t*)(o_done + QT);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -159,9 +244,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1);
             mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
         }
-        for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128); }
-        mbar_init(p_full, 128);
-        mbar_init(pv_done, 1);
+        for (int g = 0; g < QT; ++g) {
+            mbar_init(&s_full[g], 1), mbar_init(&half_done[g], 1), mbar_init(&o_done[g], 1);
+            mbar_init(&p_full[2 * g], BM), mbar_init(&p_full[2 * g + 1], BM);
+        }
         fence_barrier_init();
     }
     if (warp == 1) tmem_alloc(tmem_slot, TM_COLS);
@@ -180,11 +266,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tma_prefetch_descriptor(&map_q);
             tma_prefetch_descriptor(&map_k);
             tma_prefetch_descriptor(&map_v);
-            // Q: rows [row0, row0 + 128) of the [T, heads * 128] view, columns of this head; rows
+            // Q: rows [row0, row0 + 256) of the [T, heads * 128] view, columns of this head; rows
             // past the step's end read as zero
-            mbar_expect_tx(q_full, TILE_BYTES);
-            tma_load_2d(smem + SMEM_Q, &map_q, q_full, h * HD, row0);
-            tma_load_2d(smem + SMEM_Q + HALF_BYTES, &map_q, q_full, h * HD + 64, row0);
+            mbar_expect_tx(q_full, QT * TILE_BYTES);
+            for (int g = 0; g < QT; ++g) {
+                tma_load_2d(smem + SMEM_Q + g * TILE_BYTES, &map_q, q_full, h * HD, row0 + g * BM);
+                tma_load_2d(smem + SMEM_Q + g * TILE_BYTES + HALF_BYTES, &map_q, q_full, h * HD + 64, row0 + g * BM);
+            }
             // K runs ahead of V, in the order the products want them: K0, K1, V0, K2, V1, ...
             auto load_tile = [&](int i, bool values) -> bool {
                 const int s = i % KV_STAGES;
@@ -213,161 +301,199 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
     } else if (warp == 1) {
         // ---- products ------------------------------------------------------------------------
+        // In the order issued: S_a(0) S_b(0), then per key tile i: PV_a(i) S_a(i + 1) PV_b(i) S_b(i + 1),
+        // each PV in two halves of 64 keys.  S_g(i + 1) overwrites the columns PV_g(i) reads P from;
+        // the tensor core runs one thread's products in the order they were issued.
         if (elect_one()) {
             bool ok = mbar_wait(q_full, 0, 12);
-            const uint64_t dq0 = umma_desc_sw128(smem + SMEM_Q), dq1 = umma_desc_sw128(smem + SMEM_Q + HALF_BYTES);
-            auto issue_qk = [&](int i) -> bool {
-                const int s = i % KV_STAGES, sb = i & 1;
-                if (!mbar_wait(&k_full[s], (i / KV_STAGES) & 1, 13)) return false;
-                if (!mbar_wait(&s_empty[sb], ((i >> 1) & 1) ^ 1, 14)) return false;
-                tcgen05_fence_after();
+            int p_seen[QT] = {0, 0};                  // phases of p_full consumed
+            auto uses = [&](int g, int i) { return i >= qt[g].begin && i <= qt[g].end; };
+            auto scores = [&](int g, int i) {
+                const int s = i % KV_STAGES;
+                const uint64_t dq0 = umma_desc_sw128(smem + SMEM_Q + g * TILE_BYTES);
+                const uint64_t dq1 = umma_desc_sw128(smem + SMEM_Q + g * TILE_BYTES + HALF_BYTES);
                 const uint64_t dk0 = umma_desc_sw128(smem + SMEM_K + s * TILE_BYTES);
                 const uint64_t dk1 = umma_desc_sw128(smem + SMEM_K + s * TILE_BYTES + HALF_BYTES);
-                const uint32_t acc = tmem_base + (sb ? TM_S1 : TM_S0);
+                const uint32_t acc = tmem_base + TM_S + g * BN;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_bf16(acc, dq0 + 2 * k, dk0 + 2 * k, IDESC_QK, k > 0);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_bf16(acc, dq1 + 2 * k, dk1 + 2 * k, IDESC_QK, 1);
-                umma_commit(&k_empty[s]);        // K of this tile is free
-                umma_commit(&s_full[sb]);
-                return true;
+                umma_commit(&s_full[g]);
             };
-            if (ok) ok = issue_qk(0);
-            for (int i = 0; i < n_tiles && ok; ++i) {
-                // the next tile's scores first: they run while the softmax of tile i does
-                if (i + 1 < n_tiles) { ok = issue_qk(i + 1); if (!ok) break; }
-                const int s = i % KV_STAGES;
-                ok = mbar_wait(&v_full[s], (i / KV_STAGES) & 1, 19) && mbar_wait(p_full, i & 1, 15);
-                if (!ok) break;
+            if (ok) ok = mbar_wait(&k_full[0], 0, 13);
+            if (ok) {
                 tcgen05_fence_after();
+#pragma unroll
+                for (int g = 0; g < QT; ++g)
+                    if (uses(g, 0)) scores(g, 0);
+                umma_commit(&k_empty[0]);
+            }
+            for (int i = 0; i < n_tiles && ok; ++i) {
+                const int s = i % KV_STAGES;
+                const bool next = i + 1 < n_tiles;
+                ok = mbar_wait(&v_full[s], (i / KV_STAGES) & 1, 19);
+                if (!ok) break;
                 const uint64_t dv = umma_desc_mn_sw128(smem + SMEM_V + s * TILE_BYTES);
-                const uint64_t dp0 = umma_desc_sw128(smem + SMEM_P + (i & 1) * TILE_BYTES);
-                const uint64_t dp1 = umma_desc_sw128(smem + SMEM_P + (i & 1) * TILE_BYTES + HALF_BYTES);
-                // K of this product = keys: 16 keys = two 8-row groups = 2048 bytes a step
+                bool k_there = false;
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tmem_base + TM_O, dp0 + 2 * k, dv + (uint64_t)(k * 2048 >> 4), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
+                for (int g = 0; g < QT; ++g) {
+                    if (!ok) break;
+                    if (uses(g, i)) {
+                        const uint32_t acc = tmem_base + TM_O + g * HD, pa = tmem_base + TM_S + g * BN;
+                        // the tile's first 64 keys go while the softmax works on its last 64
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tmem_base + TM_O, dp1 + 2 * k, dv + (uint64_t)((4 + k) * 2048 >> 4), IDESC_PV, 1);
-                umma_commit(&v_empty[s]);        // V of this tile is free
-                umma_commit(pv_done);            // P is free, O is updated
+                        for (int half = 0; half < 2; ++half) {
+                            ok = mbar_wait(&p_full[2 * g + half], p_seen[g] & 1, 15);
+                            if (!ok) break;
+                            tcgen05_fence_after();
+                            // K of this product = keys: 16 keys = 8 columns of P = two 8-row groups of V = 2048 bytes
+#pragma unroll
+                            for (int k = 4 * half; k < 4 * half + 4; ++k)
+                                umma_bf16_a_tmem(acc, pa + 8 * k, dv + (uint64_t)(k * 2048 >> 4), IDESC_PV, (i > qt[g].begin || k > 0) ? 1u : 0u);
+                            if (half == 0) umma_commit(&half_done[g]);
+                        }
+                        if (!ok) break;
+                        ++p_seen[g];
+                        if (i == qt[g].end) umma_commit(&o_done[g]);
+                    }
+                    if (g == QT - 1) umma_commit(&v_empty[s]);        // V of this tile is free
+                    if (next && (uses(g, i + 1) || g == QT - 1)) {
+                        if (!k_there) {
+                            ok = mbar_wait(&k_full[(i + 1) % KV_STAGES], ((i + 1) / KV_STAGES) & 1, 13);
+                            if (!ok) break;
+                            tcgen05_fence_after();
+                            k_there = true;
+                        }
+                        if (uses(g, i + 1)) scores(g, i + 1);
+                        if (g == QT - 1) umma_commit(&k_empty[(i + 1) % KV_STAGES]);   // K of the next tile is free
+                    }
+                }
             }
         }
     } else {
-        // ---- softmax: one query row per thread ---------------------------------------------------
-        const int quarter = warp & 3;
+        // ---- softmax of one query tile, one row per thread ------------------------------------------
+        const int g = (warp - 2) >> 2;
+        const int quarter = warp & 3;                      // the quarter of the tensor-memory lanes this warp may touch
         const int r = quarter * 32 + lane;
-        const int pos = p0 + r;
+        const QueryTile mine = g == 0 ? qt[0] : qt[1];
+        const int pos = mine.p0 + r;
         const int from = (p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+        const uint32_t s_addr = tmem_base + TM_S + g * BN + lane_off;
+        const uint32_t o_addr = tmem_base + TM_O + g * HD + lane_off;
         float m_ref = -INFINITY, l = 0.0f;
-        uint8_t* prow = smem + SMEM_P + r * 128;          // this row inside each [128 x 64] half
         bool ok = true;
-        for (int i = 0; i < n_tiles && ok; ++i) {
-            const int sb = i & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (i >> 1) & 1, 16));
+        const int n_mine = mine.end - mine.begin + 1;
+        for (int j = 0; j < n_mine && ok; ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[g], j & 1, 16));
             if (!ok) break;
             tcgen05_fence_after();
-            // the whole row of scores into registers; the buffer is free for the tile after next
-            uint32_t v[128];
-            const uint32_t s_addr = tmem_base + (sb ? TM_S1 : TM_S0) + lane_off;
-            tmem_ld32<0>(s_addr, v);
-            tmem_ld32<32>(s_addr + 32, v);
-            tmem_ld32<64>(s_addr + 64, v);
-            tmem_ld32<96>(s_addr + 96, v);
-            tmem_ld_wait();
-            tcgen05_fence_before();
-            mbar_arrive(&s_empty[sb]);
             // columns [lo, lo + span] of this tile are keys this row may see (span < 0: none)
-            const int kbase = (kt_begin + i) * BN;
+            const int kbase = (kt_begin + mine.begin + j) * BN;
             const int lo = max(from - kbase, 0);
             const int span = min(pos - kbase, BN - 1) - lo;
-            if (lo != 0 || span != BN - 1) {
+            // The tile in two halves of 64 keys, each a step of the running softmax of its own: the
+            // output product over the first half runs while the second is worked on.
 #pragma unroll
-                for (int c = 0; c < BN; ++c)
-                    if (!((unsigned)(c - lo) <= (unsigned)span && span >= 0)) v[c] = 0xff800000u;       // -inf
-            }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            for (int half = 0; half < 2; ++half) {
+                constexpr int HC = BN / 2;
+                uint32_t v[HC];
+                tmem_ld32<0>(s_addr + half * HC, v);
+                tmem_ld32<32>(s_addr + half * HC + 32, v);
+                tmem_ld_wait();
+                if (lo != 0 || span != BN - 1) {
 #pragma unroll
-            for (int c = 0; c < BN; c += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(v[c]));
-                mx1 = fmaxf(mx1, __uint_as_float(v[c + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(v[c + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(v[c + 3]));
-            }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;      // scale > 0
-            // the reference maximum moves only when the tile raises it by more than the threshold
-            float m_new = m_ref;
-            if (mx > m_ref + RESCALE_THRESHOLD || m_ref == -INFINITY) m_new = fmaxf(m_ref, mx);
-            const bool rescale = m_new != m_ref && m_ref != -INFINITY;
-            const float factor = rescale ? exp2f(m_ref - m_new) : 1.0f;
-            const float neg_sub = m_new == -INFINITY ? 0.0f : -m_new;
-            // P = exp2(S * scale - m) as bf16 into this tile's P buffer (the product that read
-            // it two tiles ago finished before this tile's scores were complete)
-            uint8_t* pr = prow + sb * TILE_BYTES;
-            float sum0 = 0.0f, sum1 = 0.0f;
-#pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 8) {
-                uint32_t packed[4];
-#pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                    float e0 = ex2(fmaf(__uint_as_float(v[c0 + j]), p.scale_log2, neg_sub));
-                    float e1 = ex2(fmaf(__uint_as_float(v[c0 + j + 1]), p.scale_log2, neg_sub));
-                    sum0 += e0;
-                    sum1 += e1;
-                    __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
-                    packed[j >> 1] = *(uint32_t*)&b;
+                    for (int c = 0; c < HC; ++c)
+                        if (!((unsigned)(half * HC + c - lo) <= (unsigned)span && span >= 0)) v[c] = 0xff800000u;       // -inf
                 }
-                // 8 keys = one 16-byte piece of this row's 128-byte line in half (c0 / 64)
-                uint8_t* line = pr + (c0 >> 6) * HALF_BYTES;
-                const int piece = (c0 & 63) >> 3;
-                *(uint4*)(line + ((piece ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            }
-            l = l * factor + (sum0 + sum1);
-            m_ref = m_new;
-            // the product of the tile before has read its P and updated O by now, as a rule; every
-            // phase of this barrier is waited for in turn, so that its parity stays unambiguous
-            if (i > 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1, 17));
-                if (!ok) break;
-            }
-            // rare: bring O to the new reference
-            if (__any_sync(0xffffffffu, rescale)) {
-                tcgen05_fence_after();
+                // One pass gives P = exp2(S * scale - m) as bf16 (two keys a column), the sum and the
+                // maximum of these 64 scores.  It runs with the reference maximum the row has so far;
+                // only when these keys raise that by more than the threshold (or the row had none yet)
+                // is the pass repeated with the new one, which is rare after a row's first keys.  The
+                // maximum costs no time of its own this way: it is found on other units while the
+                // exponential unit, which bounds the pass, works.
+                float m_use = m_ref, factor = 1.0f, sum;
+                bool rescale = false;
+                uint32_t packed[HC];                   // only [0, 32) is used
 #pragma unroll 1
-                for (int c0 = 0; c0 < HD; c0 += 16) {
-                    uint32_t o[16];
-                    tmem_ld16(tmem_base + TM_O + lane_off + c0, o);
-                    tmem_ld_wait();
+                for (int attempt = 0;; ++attempt) {
+                    const float neg_sub = m_use == -INFINITY ? 0.0f : -m_use;
+                    const f32x2 scale2 = pack2(p.scale_log2, p.scale_log2), sub2 = pack2(neg_sub, neg_sub);
+                    f32x2 sum2a = pack2(0.0f, 0.0f), sum2b = sum2a;
+                    float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
-                    tmem_st16(tmem_base + TM_O + lane_off + c0, o);
+                    for (int c = 0; c < HC; c += 4) {
+                        const float2 t0 = unpack2(fma2(pack2(__uint_as_float(v[c]), __uint_as_float(v[c + 1])), scale2, sub2));
+                        const float2 t1 = unpack2(fma2(pack2(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3])), scale2, sub2));
+                        const float e0 = ex2(t0.x), e1 = ex2(t0.y), e2 = ex2(t1.x), e3 = ex2(t1.y);
+                        sum2a = add2(sum2a, pack2(e0, e1));
+                        sum2b = add2(sum2b, pack2(e2, e3));
+                        __nv_bfloat162 b0 = __floats2bfloat162_rn(e0, e1), b1 = __floats2bfloat162_rn(e2, e3);
+                        packed[c >> 1] = *(uint32_t*)&b0;
+                        packed[(c >> 1) + 1] = *(uint32_t*)&b1;
+                        mx0 = max3(mx0, __uint_as_float(v[c]), __uint_as_float(v[c + 1]));
+                        mx1 = max3(mx1, __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+                    }
+                    const float2 sa = unpack2(sum2a), sb = unpack2(sum2b);
+                    sum = (sa.x + sa.y) + (sb.x + sb.y);
+                    if (attempt == 1) break;
+                    const float mx = fmaxf(mx0, mx1) * p.scale_log2;                         // scale > 0
+                    float m_new = m_ref;
+                    if (mx > m_ref + RESCALE_THRESHOLD || m_ref == -INFINITY) m_new = fmaxf(m_ref, mx);
+                    if (!__any_sync(0xffffffffu, m_new != m_ref)) break;
+                    rescale = m_new != m_ref && m_ref != -INFINITY;
+                    factor = rescale ? exp2f(m_ref - m_new) : 1.0f;
+                    m_use = m_new;
+                }
+                // the first half over columns [0, 32) of the scores, the second over [32, 64) (whose
+                // scores the first half took)
+                tmem_st32<0>(s_addr + half * (HC / 2), packed);
+                l = l * factor + sum;
+                m_ref = m_use;
+                // O may be rescaled once the product before is done: the one over the last tile's second
+                // half was done before this tile's scores were; the one over this tile's first half is
+                // waited for here (every phase in turn, as a rule long complete)
+                if (half == 1) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&half_done[g], j & 1, 17));
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                }
+                if (__any_sync(0xffffffffu, rescale)) {        // rare
+#pragma unroll 1
+                    for (int c0 = 0; c0 < HD; c0 += 16) {
+                        uint32_t o[16];
+                        tmem_ld16(o_addr + c0, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 16; ++q) o[q] = __float_as_uint(__uint_as_float(o[q]) * factor);
+                        tmem_st16(o_addr + c0, o);
+                    }
                 }
                 tmem_st_wait();
+                tcgen05_fence_before();
+                mbar_arrive(&p_full[2 * g + half]);
             }
-            // P is in shared memory (generic proxy): make it visible to the tensor core's reads
-            fence_async_smem();
-            tcgen05_fence_before();
-            mbar_arrive(p_full);
         }
-        // ---- the row's result: O / l ------------------------------------------------------------
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (n_tiles - 1) & 1, 18));
-        if (ok) {
+        // ---- the rows' results: O / l ----------------------------------------------------------------
+        if (ok && n_mine > 0) ok = __all_sync(0xffffffffu, mbar_wait(&o_done[g], 0, 18));
+        if (ok && n_mine > 0) {
             tcgen05_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.n_heads + h) * HD;
+            __nv_bfloat16* dst = p.out + ((size_t)(row0 + g * BM + r) * p.n_heads + h) * HD;
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(tmem_base + TM_O + lane_off + c0, v);
+                uint32_t o[16];
+                tmem_ld16(o_addr + c0, o);
                 tmem_ld_wait();
-                if (r < rows) {
+                if (r < mine.rows) {
                     uint4 u0, u1;
                     __nv_bfloat162* b0 = (__nv_bfloat162*)&u0;
                     __nv_bfloat162* b1 = (__nv_bfloat162*)&u1;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        b0[j] = __floats2bfloat162_rn(__uint_as_float(v[2 * j]) * inv, __uint_as_float(v[2 * j + 1]) * inv);
-                        b1[j] = __floats2bfloat162_rn(__uint_as_float(v[8 + 2 * j]) * inv, __uint_as_float(v[8 + 2 * j + 1]) * inv);
+                    for (int q = 0; q < 4; ++q) {
+                        b0[q] = __floats2bfloat162_rn(__uint_as_float(o[2 * q]) * inv, __uint_as_float(o[2 * q + 1]) * inv);
+                        b1[q] = __floats2bfloat162_rn(__uint_as_float(o[8 + 2 * q]) * inv, __uint_as_float(o[8 + 2 * q + 1]) * inv);
                     }
                     *(uint4*)(dst + c0) = u0;
                     *(uint4*)(dst + c0 + 8) = u1;
@@ -399,7 +525,7 @@ CJ_EXPORT int cj_prefill_attention_tc(const void* q, void* out, const void* kpla
     if (total_rows <= 0 || n_requests <= 0) return 0;
     if (!q || !out || !kplane || !vplane || !req_start || !req_prior || !table) return CJ_ERR_ARG;
     if (hd != HD || page_tokens != 16) return CJ_ERR_SIZE;
-    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || n_heads > 65535 || n_pages <= 0) return CJ_ERR_SIZE;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || n_pages <= 0) return CJ_ERR_SIZE;
     if (((uintptr_t)q | (uintptr_t)kplane | (uintptr_t)vplane) & 15) return CJ_ERR_ALIGN;
     const long long plane_rows = (long long)n_pages * n_kv * 16;
     if (plane_rows > 0x7fffffffLL) return CJ_ERR_SIZE;
@@ -415,7 +541,11 @@ CJ_EXPORT int cj_prefill_attention_tc(const void* q, void* out, const void* kpla
     }
     Args a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, req_start, req_prior, table, n_requests, table_stride, page_tokens,
            n_heads, n_kv, window, scale * 1.4426950408889634f, (int)plane_rows};
-    dim3 grid((total_rows + BM - 1) / BM + n_requests, n_heads);
+    // heads run fastest, so that blocks start in the order of their length (the last rows of a
+    // request see the most keys) and the heads of one group read the same keys one after another
+    const long long row_blocks = (total_rows + QT * BM - 1) / (QT * BM) + n_requests;
+    if (row_blocks > 65535) return CJ_ERR_SIZE;
+    dim3 grid(n_heads, (unsigned)row_blocks);
     cj::launch(prefill_attention_tc_kernel, dim3(grid), dim3(THREADS), SMEM_TOTAL, stream, mq, mk, mv, a);
     return cj::launch_status();
 }

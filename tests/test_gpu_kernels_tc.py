@@ -141,6 +141,45 @@ def test_prefill_attention_tcgen05(K, heads, n_kv, window):
         assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), (r, float((got - want).abs().max()))
 
 
+def test_prefill_attention_tcgen05_late_standout_key(K):
+    """A key that stands out far above the rest appears late, in the second 64 keys of a key
+    tile: rows after it must move their reference maximum there (the pass over those scores is
+    repeated and the output so far rescaled while the product over the tile's first keys may
+    still run).  The portion starts at a position that is no multiple of a tile, and the
+    kernel gives the same bits twice."""
+    from test_gpu_kernels import paged_setup
+    import math
+    dtype, hd, page, heads, n_kv = torch.bfloat16, 128, 16, 4, 2
+    total, new, late = 1100, 900, 1000                  # 1000 % 128 = 104: the tile's second half
+    kp, vp, table, ks, vs = paged_setup([total], n_kv, hd, page, dtype, seed=210)
+    g = torch.Generator().manual_seed(211)
+    q = torch.randn(new, heads, hd, generator=g)
+    kdir = ks[0][late].to(dtype).float()
+    for h in range(heads):
+        d = kdir[h // (heads // n_kv)]
+        q[late - (total - new):, h] += 40.0 * d / d.norm() * math.sqrt(hd) / d.norm()      # score about +40 at that key
+    q = q.to(dtype).to(DEV)
+    scale = 1.0 / math.sqrt(hd)
+    starts = torch.tensor([0, new], dtype=torch.int32, device=DEV)
+    prior = torch.tensor([total - new], dtype=torch.int32, device=DEV)
+    outs = []
+    for _ in range(2):
+        out = torch.full_like(q, 5.0)
+        K.prefill_attention_tc(q, out, kp, vp, starts, prior, table, page, heads, n_kv, hd, 0, scale)
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert K.prefill_attention_tc_error() == 0
+    assert torch.equal(outs[0], outs[1])
+    qq = torch.zeros(total, heads, hd, dtype=torch.float64)
+    qq[total - new:] = q.double().cpu()
+    want = P.attention(qq, ks[0].to(dtype).double(), vs[0].to(dtype).double(), 0, scale)[total - new:]
+    got = outs[0].double().cpu()
+    assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), float((got - want).abs().max())
+    # the rows after the late key do look at it almost alone
+    v_late = vs[0][late].to(dtype).double()
+    assert (want[late - (total - new) + 1][0] - v_late[0]).abs().max() < 0.05
+
+
 def test_prefill_attention_tcgen05_refuses(K):
     q = torch.zeros(4, 2, 64, dtype=torch.bfloat16, device=DEV)
     kp = torch.zeros(2, 2, 16, 64, dtype=torch.bfloat16, device=DEV)
