@@ -308,7 +308,6 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
     const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int head_batches,
     int window, float scale, float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters,
     int max_splits) {
-    cj::after_predecessor();
     cj::release_successor();
     constexpr int COLS = HD / 8;
     constexpr int WARPS = TC_THREADS / 32;
@@ -326,7 +325,10 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
     const int group = n_heads / n_kv;
     const int h0 = kvh * group + hb * TC_HEADS;
     const int n_h = min(TC_HEADS, group - hb * TC_HEADS);
-    const int p = positions[t];
+    // The step's positions and page tables were written before the step's first kernel, not by the
+    // kernel before this one: the chain position -> table -> addresses runs while that kernel
+    // drains.  (Read past L1: the buffers are the same from step to step.)
+    const int p = __ldcg(positions + t);
     const int from = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
     const int n_keys = p - from + 1;
     const int n_splits = (n_keys + TC_CHUNK - 1) / TC_CHUNK;
@@ -334,28 +336,29 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int key0 = from + split * TC_CHUNK;
     const int count = min(TC_CHUNK, p - key0 + 1);
-    const int* tab = table + (size_t)row_req[t] * table_stride;
+    const int* tab = table + (size_t)__ldcg(row_req + t) * table_stride;
 
     if (tid < TC_CHUNK) {
         long long b = 0;
         if (tid < count) {
             int key = key0 + tid;
-            int page = tab[key / page_tokens];
+            int page = __ldcg(tab + key / page_tokens);
             b = (((long long)page * n_kv + kvh) * page_tokens + key % page_tokens) * HD;
         }
         bases[tid] = b;
     }
+    // Only the row's own position was written by the kernel before this one (the rotation and
+    // cache write of this step); it lies in the row's last chunk.  The other chunks hold keys and
+    // values of earlier steps: their fetch starts while that kernel drains.
+    const bool older_keys_only = split < n_splits - 1;
+    if (!older_keys_only) cj::after_predecessor();
     __syncthreads();
+    constexpr int ROWS_STEP = TC_THREADS / COLS;
+    const int c = tid % COLS, r0 = tid / COLS;
+    const int in_row = (c ^ (r0 & 7)) * 8;
     {
-        // q rows (zero below the heads taken), all keys, then all values; rows past the chunk's
-        // end are filled with zeros (a stale value row times a zero weight could still be NaN)
-        constexpr int ROWS_STEP = TC_THREADS / COLS;
-        const int c = tid % COLS, r0 = tid / COLS;
-        const int in_row = (c ^ (r0 & 7)) * 8;
-        if (r0 < 16) {
-            const bool live = r0 < n_h;
-            cp_async16_zfill(qs + r0 * HD + in_row, q + ((size_t)t * n_heads + h0 + (live ? r0 : 0)) * HD + c * 8, live);
-        }
+        // all keys, then all values; rows past the chunk's end are filled with zeros (a stale
+        // value row times a zero weight could still be NaN)
 #pragma unroll
         for (int j = 0; j < TC_CHUNK / ROWS_STEP; ++j) {
             int r = r0 + j * ROWS_STEP;
@@ -368,6 +371,13 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
             cp_async16_zfill(vs + r * HD + in_row, vplane + bases[r] + c * 8, r < count);
         }
         cp_async_commit();
+    }
+    if (older_keys_only) cj::after_predecessor();
+    if (r0 < 16) {
+        // the queries (the kernel before wrote them): q rows, zero below the heads taken
+        uint4 qv = make_uint4(0u, 0u, 0u, 0u);
+        if (r0 < n_h) qv = __ldcg((const uint4*)(q + ((size_t)t * n_heads + h0 + r0) * HD + c * 8));
+        *(uint4*)(qs + r0 * HD + in_row) = qv;
     }
     cp_async_wait<1>();
     __syncthreads();

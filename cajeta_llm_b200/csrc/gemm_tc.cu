@@ -52,6 +52,7 @@ struct Args {
     int groups;
     int k_splits;               // > 1: each split stores its partial at out + split * split_stride
     long long split_stride;
+    int offsets_settled;        // the groups' offsets were complete before the kernel before this one began
 };
 
 template <int N_MMA, bool SWAP, bool DUAL, int STAGES>
@@ -99,7 +100,7 @@ __device__ __forceinline__ TileCoord decode_tile(const Args& p, int tile, int fe
         local -= tiles_before[group] * feat_tiles;
         f = local / n_tt;
         tt = local - f * n_tt;
-        int g_lo = p.group_offsets[group], g_hi = p.group_offsets[group + 1];
+        int g_lo = __ldcg(p.group_offsets + group), g_hi = __ldcg(p.group_offsets + group + 1);
         c.tok0 = g_lo + tt * TOK_TILE;
         c.tok_end = min(g_hi, c.tok0 + TOK_TILE);
     } else {
@@ -160,18 +161,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         fence_barrier_init();
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
-    // Everything above touched only this block's own shared and tensor memory.  A grouped
-    // launch now reads the groups' offsets, which an earlier kernel wrote; a dense one defers
-    // the wait into its roles, so that its first weight tiles - which no kernel writes - are
-    // on their way while the kernel before is still draining.
+    // Everything above touched only this block's own shared and tensor memory.  What follows
+    // reads the groups' offsets (grouped launches) and then, per role, weights and activations.
+    // Weights are written by no kernel, so the first ring of weight tiles leaves before the wait
+    // for the kernel before, while that kernel is still draining.  The offsets may be read that
+    // early only if the caller says that they were complete before the kernel before this one
+    // began (they are read past L1, which may hold an older step's values); else the block
+    // waits first.
     const bool dense = p.group_offsets == nullptr;
-    if (!dense) cj::after_predecessor();
+    const bool early_ok = dense || p.offsets_settled != 0;
+    if (!early_ok) cj::after_predecessor();
     if (p.group_offsets && warp == 2) {
         // token tiles before each group (a warp scan over the groups, 32 at a time)
         int carry = 0;
         for (int g0 = 0; g0 < p.groups; g0 += 32) {
             int g = g0 + lane;
-            int n = g < p.groups ? (p.group_offsets[g + 1] - p.group_offsets[g] + TOK_TILE - 1) / TOK_TILE : 0;
+            int n = g < p.groups ? (__ldcg(p.group_offsets + g + 1) - __ldcg(p.group_offsets + g) + TOK_TILE - 1) / TOK_TILE : 0;
             int inc = n;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -200,7 +205,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             tma_prefetch_descriptor(&map_w);
             if (DUAL) tma_prefetch_descriptor(&map_w2);
             uint32_t early = 0;               // stages whose weight tiles left before the wait
-            if (dense) {
+            if (early_ok) {
                 for (int tile = blockIdx.x; tile < total_tiles && early < STAGES; tile += gridDim.x) {
                     TileCoord c = decode_tile<TOK_TILE, FEAT_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before);
                     if (!c.valid) continue;
@@ -239,7 +244,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
     } else if (warp == 1) {
         // ---- product issue -----------------------------------------------------------------
-        if (dense) cj::after_predecessor();
+        if (early_ok) cj::after_predecessor();
         if (elect_one()) {
             uint32_t it = 0, acc_it = 0;
             bool ok = true;
@@ -284,7 +289,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
     } else {
         // ---- epilogue: warps 2..5, each its own quarter of the 128 lanes --------------------
-        if (dense) cj::after_predecessor();
+        if (early_ok) cj::after_predecessor();
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;           // accumulator row of this thread
         uint32_t acc_it = 0;
@@ -461,11 +466,14 @@ int dispatch_n(int n_mma, const CUtensorMap& mx, const CUtensorMap& mw, const CU
 // 1 = weights on the rows (tile 128 features x n_mma tokens).  epilogue: 0 float32 store,
 // 1 float32 accumulate, 2 SwiGLU to bf16 (needs w2), 3 bf16 store.  k_splits > 1 only with
 // epilogue 0: split s stores its partial sum at out + s * split_stride (the bias goes to
-// split 0).  Refuses (negative code) what it cannot run; never a wrong result.
+// split 0).  offsets_settled: non-zero if group_offsets were complete before the kernel
+// before this launch began (not merely before this launch): the kernel then reads them, and
+// sends for its first weight tiles, while that kernel is still draining.  Refuses (negative
+// code) what it cannot run; never a wrong result.
 CJ_EXPORT int cj_gemm_tc(const void* x, long long ldx, const void* w, const void* w2, const float* bias, void* out,
                          long long ldo, int tokens, int features, int K, int epilogue, int swap, int n_mma,
                          const int* group_offsets, int groups, int k_splits, long long split_stride,
-                         cudaStream_t stream) {
+                         int offsets_settled, cudaStream_t stream) {
     if (tokens <= 0 || features <= 0) return 0;
     if (!x || !w || !out || K <= 0) return CJ_ERR_ARG;
     if (K % 8 != 0 || ldx % 8 != 0) return CJ_ERR_ALIGN;               // TMA: 16-byte strides
@@ -480,7 +488,7 @@ CJ_EXPORT int cj_gemm_tc(const void* x, long long ldx, const void* w, const void
     if (!make_map_bf16(&mw, w, total_w_rows, K, K, w_box)) return CJ_ERR_ARG;
     if (w2) { if (!make_map_bf16(&mw2, w2, total_w_rows, K, K, w_box)) return CJ_ERR_ARG; }
     else mw2 = mw;
-    Args a{tokens, features, K, out, ldo, bias, group_offsets, groups, k_splits, split_stride};
+    Args a{tokens, features, K, out, ldo, bias, group_offsets, groups, k_splits, split_stride, offsets_settled};
 #define CASE(EPI, DUAL)                                                                              \
     if (swap) return dispatch_n<true, DUAL, EPI>(n_mma, mx, mw, mw2, a, stream);                      \
     else return dispatch_n<false, DUAL, EPI>(n_mma, mx, mw, mw2, a, stream);

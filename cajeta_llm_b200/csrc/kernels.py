@@ -309,7 +309,8 @@ EPI_STORE_F32, EPI_ACC_F32, EPI_SWIGLU_BF16, EPI_STORE_BF16 = 0, 1, 2, 3
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, swap: bool, n_mma: int,
             bias: Optional[torch.Tensor] = None, w_up: Optional[torch.Tensor] = None,
-            group_offsets: Optional[torch.Tensor] = None, tokens: Optional[int] = None, k_splits: int = 1) -> None:
+            group_offsets: Optional[torch.Tensor] = None, tokens: Optional[int] = None, k_splits: int = 1,
+            offsets_settled: bool = False) -> None:
     """Tensor-core product out[token, feature] (+)= x[token, :] . w[feature, :] (+ bias) in
     bfloat16 with float32 accumulation (tcgen05, TMA).
 
@@ -317,7 +318,9 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     features x ``n_mma`` (16, 32, 64, 96, 128, 160, 192, 256) tokens.  ``epilogue``: EPI_STORE_F32, EPI_ACC_F32,
     EPI_SWIGLU_BF16 (``w_up`` given), EPI_STORE_BF16.  With ``group_offsets`` the rows of
     ``x`` are sorted by group and ``w`` is [groups, features, K].  ``k_splits`` > 1 (store
-    only): ``out`` is [k_splits, tokens, features] of partial sums.
+    only): ``out`` is [k_splits, tokens, features] of partial sums.  ``offsets_settled``: the
+    kernel that wrote ``group_offsets`` is not the one launched just before this product but an
+    earlier one; the product then reads them before it waits for the kernel before it.
     """
     _need(x, "x", torch.bfloat16), _need(w, "w", torch.bfloat16), _need(out, "out")
     features, K = w.shape[-2], w.shape[-1]
@@ -339,7 +342,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     ldo = out.stride(-2)
     st = library("gemm_tc").cj_gemm_tc(
         _ptr(x), _ll(x.stride(0)), _ptr(w), _ptr(w_up), _ptr(bias), _ptr(out), _ll(ldo), _i(T), _i(features), _i(K),
-        _i(epilogue), _i(1 if swap else 0), _i(n_mma), _ptr(group_offsets), _i(G), _i(k_splits), _ll(split_stride), _stream())
+        _i(epilogue), _i(1 if swap else 0), _i(n_mma), _ptr(group_offsets), _i(G), _i(k_splits), _ll(split_stride),
+        _i(1 if offsets_settled and group_offsets is not None else 0), _stream())
     _check(st, "gemm_tc")
 
 

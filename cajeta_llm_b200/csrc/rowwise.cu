@@ -186,13 +186,15 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int 
                                      const int* __restrict__ table, int table_stride, int page_tokens,
                                      int n_heads, int n_kv, int hd, int rot, const float* __restrict__ inv_freq,
                                      int write_kv) {
-    cj::after_predecessor();
     cj::release_successor();
     extern __shared__ float cs[];                 // cos[half] then sin[half]
     const int t = blockIdx.x;
     // with few rows the units of a row are shared out over gridDim.y blocks
     const int part = blockIdx.y, parts = gridDim.y;
-    const int pos = positions[t];
+    // The step's positions and page tables were written before the step's first kernel, not by the
+    // kernel before this one: the angles and the page's address are worked out while that kernel
+    // drains.  (Read past L1: the buffers are the same from step to step.)
+    const int pos = __ldcg(positions + t);
     const float* row = qkv + (size_t)t * ld;
     const int half = rot >> 1;
     for (int d = threadIdx.x; d < half; d += blockDim.x) {
@@ -200,14 +202,15 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int 
         cs[d] = cosf(ang);
         cs[half + d] = sinf(ang);
     }
-    __syncthreads();
     size_t kv_base = 0;
     bool have_page = false;
     if (write_kv) {
-        int page = table[(size_t)row_req[t] * table_stride + pos / page_tokens];
+        int page = __ldcg(table + (size_t)__ldcg(row_req + t) * table_stride + pos / page_tokens);
         have_page = page >= 0;                     // no page: the host never schedules this
         kv_base = ((size_t)(have_page ? page : 0) * n_kv) * page_tokens * hd + (size_t)(pos % page_tokens) * hd;
     }
+    cj::after_predecessor();
+    __syncthreads();
     const bool even = (hd % 2 == 0) && (half % 2 == 0);
     if (even) {
         // rotated part of q and k: units of (head slot, dim pair below half)

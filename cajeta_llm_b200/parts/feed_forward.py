@@ -217,7 +217,7 @@ class SparseMoE(Part):
         act = torch.empty((n_slots, self.inter), dtype=rt.act_dtype, device=dev)
         project(rt, x, self.w_gate, act, w_up=self.w_up, group_offsets=offsets, a_row_index=slot_token, max_group_rows=T)
         y = torch.empty((n_slots, self.hidden), dtype=torch.float32, device=dev)
-        project(rt, act, self.w_down, y, group_offsets=offsets, max_group_rows=T)
+        project(rt, act, self.w_down, y, group_offsets=offsets, max_group_rows=T, offsets_settled=True)
 
         shared = None
         if C > 0:

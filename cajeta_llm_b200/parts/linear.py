@@ -77,11 +77,15 @@ def _pair_tile(rows: int, w: torch.Tensor, swiglu: bool, grouped: bool) -> int:
 
 def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
             accumulate: bool = False, w_up: Optional[torch.Tensor] = None, group_offsets: Optional[torch.Tensor] = None,
-            a_row_index: Optional[torch.Tensor] = None, max_group_rows: Optional[int] = None) -> None:
+            a_row_index: Optional[torch.Tensor] = None, max_group_rows: Optional[int] = None,
+            offsets_settled: bool = False) -> None:
     """``x``: [tokens, K]; ``w``: [features, K] or, with ``group_offsets``, [groups, features, K]
     where output row s belongs to the group whose range holds s and reads row
     ``a_row_index[s]`` of ``x`` (or row s).  ``w_up`` selects the SwiGLU form (``out`` in the
-    activation dtype).  ``max_group_rows`` bounds the rows of any one group when known."""
+    activation dtype).  ``max_group_rows`` bounds the rows of any one group when known.
+    ``offsets_settled``: the kernel that wrote ``group_offsets`` is not the last one launched
+    before this call's product (another kernel of this engine ran since, or this call's own
+    row gather does); the product may then read the offsets before it waits for that kernel."""
     if not _tc_ok(runtime, x, w):
         K.gemm(x, w, out, bias=bias, accumulate=accumulate, w_up=w_up, group_offsets=group_offsets, a_row_index=a_row_index)
         return
@@ -90,6 +94,7 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
         gathered = torch.empty((rows, x.shape[-1]), dtype=x.dtype, device=x.device)
         K.gather_rows(x, a_row_index, gathered)
         x = gathered
+        offsets_settled = True
     if w_up is not None:
         epi = K.EPI_SWIGLU_BF16
     elif out.dtype == torch.bfloat16:
@@ -111,10 +116,12 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
         # many rows: tiles of 256 features on pairs of SMs, each loading half of the token rows
         K.gemm_tc2(x, w, out, epi, pair_tile, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows)
     elif tile:
-        K.gemm_tc(x, w, out, epi, True, tile, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows)
+        K.gemm_tc(x, w, out, epi, True, tile, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows,
+                  offsets_settled=offsets_settled)
     else:
         n_mma = 256 if (w_up is None and w.shape[-2] >= 512) else 128
-        K.gemm_tc(x, w, out, epi, False, n_mma, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows)
+        K.gemm_tc(x, w, out, epi, False, n_mma, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows,
+                  offsets_settled=offsets_settled)
 
 
 def project_split(runtime, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
