@@ -320,7 +320,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     v[j] = __uint_as_float(v0[j]);
-                    if (EPI == EPI_SWIGLU_BF16) v[j] = cj::silu(v[j]) * __uint_as_float(v1[j]);
+                    // the result is rounded to bfloat16 (8 bits): the fast exponential and division (2 ulp of float32) do not show
+                    if (EPI == EPI_SWIGLU_BF16) v[j] = __fdividef(v[j], 1.0f + __expf(-v[j])) * __uint_as_float(v1[j]);
                 }
                 if (!SWAP) {
                     // this thread owns one token row and 16 consecutive features of it

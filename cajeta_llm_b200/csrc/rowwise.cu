@@ -135,6 +135,99 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     }
 }
 
+// The same norm with four elements a thread and load: the form for rows of a multiple of four
+// elements (16-byte loads of the row, the weight and the partial sums; 8- or 16-byte stores).
+// V = 16-byte units a thread holds in registers.
+template <typename TO> __device__ __forceinline__ void store4(TO* dst, float4 y);
+template <> __device__ __forceinline__ void store4<float>(float* dst, float4 y) { *(float4*)dst = y; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float4 y) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(y.x, y.y), b = __floats2bfloat162_rn(y.z, y.w);
+    uint2 u;
+    u.x = *(uint32_t*)&a;
+    u.y = *(uint32_t*)&b;
+    *(uint2*)dst = u;
+}
+
+__device__ __forceinline__ void write_split4(__nv_bfloat16* dst, int H, float4 y) {
+    float4 hi = make_float4(__bfloat162float(__float2bfloat16_rn(y.x)), __bfloat162float(__float2bfloat16_rn(y.y)),
+                            __bfloat162float(__float2bfloat16_rn(y.z)), __bfloat162float(__float2bfloat16_rn(y.w)));
+    float4 r1 = make_float4(y.x - hi.x, y.y - hi.y, y.z - hi.z, y.w - hi.w);
+    float4 mid = make_float4(__bfloat162float(__float2bfloat16_rn(r1.x)), __bfloat162float(__float2bfloat16_rn(r1.y)),
+                             __bfloat162float(__float2bfloat16_rn(r1.z)), __bfloat162float(__float2bfloat16_rn(r1.w)));
+    float4 lo = make_float4(r1.x - mid.x, r1.y - mid.y, r1.z - mid.z, r1.w - mid.w);
+    store4<__nv_bfloat16>(dst, hi);             // the store's rounding leaves hi and mid as they are and rounds lo
+    store4<__nv_bfloat16>(dst + H, mid);
+    store4<__nv_bfloat16>(dst + 2 * H, lo);
+}
+
+template <typename TO, int V>
+__global__ void rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ w, float eps, int H,
+                                   TO* __restrict__ out, float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_split,
+                                   const int* __restrict__ row_index, const float* __restrict__ partials, int n_partials,
+                                   long long partial_stride) {
+    cj::after_predecessor();
+    cj::release_successor();
+    __shared__ float partial[32];
+    __shared__ float scale_s;
+    const int r = blockIdx.x, n4 = H >> 2;
+    float4* src = (float4*)(x + (size_t)(row_index ? row_index[r] : r) * H);
+    const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 xv[V], wv[V];
+#pragma unroll
+    for (int q = 0; q < V; ++q) {
+        int u = threadIdx.x + q * blockDim.x;
+        xv[q] = u < n4 ? src[u] : zero;
+        wv[q] = u < n4 ? ((const float4*)w)[u] : zero;
+    }
+    if (partials) {
+        // the split sums of the product before this norm: added in split order, stored back
+        for (int s = 0; s < n_partials; ++s)
+#pragma unroll
+            for (int q = 0; q < V; ++q) {
+                int u = threadIdx.x + q * blockDim.x;
+                if (u < n4) {
+                    float4 p4 = ((const float4*)(partials + s * partial_stride + (size_t)r * H))[u];
+                    xv[q].x += p4.x; xv[q].y += p4.y; xv[q].z += p4.z; xv[q].w += p4.w;
+                }
+            }
+#pragma unroll
+        for (int q = 0; q < V; ++q) {
+            int u = threadIdx.x + q * blockDim.x;
+            if (u < n4) src[u] = xv[q];
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int q = 0; q < V; ++q) {
+        ss = fmaf(xv[q].x, xv[q].x, ss);
+        ss = fmaf(xv[q].y, xv[q].y, ss);
+        ss = fmaf(xv[q].z, xv[q].z, ss);
+        ss = fmaf(xv[q].w, xv[q].w, ss);
+    }
+    ss = warp_sum(ss);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    if (lane == 0) partial[warp] = ss;
+    __syncthreads();
+    if (warp == 0) {
+        float v = lane < nwarps ? partial[lane] : 0.0f;
+        v = warp_sum(v);
+        if (lane == 0) scale_s = 1.0f / sqrtf(v / (float)H + eps);
+    }
+    __syncthreads();
+    const float scale = scale_s;
+#pragma unroll
+    for (int q = 0; q < V; ++q) {
+        int u = threadIdx.x + q * blockDim.x;
+        if (u < n4) {
+            float4 y = make_float4(xv[q].x * scale * wv[q].x, xv[q].y * scale * wv[q].y, xv[q].z * scale * wv[q].z,
+                                   xv[q].w * scale * wv[q].w);
+            store4<TO>(out + (size_t)r * H + 4 * u, y);
+            if (out_f32) *(float4*)(out_f32 + (size_t)r * H + 4 * u) = y;
+            if (out_split) write_split4(out_split + (size_t)r * 3 * H + 4 * u, H, y);
+        }
+    }
+}
+
 // partials (optional): [n_partials][rows][H] float32 with partial_stride elements between
 // them; x[r] += sum of its partials first (the residual add of a product that was split
 // along K), and x keeps the sum.  Not combined with row_index.  out_split (optional):
@@ -145,6 +238,25 @@ CJ_EXPORT int cj_rmsnorm(float* x, const float* w, float eps, int rows, int H, v
     if (rows <= 0) return 0;
     if (!x || !w || !out || H <= 0) return CJ_ERR_ARG;
     if (partials && (row_index || n_partials < 1)) return CJ_ERR_ARG;
+    // rows of a multiple of four elements, every pointer on a 16-byte boundary: four elements a load
+    const bool aligned = ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)out) | ((uintptr_t)out_f32) | ((uintptr_t)out_split)
+                           | ((uintptr_t)partials)) & 15) == 0;
+    if (H % 4 == 0 && H <= 8192 && aligned && (!partials || partial_stride % 4 == 0)) {
+        const int n4 = H / 4;
+        int vthreads = n4 >= 512 ? 512 : ((n4 + 31) / 32) * 32;
+        int v = (n4 + vthreads - 1) / vthreads;
+#define LAUNCHV(TO, V) cj::launch(rmsnorm_vec_kernel<TO, V>, dim3(rows), dim3(vthreads), 0, stream, x, w, eps, H, (TO*)out, out_f32, (__nv_bfloat16*)out_split, row_index, partials, n_partials, partial_stride)
+#define PICKV(TO)                                  \
+    if (v <= 1) LAUNCHV(TO, 1);                    \
+    else if (v <= 2) LAUNCHV(TO, 2);               \
+    else LAUNCHV(TO, 4)
+        if (out_dtype == CJ_F32) { PICKV(float); }
+        else if (out_dtype == CJ_BF16) { PICKV(__nv_bfloat16); }
+        else return CJ_ERR_DTYPE;
+#undef PICKV
+#undef LAUNCHV
+        return launch_status();
+    }
     int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     int per = (H + threads - 1) / threads;
 #define LAUNCH(TO, PER) cj::launch(rmsnorm_kernel<TO, PER>, dim3(rows), dim3(threads), 0, stream, x, w, eps, H, (TO*)out, out_f32, (__nv_bfloat16*)out_split, row_index, partials, n_partials, partial_stride)
@@ -187,7 +299,7 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int 
                                      int n_heads, int n_kv, int hd, int rot, const float* __restrict__ inv_freq,
                                      int write_kv) {
     cj::release_successor();
-    extern __shared__ float cs[];                 // cos[half] then sin[half]
+    extern __shared__ __align__(16) float cs[];   // cos[half] then sin[half]
     const int t = blockIdx.x;
     // with few rows the units of a row are shared out over gridDim.y blocks
     const int part = blockIdx.y, parts = gridDim.y;
@@ -211,6 +323,49 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int ld, int 
     }
     cj::after_predecessor();
     __syncthreads();
+    // head sizes and rotary parts of a multiple of eight, rows on 16-byte boundaries: units of four dims
+    const bool quad = (hd % 4 == 0) && (half % 4 == 0) && ((ld | q_off | k_off | v_off) % 4 == 0) &&
+                      ((((uintptr_t)qkv) | ((uintptr_t)q_out) | ((uintptr_t)kplane) | ((uintptr_t)vplane)) & 15) == 0;
+    if (quad) {
+        const int units_per_slot = half / 4;
+        const int rot_slots = n_heads + (write_kv && have_page ? n_kv : 0);
+        for (int u = part * blockDim.x + threadIdx.x; u < rot_slots * units_per_slot; u += parts * blockDim.x) {
+            int slot = u / units_per_slot, d = (u % units_per_slot) * 4;
+            bool is_q = slot < n_heads;
+            const float* src = is_q ? row + q_off + slot * hd : row + k_off + (slot - n_heads) * hd;
+            float4 a = *(const float4*)(src + d), b = *(const float4*)(src + d + half);
+            float4 c = *(const float4*)(cs + d), sn = *(const float4*)(cs + half + d);
+            float4 lo = make_float4(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y, a.z * c.z - b.z * sn.z, a.w * c.w - b.w * sn.w);
+            float4 hi = make_float4(a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y, a.z * sn.z + b.z * c.z, a.w * sn.w + b.w * c.w);
+            if (is_q) {
+                TQ* dst = q_out + ((size_t)t * n_heads + slot) * hd;
+                store4<TQ>(dst + d, lo);
+                store4<TQ>(dst + d + half, hi);
+            } else {
+                TC* dst = kplane + kv_base + (size_t)(slot - n_heads) * page_tokens * hd;
+                store4<TC>(dst + d, lo);
+                store4<TC>(dst + d + half, hi);
+            }
+        }
+        const int tail = hd - rot;                 // dims past the rotary part pass through
+        if (tail > 0) {
+            for (int u = part * blockDim.x + threadIdx.x; u < rot_slots * (tail / 4); u += parts * blockDim.x) {
+                int slot = u / (tail / 4), d = rot + (u % (tail / 4)) * 4;
+                bool is_q = slot < n_heads;
+                const float* src = is_q ? row + q_off + slot * hd : row + k_off + (slot - n_heads) * hd;
+                float4 a = *(const float4*)(src + d);
+                if (is_q) store4<TQ>(q_out + ((size_t)t * n_heads + slot) * hd + d, a);
+                else store4<TC>(kplane + kv_base + (size_t)(slot - n_heads) * page_tokens * hd + d, a);
+            }
+        }
+        if (write_kv && have_page) {
+            for (int u = part * blockDim.x + threadIdx.x; u < n_kv * (hd / 4); u += parts * blockDim.x) {
+                int kh = u / (hd / 4), d = (u % (hd / 4)) * 4;
+                store4<TC>(vplane + kv_base + (size_t)kh * page_tokens * hd + d, *(const float4*)(row + v_off + kh * hd + d));
+            }
+        }
+        return;
+    }
     const bool even = (hd % 2 == 0) && (half % 2 == 0);
     if (even) {
         // rotated part of q and k: units of (head slot, dim pair below half)
@@ -389,6 +544,26 @@ CJ_EXPORT int cj_moe_combine(float* hs, const float* y, const int* slot_of_pick,
 // of experts into expert order so that each expert reads a contiguous block
 // (model/MoeFfn.cajeta:2644-2777 gathers rows per expert the same way).
 // ---------------------------------------------------------------------------------
+// a warp a row, eight rows a block: a lane has up to eight 16-byte loads of its row in flight at once
+__global__ void gather_rows16_kernel(uint4* __restrict__ out, const uint4* __restrict__ x, const int* __restrict__ index,
+                                     int rows, int n16) {
+    cj::after_predecessor();
+    cj::release_successor();
+    const int lane = threadIdx.x & 31, s = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (s >= rows) return;
+    const uint4* src = x + (size_t)index[s] * n16;
+    uint4* dst = out + (size_t)s * n16;
+    for (int i0 = lane; i0 < n16; i0 += 32 * 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (i0 + 32 * j < n16) v[j] = src[i0 + 32 * j];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (i0 + 32 * j < n16) dst[i0 + 32 * j] = v[j];
+    }
+}
+
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ index, int H) {
     cj::after_predecessor();
@@ -409,6 +584,13 @@ __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x,
 CJ_EXPORT int cj_gather_rows(void* out, const void* x, int dtype, const int* index, int rows, int H, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (!out || !x || !index || H <= 0) return CJ_ERR_ARG;
+    if (dtype != CJ_F32 && dtype != CJ_BF16) return CJ_ERR_DTYPE;
+    const size_t row_bytes = (size_t)H * (dtype == CJ_F32 ? 4 : 2);
+    if (rows >= 64 && row_bytes % 16 == 0 && ((((uintptr_t)out) | ((uintptr_t)x)) & 15) == 0) {
+        cj::launch(gather_rows16_kernel, dim3((rows + 7) / 8), dim3(256), 0, stream, (uint4*)out, (const uint4*)x, index, rows,
+                   (int)(row_bytes / 16));
+        return launch_status();
+    }
     int threads = H >= 1024 ? 256 : 128;
     if (dtype == CJ_F32) cj::launch(gather_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, (float*)out, (const float*)x, index, H);
     else if (dtype == CJ_BF16) cj::launch(gather_rows_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, index, H);

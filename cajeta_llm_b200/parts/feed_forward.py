@@ -144,6 +144,11 @@ class SparseMoE(Part):
                 self.w_gate[E:].copy_(ws_gate.view(C, I, self.hidden))
                 self.w_up[E:].copy_(ws_up.view(C, I, self.hidden))
                 self.w_down[E:].copy_(ws_down.view(self.hidden, C, I).permute(1, 0, 2))
+                if rt.fast_kernels:
+                    # steps with many rows run the shared expert as dense products of its own (see
+                    # forward): gate and up are then the chunks' rows seen as one matrix, the down
+                    # projection is held a second time, whole
+                    self.ws_down = ws_down
             else:
                 self.ws_gate, self.ws_up, self.ws_down = ws_gate, ws_up, ws_down
             if self.shared_gate:
@@ -176,6 +181,12 @@ class SparseMoE(Part):
         padded[:w.shape[0]] = wb
         self.router_split = torch.cat([padded, padded, padded], dim=1).contiguous()
 
+    # From this many rows on, the shared expert leaves the grouped products: as extra groups it
+    # costs a copy of every row per chunk in the gather, a float32 partial result per chunk out of
+    # the down product and as many reads in the combine - bytes that a step with few rows does not
+    # notice beside the weights, and a step with many rows does.
+    SHARED_DENSE_MIN_ROWS = 512
+
     def wants_split_input(self, rows: int) -> bool:
         return self.router_split is not None and rows >= self.SPLIT_ROUTER_MIN_ROWS
 
@@ -206,7 +217,8 @@ class SparseMoE(Part):
         shared_scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.shared_gate else None
         self._route(x_exact, sel, wts, shared_scale)
 
-        C = self.shared_chunks
+        shared_dense = self.ws_down is not None and self.shared_chunks > 0 and T >= self.SHARED_DENSE_MIN_ROWS
+        C = 0 if shared_dense else self.shared_chunks
         n_slots = T * k + C * T
         offsets = torch.empty((E + C + 1,), dtype=torch.int32, device=dev)
         slot_token = torch.empty((n_slots,), dtype=torch.int32, device=dev)
@@ -215,16 +227,23 @@ class SparseMoE(Part):
         self.last_offsets = offsets          # kept for measurement: which experts the last step touched
 
         act = torch.empty((n_slots, self.inter), dtype=rt.act_dtype, device=dev)
-        project(rt, x, self.w_gate, act, w_up=self.w_up, group_offsets=offsets, a_row_index=slot_token, max_group_rows=T)
+        G = E + C
+        project(rt, x, self.w_gate[:G], act, w_up=self.w_up[:G], group_offsets=offsets, a_row_index=slot_token,
+                max_group_rows=T)
         y = torch.empty((n_slots, self.hidden), dtype=torch.float32, device=dev)
-        project(rt, act, self.w_down, y, group_offsets=offsets, max_group_rows=T, offsets_settled=True)
+        project(rt, act, self.w_down[:G], y, group_offsets=offsets, max_group_rows=T, offsets_settled=True)
 
         shared = None
         if C > 0:
             shared = y[T * k:].view(C, T, self.hidden)
         elif self.shared_inter > 0:
             sact = torch.empty((T, self.shared_inter), dtype=rt.act_dtype, device=dev)
-            project(rt, x, self.ws_gate, sact, w_up=self.ws_up)
+            if shared_dense:
+                ws_gate = self.w_gate[E:].view(self.shared_inter, self.hidden)
+                ws_up = self.w_up[E:].view(self.shared_inter, self.hidden)
+            else:
+                ws_gate, ws_up = self.ws_gate, self.ws_up
+            project(rt, x, ws_gate, sact, w_up=ws_up)
             shared = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
             project(rt, sact, self.ws_down, shared)
         K.moe_combine(residual, y, slot_of_pick, wts, k, shared, shared_scale)

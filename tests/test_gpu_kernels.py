@@ -41,7 +41,8 @@ def test_embed_gather(K, dtype):
     assert torch.equal(out, table[ids.long()].float())
 
 
-@pytest.mark.parametrize("H", [72, 1000, 2048, 5000])
+# four elements a load: 72, 1000, 2048, 3584 (two loads a thread), 5000 (four); one at a time: 1002, 10000
+@pytest.mark.parametrize("H", [72, 1000, 1002, 2048, 3584, 5000, 10000])
 def test_rmsnorm(K, H):
     x = rnd(7, H, seed=2, scale=3.0)
     w = rnd(H, seed=3)
@@ -68,6 +69,39 @@ def test_rmsnorm_adds_pending_partial_sums_first(K):
     K.rmsnorm(x, w, 1e-6, out, out32, None, parts)
     assert torch.allclose(x.double(), total, atol=1e-6)                      # the residual stream keeps the sum
     assert torch.allclose(out32.double().cpu(), P.rmsnorm(total.cpu(), w.double().cpu(), 1e-6), atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("H", [200, 202, 3584])
+def test_rmsnorm_partial_sums_and_three_term_form(K, H):
+    """Partial sums are added first whatever the row's width; the three bfloat16 terms add up to
+    the float32 result to 2^-24 of its size (hi is the ordinary bfloat16 result)."""
+    x = rnd(6, H, seed=4, scale=2.0)
+    parts = rnd(2, 6, H, seed=9)
+    w = rnd(H, seed=5)
+    total = x.double() + parts.double().sum(0)
+    out = torch.empty(6, H, device=DEV, dtype=torch.bfloat16)
+    split = torch.empty(6, 3 * H, device=DEV, dtype=torch.bfloat16)
+    K.rmsnorm(x, w, 1e-6, out, None, None, parts, split)
+    want = P.rmsnorm(total.cpu(), w.double().cpu(), 1e-6)
+    assert torch.allclose(x.double(), total, atol=1e-6)
+    assert torch.equal(split[:, :H], out)
+    three = split.double().view(6, 3, H).sum(1).cpu()
+    assert torch.allclose(three, want, atol=1e-5, rtol=1e-5)
+    exact = torch.empty(6, H, device=DEV)
+    K.rmsnorm(x, w, 1e-6, out, exact, None, None, None)
+    assert float((three - exact.double().cpu()).abs().max()) <= 2.0 ** -22 * float(exact.abs().max())
+
+
+@pytest.mark.parametrize("dtype,H", [(torch.bfloat16, 2048), (torch.bfloat16, 72), (torch.float32, 100), (torch.bfloat16, 67)])
+@pytest.mark.parametrize("rows", [5, 300])
+def test_gather_rows(K, dtype, H, rows):
+    """Few rows: a block a row; many rows of a multiple of 16 bytes: a warp a row."""
+    x = rnd(41, H, seed=11, dtype=dtype)
+    g = torch.Generator().manual_seed(rows)
+    index = torch.randint(0, 41, (rows,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.empty(rows, H, device=DEV, dtype=dtype)
+    K.gather_rows(x, index, out)
+    assert torch.equal(out, x[index.long()])
 
 
 @pytest.mark.parametrize("M,N,K_", [(1, 5, 7), (3, 70, 100), (65, 129, 33), (130, 64, 257)])
@@ -278,7 +312,8 @@ def test_attention_finds_one_far_key_among_hundreds_and_the_edge_of_the_window(K
         assert close == inside, (w, inside)
 
 
-@pytest.mark.parametrize("hd,rot", [(16, 16), (24, 24), (64, 32), (128, 128)])
+# units of four dims: (16, 16), (24, 24), (64, 32), (128, 128); of two: (20, 12); one at a time: (18, 6)
+@pytest.mark.parametrize("hd,rot", [(16, 16), (24, 24), (64, 32), (128, 128), (20, 12), (18, 6)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_rope_and_cache_write(K, hd, rot, dtype):
     heads, n_kv, page, T = 3, 2, 4, 11
