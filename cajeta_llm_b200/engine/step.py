@@ -93,6 +93,8 @@ class _CapturedStep:
 
 
 GRAPH_CONTEXT_BUCKET = 1024     # captured decode steps are keyed by the context rounded up to this
+MIXED_CAPTURE_AFTER = 2         # a step shape (rows, requests, wanted) is captured when it is met this often
+MIXED_GRAPHS_MAX = 16           # captured step shapes kept; the one replayed longest ago goes first
 WAIT_CHECK_EVERY = 64           # steps between looks at the kernels' wait-error flags
 
 
@@ -105,6 +107,14 @@ class ModelRunner:
     metadata (tokens, positions, block tables) lives in a static device buffer that is
     refreshed before each replay.  The captured kernels are the same ones an uncaptured
     step launches, so both give the same logits.
+
+    Steps with prompt portions are bound by the host too when they are small (a few hundred
+    launches from Python take longer than the device needs for a few hundred rows).  Which
+    kernels such a step launches, and with which grids, depends only on its number of rows,
+    of requests and of wanted rows - how the rows are shared out among the requests, where
+    each request stands and which pages it owns is device metadata - so a shape that comes
+    again (the portions of one long prompt beside the same decoding requests, prompts of one
+    length) is captured at its second appearance and replayed from then on.
     """
 
     def __init__(self, model: Model, page_tokens: int = 16, max_seqs: int = 4, max_tokens_per_seq: int = 4096,
@@ -125,6 +135,8 @@ class ModelRunner:
             from ..csrc import build as _build
             _build.build_all(sorted(n for n in model.libraries() if n in _build.LIBRARIES))
         self._graphs: Dict[Tuple[int, int], _CapturedStep] = {}
+        self._mixed_graphs: Dict[Tuple[int, int, int], _CapturedStep] = {}   # by (rows, requests, wanted), oldest use first
+        self._mixed_seen: Dict[Tuple[int, int, int], int] = {}
         self._graph_pool = None
         self._decode_host: Dict[Tuple[int, int], tuple] = {}   # pinned metadata of decode steps by (rows, width), reused
         self._meta_copied = None                               # event: the last copy out of the buffer in use is over
@@ -150,12 +162,51 @@ class ModelRunner:
             self.check_waits()
         if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and not self.cache.state:
             return self._step_captured(entries)
-        ctx = self._prepare(entries)
-        logits = self._forward(ctx)
+        if self.cuda_graphs and not self.cache.state:
+            logits = self._step_mixed(entries)
+        else:
+            logits = self._forward(self._prepare(entries))
         for e in entries:
             self.cache.commit(e.slot, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def _step_mixed(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A step with prompt portions on the bfloat16 path: uncaptured the first time its shape
+        (rows, requests, wanted rows) is met, captured the second time, replayed afterwards."""
+        from ..csrc import kernels as K
+        key = (sum(len(e.tokens) for e in entries), len(entries), sum(len(e.want) for e in entries))
+        cap = self._mixed_graphs.get(key)
+        if cap is None:
+            seen = self._mixed_seen[key] = self._mixed_seen.get(key, 0) + 1
+            if len(self._mixed_seen) > 4096:
+                self._mixed_seen.clear()
+            if seen < MIXED_CAPTURE_AFTER:
+                return self._forward(self._prepare(entries))
+        # block tables as wide as they can ever get: the captured kernels keep the row stride
+        host, layout = self._build_meta(entries, self.cache.books.max_pages_per_seq)
+        if cap is None:
+            meta = torch.empty(host.shape, dtype=torch.int32, device=self.runtime.device)
+            meta.copy_(host, non_blocking=True)
+            ctx = self._context(meta, layout, entries)
+            logits = self._forward(ctx)                      # this step's result, uncaptured
+            torch.cuda.synchronize()
+            before = K.launches
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                static_logits = self._forward(ctx)
+            while len(self._mixed_graphs) >= MIXED_GRAPHS_MAX:
+                self._mixed_graphs.pop(next(iter(self._mixed_graphs)))
+            self._mixed_graphs[key] = _CapturedStep(graph, meta, static_logits, K.launches - before, None)
+            return logits
+        self._mixed_graphs[key] = self._mixed_graphs.pop(key)      # most recently used last
+        cap.meta.copy_(host, non_blocking=True)
+        cap.graph.replay()
+        K.launches += cap.launches
+        self.graph_replays += 1
+        return cap.logits.clone()              # the static buffer is overwritten by the next replay
 
     def check_waits(self) -> None:
         """Every wait inside the tensor-core kernels is bounded; one that ran out left a code

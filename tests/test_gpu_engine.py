@@ -225,6 +225,44 @@ def test_captured_decode_steps_give_the_same_logits_as_uncaptured_ones(model_dir
     helpers.assert_close(outs[True], want, "bfloat16", "captured decode", margins)
 
 
+def test_captured_steps_with_prompt_portions_give_the_same_logits_as_uncaptured_ones(model_dirs):
+    """A step shape (rows, requests, wanted rows) that comes again is captured and replayed.  The
+    replays must equal, bit for bit, the same steps launched kernel by kernel: with the rows shared
+    out differently among the requests, at other positions, on other pages, beside decode steps."""
+    from cajeta_llm_b200.engine.step import StepEntry
+    vocab = helpers.MEDIUM["vocab_size"]
+    seqs = [helpers.random_tokens(vocab, 150, seed=300 + i) for i in range(3)]
+    # every step: 24 rows, 3 requests, 4 wanted; the split of the rows changes from step to step
+    splits = [(10, 13, 1), (1, 22, 1), (8, 8, 8), (20, 2, 2), (3, 1, 20), (12, 11, 1)]
+    outs = {}
+    for graphs in (False, True):
+        r = runner_for(model_dirs["M"], "bfloat16", page_tokens=16, max_seqs=4, max_tokens_per_seq=160, cuda_graphs=graphs)
+        slots = [r.admit() for _ in seqs]
+        at = [0, 0, 0]
+        got = []
+        for n in splits:
+            entries = []
+            for i in range(3):
+                want = [0, n[i] - 1] if i == 0 and n[i] > 1 else [n[i] - 1]
+                entries.append(StepEntry(slots[i], seqs[i][at[i]:at[i] + n[i]], want))
+                at[i] += n[i]
+            if n[0] == 1:                          # four wanted rows in every step
+                entries[1] = StepEntry(entries[1].slot, entries[1].tokens, [0, n[1] - 1])
+            got.append(r.step(entries).clone())
+            # a decode step in between (a graph of its own)
+            got.append(r.step([StepEntry(slots[i], [seqs[i][at[i]]], [0]) for i in range(3)]).clone())
+            at = [a + 1 for a in at]
+        outs[graphs] = torch.cat(got).cpu()
+        if graphs:
+            assert len(r._mixed_graphs) == 1 and r.graph_replays >= len(splits) - 2 + len(splits) - 1
+    assert torch.equal(outs[True], outs[False])
+    # and against the plain implementation: the last wanted row of each request in the last portion step
+    at = [sum(n[i] for n in splits) + len(splits) for i in range(3)]
+    want = torch.stack([helpers.plain_logits(model_dirs["M"], seqs[i][:at[i]])[at[i] - 1] for i in range(3)])
+    margins = torch.stack([helpers.plain_margins(model_dirs["M"], seqs[i][:at[i]])[at[i] - 1] for i in range(3)])
+    helpers.assert_close(outs[True][-3:], want, "bfloat16", "captured mixed steps", margins)
+
+
 def test_real_layer_sizes_match_the_plain_implementation(tmp_path):
     """Layers of the benchmark's sizes (fewer of them): a prompt in one step, in portions
     beside another request's decode tokens, and token by token, in float32 and bfloat16."""
