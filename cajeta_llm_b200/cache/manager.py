@@ -12,8 +12,8 @@ It is built from the needs that the model's schedule entries declare
   (The reference has no recurrent state; its fixed-size per-slot things are scratch and
   histograms, model/DeviceKv.cajeta:44-48, model/MoeFfn.cajeta:2830-2836.)
 
-All bookkeeping is on the host; the block-table rows of the requests in a step are
-uploaded with the step's other metadata.
+All bookkeeping is on the host, in native code (:mod:`cajeta_llm_b200.cache.pages`); the
+block-table rows of the requests in a step are uploaded with the step's other metadata.
 """
 from __future__ import annotations
 
@@ -122,11 +122,7 @@ class CacheManager:
 
     def table_width(self, slots: Sequence[int]) -> int:
         """Columns that cover every page the given slots have ever been given."""
-        w = 1
-        for g in self.books.groups:
-            for s in slots:
-                w = max(w, int(g.next_page[s]))
-        return w
+        return self.books.table_width(slots)
 
     def plane(self, entry: int) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor], Optional[int]]:
         g = self.entry_group[entry]

@@ -1,4 +1,9 @@
-"""The books of the cache manager: pages, block tables, request slots.  Host logic only.
+"""The books of the cache manager: pages, block tables, request slots.
+
+The bookkeeping itself is native code (``csrc/host_books.cpp``, compiled with the host
+compiler and loaded through ctypes: no GPU and no CUDA toolkit is needed for it); this
+module is its Python face.  Block tables, lengths and live ranges are numpy views of the
+native arrays, not copies.
 
 Keys and values live in pages of ``page_tokens`` positions.  Layers with the same
 needs (kv heads, head size, window) form a *group*: the group has its own pool of
@@ -24,64 +29,113 @@ model/KvPool.cajeta:234-255).
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence
 
 import numpy as np
+
+from ..csrc import build as _build
 
 
 class CacheError(RuntimeError):
     """A misuse of the cache books (double free, unknown slot, table overflow)."""
 
 
+_lib: Optional[ctypes.CDLL] = None
+_P = ctypes.c_void_p
+_IP = ctypes.POINTER(ctypes.c_int)
+
+
+def _native() -> ctypes.CDLL:
+    """The native books, compiled at first use."""
+    global _lib
+    if _lib is None:
+        lib = ctypes.CDLL(_build.build("host_books"))
+        c_int, c_ll = ctypes.c_int, ctypes.c_longlong
+        sigs = {
+            "cj_pages_create": (_P, [c_int]), "cj_pages_destroy": (None, [_P]), "cj_pages_error": (ctypes.c_char_p, [_P]),
+            "cj_pages_free_count": (c_int, [_P]), "cj_pages_take": (c_int, [_P, c_int, _IP]),
+            "cj_pages_give_back": (c_int, [_P, _IP, c_int]), "cj_pages_check": (c_int, [_P]),
+            "cj_books_create": (_P, [c_int, _IP, _IP, c_int, c_int, c_int]), "cj_books_destroy": (None, [_P]),
+            "cj_books_error": (ctypes.c_char_p, [_P]),
+            "cj_books_length": (_P, [_P]), "cj_books_live": (_P, [_P]), "cj_books_table": (_P, [_P, c_int]),
+            "cj_books_first_live": (_P, [_P, c_int]), "cj_books_next_page": (_P, [_P, c_int]),
+            "cj_books_width": (c_int, [_P]), "cj_books_free_slots": (c_int, [_P]), "cj_books_free_count": (c_int, [_P, c_int]),
+            "cj_books_admit": (c_int, [_P]), "cj_books_release": (c_int, [_P, c_int]),
+            "cj_books_pages_needed": (c_int, [_P, c_int, c_int, _IP]), "cj_books_reserve": (c_int, [_P, c_int, c_int]),
+            "cj_books_reserve_step": (c_int, [_P, _IP, _IP, c_int, _IP]), "cj_books_commit": (c_int, [_P, c_int, c_int]),
+            "cj_books_reserve_one_each": (c_int, [_P, _IP, c_int, _P]), "cj_books_commit_one_each": (c_int, [_P, _IP, c_int]),
+            "cj_books_table_width": (c_int, [_P, _IP, c_int]),
+            "cj_books_layout_step": (c_ll, [_P, c_int, _IP, _IP, _IP, _IP, _IP, c_int, _P, c_ll]),
+            "cj_books_check": (c_int, [_P]),
+        }
+        for name, (res, args) in sigs.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def _ints(values: Sequence[int]) -> np.ndarray:
+    return np.ascontiguousarray(values, dtype=np.int32)
+
+
+def _ip(a: np.ndarray):
+    return a.ctypes.data_as(_IP)
+
+
+def _view(ptr: int, shape, dtype) -> np.ndarray:
+    n = int(np.prod(shape))
+    if n == 0 or not ptr:
+        return np.zeros(shape, dtype=dtype)
+    buf = (ctypes.c_char * (n * np.dtype(dtype).itemsize)).from_address(ptr)
+    return np.frombuffer(buf, dtype=dtype).reshape(shape)
+
+
 class PageAllocator:
-    """Free list of one group's pages (LIFO, like the reference's free-list stack)."""
+    """Free list of one group's pages (a stack, like the reference's free list)."""
 
     def __init__(self, num_pages: int):
         if num_pages < 0:
             raise CacheError(f"num_pages must be >= 0, found {num_pages}")
+        self._lib = _native()
+        self._h = self._lib.cj_pages_create(num_pages)
         self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))
-        self._held = np.zeros(num_pages, dtype=bool)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.cj_pages_destroy(h)
+
+    def _fail(self):
+        raise CacheError(self._lib.cj_pages_error(self._h).decode())
 
     @property
     def free_count(self) -> int:
-        return len(self._free)
+        return self._lib.cj_pages_free_count(self._h)
 
     @property
     def used_count(self) -> int:
-        return self.num_pages - len(self._free)
+        return self.num_pages - self.free_count
 
     def take(self, n: int) -> Optional[List[int]]:
         """``n`` pages, or None (and nothing taken) when fewer are free."""
-        if n < 0:
-            raise CacheError(f"cannot take {n} pages")
-        if n > len(self._free):
-            return None
-        out = [self._free.pop() for _ in range(n)]
-        for p in out:
-            if self._held[p]:
-                raise CacheError(f"page {p} handed out twice")
-            self._held[p] = True
-        return out
+        out = np.empty(max(n, 1), dtype=np.int32)
+        st = self._lib.cj_pages_take(self._h, n, _ip(out))
+        if st < 0:
+            self._fail()
+        return out[:n].tolist() if st else None
 
     def give_back(self, pages: Sequence[int]) -> None:
-        for p in pages:
-            if not 0 <= p < self.num_pages:
-                raise CacheError(f"page {p} does not exist")
-            if not self._held[p]:
-                raise CacheError(f"page {p} freed twice")
-            self._held[p] = False
-            self._free.append(p)
+        a = _ints(pages)
+        if self._lib.cj_pages_give_back(self._h, _ip(a), a.size) < 0:
+            self._fail()
 
     def check(self) -> None:
         """No page lost, held twice or free twice."""
-        free = set(self._free)
-        if len(free) != len(self._free):
-            raise CacheError("a page is on the free list twice")
-        for p in range(self.num_pages):
-            if self._held[p] == (p in free):
-                raise CacheError(f"page {p} is {'both held and free' if self._held[p] else 'neither held nor free'}")
+        if self._lib.cj_pages_check(self._h) < 0:
+            self._fail()
 
 
 @dataclass(frozen=True)
@@ -93,57 +147,35 @@ class GroupSpec:
     window: int      # 0: every key is kept
 
 
-class GroupBook:
-    """Block tables and page ownership of one group."""
+class _GroupPages:
+    """Page counts of one group of the books."""
 
-    def __init__(self, spec: GroupSpec, num_pages: int, page_tokens: int, max_seqs: int, max_pages_per_seq: int):
+    def __init__(self, books: "CacheBooks", index: int, num_pages: int):
+        self._books, self._index, self.num_pages = books, index, num_pages
+
+    @property
+    def free_count(self) -> int:
+        return self._books._lib.cj_books_free_count(self._books._h, self._index)
+
+    @property
+    def used_count(self) -> int:
+        return self.num_pages - self.free_count
+
+
+class GroupBook:
+    """Block tables and page ownership of one group, as views of the native books."""
+
+    def __init__(self, books: "CacheBooks", index: int, spec: GroupSpec, num_pages: int):
+        lib, h = books._lib, books._h
         self.spec = spec
-        self.page_tokens = page_tokens
-        self.allocator = PageAllocator(num_pages)
-        self.table = np.full((max_seqs, max_pages_per_seq), -1, dtype=np.int32)
-        self.first_live = np.zeros(max_seqs, dtype=np.int64)   # lowest logical page still held
-        self.next_page = np.zeros(max_seqs, dtype=np.int64)    # logical pages ever given (held: [first_live, next_page))
+        self.page_tokens = books.page_tokens
+        self.allocator = _GroupPages(books, index, num_pages)
+        self.table = _view(lib.cj_books_table(h, index), (books.max_seqs, books.max_pages_per_seq), np.int32)
+        self.first_live = _view(lib.cj_books_first_live(h, index), (books.max_seqs,), np.int64)   # lowest logical page still held
+        self.next_page = _view(lib.cj_books_next_page(h, index), (books.max_seqs,), np.int64)     # logical pages ever given
 
     def pages_for(self, length: int) -> int:
         return -(-length // self.page_tokens)
-
-    def pages_needed(self, slot: int, length: int, n_new: int) -> int:
-        return max(0, self.pages_for(length + n_new) - int(self.next_page[slot]))
-
-    def grow(self, slot: int, length: int, n_new: int, pages: List[int]) -> None:
-        start = int(self.next_page[slot])
-        if start + len(pages) > self.table.shape[1]:
-            raise CacheError(f"request in slot {slot} needs {start + len(pages)} pages; a table row holds {self.table.shape[1]}")
-        for i, p in enumerate(pages):
-            self.table[slot, start + i] = p
-        self.next_page[slot] = start + len(pages)
-
-    def trim_window(self, slot: int, length: int) -> int:
-        """Give back the pages that lie wholly behind the window of the next token."""
-        w = self.spec.window
-        if w <= 0:
-            return 0
-        dead_below = length + 1 - w                       # positions < dead_below are never read again
-        if dead_below <= 0:
-            return 0
-        last_dead = min(dead_below // self.page_tokens, int(self.next_page[slot]))   # pages [first_live, last_dead) are dead
-        first = int(self.first_live[slot])
-        if last_dead <= first:
-            return 0
-        pages = [int(self.table[slot, j]) for j in range(first, last_dead)]
-        self.allocator.give_back(pages)
-        self.table[slot, first:last_dead] = -1
-        self.first_live[slot] = last_dead
-        return len(pages)
-
-    def release(self, slot: int) -> int:
-        first, nxt = int(self.first_live[slot]), int(self.next_page[slot])
-        pages = [int(self.table[slot, j]) for j in range(first, nxt)]
-        self.allocator.give_back(pages)
-        self.table[slot, :nxt] = -1
-        self.first_live[slot] = 0
-        self.next_page[slot] = 0
-        return len(pages)
 
     def held_pages(self, slot: int) -> List[int]:
         return [int(self.table[slot, j]) for j in range(int(self.first_live[slot]), int(self.next_page[slot]))]
@@ -158,39 +190,47 @@ class CacheBooks:
             raise CacheError(f"page_tokens must be >= 1, found {page_tokens}")
         if len(groups) != len(num_pages):
             raise CacheError("one page count per group is needed")
+        self._lib = _native()
         self.page_tokens = page_tokens
         self.max_seqs = max_seqs
         self.max_tokens_per_seq = max_tokens_per_seq
         self.max_pages_per_seq = -(-max_tokens_per_seq // page_tokens)
-        self.groups = [GroupBook(g, n, page_tokens, max_seqs, self.max_pages_per_seq) for g, n in zip(groups, num_pages)]
-        self.length = np.zeros(max_seqs, dtype=np.int64)
-        self.live = np.zeros(max_seqs, dtype=bool)
-        self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
+        windows, counts = _ints([g.window for g in groups]), _ints(list(num_pages))
+        self._h = self._lib.cj_books_create(len(groups), _ip(windows), _ip(counts), page_tokens, max_seqs, max_tokens_per_seq)
+        if not self._h:
+            raise CacheError(f"the books cannot be made for {len(groups)} groups of {list(num_pages)} pages, "
+                             f"{max_seqs} requests of {max_tokens_per_seq} tokens")
+        self.groups = [GroupBook(self, i, g, n) for i, (g, n) in enumerate(zip(groups, num_pages))]
+        self.length = _view(self._lib.cj_books_length(self._h), (max_seqs,), np.int64)
+        self.live = _view(self._lib.cj_books_live(self._h), (max_seqs,), np.bool_)
+        self._needs = np.zeros(max(1, len(groups)), dtype=np.int32)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            # the views must not outlive the arrays they look at
+            self.groups, self.length, self.live = [], None, None
+            self._lib.cj_books_destroy(h)
+
+    def _fail(self):
+        raise CacheError(self._lib.cj_books_error(self._h).decode())
 
     # -- slots -----------------------------------------------------------------------
     @property
     def free_slots(self) -> int:
-        return len(self._free_slots)
+        return self._lib.cj_books_free_slots(self._h)
 
     def admit(self) -> Optional[int]:
         """A free slot for a new request (length 0), or None when all are taken."""
-        if not self._free_slots:
-            return None
-        s = self._free_slots.pop()
-        self.live[s] = True
-        self.length[s] = 0
-        return s
-
-    def _need_live(self, slot: int) -> None:
-        if not (0 <= slot < self.max_seqs) or not self.live[slot]:
-            raise CacheError(f"slot {slot} holds no request")
+        s = self._lib.cj_books_admit(self._h)
+        return s if s >= 0 else None
 
     # -- pages -----------------------------------------------------------------------
     def pages_needed(self, slot: int, n_new: int) -> List[int]:
         """New pages per group that appending ``n_new`` tokens would draw."""
-        self._need_live(slot)
-        L = int(self.length[slot])
-        return [g.pages_needed(slot, L, n_new) for g in self.groups]
+        if self._lib.cj_books_pages_needed(self._h, slot, n_new, _ip(self._needs)) < 0:
+            self._fail()
+        return self._needs[:len(self.groups)].tolist()
 
     def free_pages(self) -> List[int]:
         return [g.allocator.free_count for g in self.groups]
@@ -204,99 +244,68 @@ class CacheBooks:
 
     def reserve(self, slot: int, n_new: int) -> bool:
         """Make sure pages exist for positions ``[length, length + n_new)``; all or nothing."""
-        self._need_live(slot)
-        L = int(self.length[slot])
-        if L + n_new > self.max_tokens_per_seq:
-            raise CacheError(f"request in slot {slot} would reach {L + n_new} tokens; the limit is {self.max_tokens_per_seq}")
-        needs = [g.pages_needed(slot, L, n_new) for g in self.groups]
-        if any(n > g.allocator.free_count for n, g in zip(needs, self.groups)):
-            return False
-        for n, g in zip(needs, self.groups):
-            pages = g.allocator.take(n)
-            assert pages is not None
-            g.grow(slot, L, n_new, pages)
-        return True
+        st = self._lib.cj_books_reserve(self._h, slot, n_new)
+        if st < 0:
+            self._fail()
+        return bool(st)
+
+    def reserve_step(self, slots: Sequence[int], n_new: Sequence[int]) -> Optional[List[int]]:
+        """``reserve`` for every request of a step, all or nothing over the whole step.  Returns
+        None when the pages were reserved, else (nothing changed) the new pages per group that
+        the step wants."""
+        s, n = _ints(slots), _ints(n_new)
+        st = self._lib.cj_books_reserve_step(self._h, _ip(s), _ip(n), s.size, _ip(self._needs))
+        if st < 0:
+            self._fail()
+        return None if st else self._needs[:len(self.groups)].tolist()
 
     # -- one token for each of several requests (a decode step), the books' hot path -------------
     def reserve_one_each(self, slots: Sequence[int]) -> Optional[np.ndarray]:
         """``reserve(slot, 1)`` for every slot, all or nothing over the whole list.  Returns the
         requests' lengths (before the new token) or None when the pages are not there."""
-        idx = np.asarray(slots, dtype=np.int64)
-        if idx.size == 0:
-            return np.zeros(0, dtype=np.int64)
-        if idx.min() < 0 or idx.max() >= self.max_seqs or not self.live[idx].all():
-            bad = [int(s) for s in idx if not (0 <= s < self.max_seqs) or not self.live[s]]
-            raise CacheError(f"slot {bad[0]} holds no request")
-        L = self.length[idx]
-        if int(L.max()) + 1 > self.max_tokens_per_seq:
-            s = int(idx[int(L.argmax())])
-            raise CacheError(f"request in slot {s} would reach {int(L.max()) + 1} tokens; the limit is {self.max_tokens_per_seq}")
-        wanting = []
-        for g in self.groups:
-            short = np.nonzero(-(-(L + 1) // self.page_tokens) > g.next_page[idx])[0]
-            if short.size > g.allocator.free_count:
-                return None
-            wanting.append(short)
-        for g, short in zip(self.groups, wanting):
-            for i in short:
-                pages = g.allocator.take(1)
-                assert pages is not None
-                g.grow(int(idx[i]), int(L[i]), 1, pages)
-        return L
+        s = _ints(slots)
+        prior = np.empty(s.size, dtype=np.int64)
+        st = self._lib.cj_books_reserve_one_each(self._h, _ip(s), s.size, prior.ctypes.data)
+        if st < 0:
+            self._fail()
+        return prior if st else None
 
     def commit_one_each(self, slots: Sequence[int]) -> None:
         """``commit(slot, 1)`` for every slot."""
-        idx = np.asarray(slots, dtype=np.int64)
-        if idx.size == 0:
-            return
-        self.length[idx] += 1
-        L = self.length[idx]
-        for g in self.groups:
-            if (-(-L // self.page_tokens) > g.next_page[idx]).any():
-                raise CacheError("a token was committed without reserved pages")
-            if g.spec.window > 0:
-                for s, n in zip(idx, L):
-                    g.trim_window(int(s), int(n))
+        s = _ints(slots)
+        if self._lib.cj_books_commit_one_each(self._h, _ip(s), s.size) < 0:
+            self._fail()
 
     def commit(self, slot: int, n_new: int) -> None:
         """The step that wrote ``n_new`` tokens is launched: advance the length and give
         back pages that have passed behind a window."""
-        self._need_live(slot)
-        self.length[slot] += n_new
-        L = int(self.length[slot])
-        for g in self.groups:
-            if g.pages_for(L) > int(g.next_page[slot]):
-                raise CacheError(f"slot {slot}: committed {L} tokens without reserved pages")
-            g.trim_window(slot, L)
+        if self._lib.cj_books_commit(self._h, slot, n_new) < 0:
+            self._fail()
 
     def release(self, slot: int) -> None:
         """Give back everything the request holds; the slot is free again."""
-        self._need_live(slot)
-        for g in self.groups:
-            g.release(slot)
-        self.length[slot] = 0
-        self.live[slot] = False
-        self._free_slots.append(slot)
+        if self._lib.cj_books_release(self._h, slot) < 0:
+            self._fail()
+
+    # -- what a step takes to the device -------------------------------------------------------
+    def table_width(self, slots: Sequence[int]) -> int:
+        """Columns that cover every page the given slots have ever been given."""
+        s = _ints(slots)
+        return self._lib.cj_books_table_width(self._h, _ip(s), s.size)
+
+    def layout_step(self, slots: np.ndarray, n_tokens: np.ndarray, tokens: np.ndarray, n_want: np.ndarray,
+                    wants: np.ndarray, width: int, out: np.ndarray) -> int:
+        """Lays a step's metadata into ``out`` (int32): tokens | positions | row -> request |
+        request starts | prior lengths | slots | wanted rows | one slab ``[requests, width]`` of
+        block-table rows per group.  All arguments are contiguous int32 arrays; returns the
+        number of values written."""
+        n = self._lib.cj_books_layout_step(self._h, slots.size, _ip(slots), _ip(n_tokens), _ip(tokens), _ip(n_want),
+                                           _ip(wants), width, out.ctypes.data, out.size)
+        if n < 0:
+            self._fail()
+        return int(n)
 
     def check(self) -> None:
         """Invariants: no page lost, held twice or freed twice; tables agree with owners."""
-        for g in self.groups:
-            g.allocator.check()
-            owners: Dict[int, int] = {}
-            for s in range(self.max_seqs):
-                held = g.held_pages(s)
-                if not self.live[s] and held:
-                    raise CacheError(f"free slot {s} still holds pages {held}")
-                for p in held:
-                    if p < 0:
-                        raise CacheError(f"slot {s} has a hole in its live pages")
-                    if p in owners:
-                        raise CacheError(f"page {p} is held by slots {owners[p]} and {s}")
-                    owners[p] = s
-                row = g.table[s]
-                live_range = set(range(int(g.first_live[s]), int(g.next_page[s])))
-                for j in range(row.shape[0]):
-                    if (row[j] >= 0) != (j in live_range):
-                        raise CacheError(f"slot {s}: table entry {j} disagrees with the live range")
-            if len(owners) != g.allocator.used_count:
-                raise CacheError(f"{g.allocator.used_count} pages are out, {len(owners)} are in tables")
+        if self._lib.cj_books_check(self._h) < 0:
+            self._fail()

@@ -1,6 +1,7 @@
-"""Builds the CUDA sources of this folder into shared libraries for sm_100a.
+"""Builds the CUDA sources of this folder into shared libraries for sm_100a, and the
+host-only C++ sources (the cache manager's books) with the host compiler.
 
-Each ``.cu`` file becomes its own library with C linkage, loaded through ``ctypes``; a
+Each source file becomes its own library with C linkage, loaded through ``ctypes``; a
 library is compiled the first time one of its functions is wanted, so a run compiles
 only what its model needs.  The file name of a built library carries a hash of its
 source, of the shared header and of the compiler flags: a library that does not match
@@ -43,6 +44,14 @@ LIBRARIES: Dict[str, str] = {
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "sampling_static.h"]
 
+# host-only libraries (no CUDA): compiled with the host C++ compiler, so that the books of the
+# cache manager also load on a machine without nvcc or a GPU
+HOST_LIBRARIES: Dict[str, str] = {
+    "host_books": "host_books.cpp",
+}
+LIBRARIES.update(HOST_LIBRARIES)
+CXX_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+
 
 class BuildError(RuntimeError):
     pass
@@ -55,14 +64,43 @@ def _nvcc() -> Optional[str]:
     return None
 
 
+def _cxx() -> Optional[str]:
+    for cand in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        path = shutil.which(cand) if cand else None
+        if path:
+            return path
+    return None
+
+
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    for rel in [LIBRARIES[name]] + HEADERS:
+    host = name in HOST_LIBRARIES
+    for rel in [LIBRARIES[name]] + ([] if host else HEADERS):
         with open(os.path.join(HERE, rel), "rb") as f:
             h.update(rel.encode())
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(CXX_FLAGS if host else NVCC_FLAGS).encode())
     return h.hexdigest()[:16]
+
+
+def _command(name: str, tmp: str) -> List[str]:
+    """The compiler call that builds library ``name`` into ``tmp``."""
+    src = os.path.join(HERE, LIBRARIES[name])
+    if name in HOST_LIBRARIES:
+        cxx = _cxx()
+        if cxx is None:
+            raise BuildError(f"library '{name}' is not built and no C++ compiler (g++, c++, clang++ or $CXX) was found")
+        return [cxx] + CXX_FLAGS + ["-o", tmp, src]
+    nvcc = _nvcc()
+    if nvcc is None:
+        raise BuildError(
+            f"kernel library '{name}' is not built and nvcc was not found; "
+            "this engine has no fallback without its CUDA kernels")
+    return [nvcc] + NVCC_FLAGS + ["-I", HERE, "-o", tmp, src]
+
+
+def _target(name: str) -> str:
+    return "the host" if name in HOST_LIBRARIES else "sm_100a"
 
 
 def _build_dirs() -> List[str]:
@@ -125,17 +163,12 @@ def build(name: str, verbose: bool = True) -> str:
         found = find_built(name)
         if found:
             return found
-        nvcc = _nvcc()
-        if nvcc is None:
-            raise BuildError(
-                f"kernel library '{name}' is not built and nvcc was not found; "
-                "this engine has no fallback without its CUDA kernels")
         out_dir = _writable_dir()
         out = os.path.join(out_dir, _file_name(name))
         tmp = out + f".tmp{os.getpid()}"
-        cmd = [nvcc] + NVCC_FLAGS + ["-I", HERE, "-o", tmp, os.path.join(HERE, LIBRARIES[name])]
+        cmd = _command(name, tmp)
         if verbose:
-            print(f"[cajeta_llm_b200] compiling {LIBRARIES[name]} for sm_100a ...", file=sys.stderr, flush=True)
+            print(f"[cajeta_llm_b200] compiling {LIBRARIES[name]} for {_target(name)} ...", file=sys.stderr, flush=True)
         t0 = time.time()
         done = threading.Event()
 
@@ -157,7 +190,7 @@ def build(name: str, verbose: bool = True) -> str:
                 os.remove(tmp)
             except OSError:
                 pass
-            raise BuildError(f"nvcc failed for {LIBRARIES[name]}:\n{proc.stdout}")
+            raise BuildError(f"{os.path.basename(cmd[0])} failed for {LIBRARIES[name]}:\n{proc.stdout}")
         os.replace(tmp, out)
         _drop_stale(out_dir, name, os.path.basename(out))
         if verbose:
@@ -195,16 +228,13 @@ def build_all(names: Optional[Iterable[str]] = None, verbose: bool = True) -> Di
 
 
 def _compile_unlocked(name: str, verbose: bool) -> None:
-    nvcc = _nvcc()
-    if nvcc is None:
-        raise BuildError("nvcc was not found")
     out_dir = _writable_dir()
     out = os.path.join(out_dir, _file_name(name))
     tmp = out + f".tmp{os.getpid()}_{threading.get_ident()}"
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", HERE, "-o", tmp, os.path.join(HERE, LIBRARIES[name])]
+    cmd = _command(name, tmp)
     t0 = time.time()
     if verbose:
-        print(f"[cajeta_llm_b200] compiling {LIBRARIES[name]} for sm_100a ...", file=sys.stderr, flush=True)
+        print(f"[cajeta_llm_b200] compiling {LIBRARIES[name]} for {_target(name)} ...", file=sys.stderr, flush=True)
     proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                           env={**os.environ, "TMPDIR": out_dir})
     if proc.returncode != 0:
@@ -212,7 +242,7 @@ def _compile_unlocked(name: str, verbose: bool) -> None:
             os.remove(tmp)
         except OSError:
             pass
-        raise BuildError(f"nvcc failed for {LIBRARIES[name]}:\n{proc.stdout}")
+        raise BuildError(f"{os.path.basename(cmd[0])} failed for {LIBRARIES[name]}:\n{proc.stdout}")
     os.replace(tmp, out)
     _drop_stale(out_dir, name, os.path.basename(out))
     if verbose:

@@ -361,58 +361,39 @@ class ModelRunner:
     def _build_meta(self, entries: Sequence[StepEntry], width: Optional[int]):
         """Checks the step, reserves its pages and lays its metadata into one pinned int32
         buffer: tokens | positions | row->request | request starts | prior lengths | slots |
-        wanted rows | one block-table slab per cache group."""
+        wanted rows | one block-table slab per cache group.  The reservation (all or nothing
+        over the whole step) and the layout are the native books' work."""
         cache = self.cache
         vocab = self.model.vocab
         slots = [e.slot for e in entries]
         if len(set(slots)) != len(slots):
             raise StepError("a request appears twice in one step")
         # every check comes before the first change of the books
-        needs = []
+        counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=len(entries))
+        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if tokens.min() < 0 or tokens.max() >= vocab:
+            bad = int(tokens[(tokens < 0) | (tokens >= vocab)][0])
+            raise StepError(f"token id {bad} is outside the vocabulary [0, {vocab})")
         for e in entries:
-            toks = np.asarray(e.tokens, dtype=np.int64)
-            if toks.min() < 0 or toks.max() >= vocab:
-                bad = int(toks[(toks < 0) | (toks >= vocab)][0])
-                raise StepError(f"token id {bad} is outside the vocabulary [0, {vocab})")
             for w in e.want:
                 if not 0 <= w < len(e.tokens):
                     raise StepError(f"want index {w} is outside the {len(e.tokens)} tokens of the entry")
-            needs.append(cache.pages_needed(e.slot, len(e.tokens)))
-        if not cache.books.fits(needs):
-            raise OutOfPages(f"step needs {[sum(n[g] for n in needs) for g in range(cache.num_groups)]} new pages per group; "
-                             f"free: {cache.free_pages()}")
-        for e in entries:
-            ok = cache.reserve(e.slot, len(e.tokens))
-            assert ok
+        n_want = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=len(entries))
+        wants = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=int(n_want.sum()))
+        slot_arr = np.asarray(slots, dtype=np.int32)
+        short = cache.books.reserve_step(slot_arr, counts)        # also refuses a slot that holds no request
+        if short is not None:
+            raise OutOfPages(f"step needs {short} new pages per group; free: {cache.free_pages()}")
+        req_prior = [cache.length(s) for s in slots]
 
         R = len(entries)
-        T = sum(len(e.tokens) for e in entries)
-        n_want = sum(len(e.want) for e in entries)
+        T = int(counts.sum())
         if width is None:
             width = cache.table_width(slots)
         G = cache.num_groups
-        sizes = [T, T, T, R + 1, R, R, n_want] + [R * width] * G
+        sizes = [T, T, T, R + 1, R, R, int(n_want.sum())] + [R * width] * G
         offs = np.concatenate([[0], np.cumsum(sizes)])
         host = torch.empty((int(offs[-1]),), dtype=torch.int32, pin_memory=True)
-        h = host.numpy()
-        req_start, req_prior = [0], []
-        row = 0
-        wi = 0
-        for r, e in enumerate(entries):
-            n = len(e.tokens)
-            prior = cache.length(e.slot)
-            h[offs[0] + row: offs[0] + row + n] = np.asarray(e.tokens, dtype=np.int32)
-            h[offs[1] + row: offs[1] + row + n] = np.arange(prior, prior + n, dtype=np.int32)
-            h[offs[2] + row: offs[2] + row + n] = r
-            for w in e.want:
-                h[offs[6] + wi] = row + w
-                wi += 1
-            req_prior.append(prior)
-            row += n
-            req_start.append(row)
-        h[offs[3]: offs[3] + R + 1] = req_start
-        h[offs[4]: offs[4] + R] = req_prior
-        h[offs[5]: offs[5] + R] = slots
-        for g in range(G):
-            h[offs[7 + g]: offs[7 + g] + R * width] = cache.table_rows(g, slots, width).reshape(-1)
+        cache.books.layout_step(slot_arr, counts, tokens.astype(np.int32), n_want, wants, width, host.numpy())
+        req_start = np.concatenate([[0], np.cumsum(counts)]).tolist()
         return host, (offs, R, width, G, req_start, req_prior, slots)

@@ -186,3 +186,106 @@ def test_manager_groups_layers_by_their_needs():
         CacheManager([None, full], [None, None], [None, 0], 4, 2, 32, 6, None, None)
     with pytest.raises(CacheError, match="window"):
         CacheManager([win, full], [None, None], [None, 0], 4, 2, 32, 6, None, None)
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(0, 2 ** 31), st.sampled_from([0, 5, 9]), st.sampled_from([2, 4, 16]))
+def test_native_books_agree_with_the_plain_books_call_for_call(seed, window, page_tokens):
+    """The engine's books (native code) and the plain Python books, driven by the same random
+    order of admissions, reservations (one request, a whole step, one token each), commits and
+    releases: the same answers, page ids, tables, lengths and free counts after every call."""
+    import numpy as np
+    import plain_books as PB
+    rng = random.Random(seed)
+    specs = [(2, 16, 0)] + ([(2, 16, window)] if window else [])
+    a = CacheBooks([GroupSpec(*s) for s in specs], [11] * len(specs), page_tokens, 4, 48)
+    b = PB.CacheBooks([PB.GroupSpec(*s) for s in specs], [11] * len(specs), page_tokens, 4, 48)
+    live = []
+    for _ in range(150):
+        op = rng.random()
+        if op < 0.2:
+            s = a.admit()
+            assert s == b.admit()
+            if s is not None:
+                live.append(s)
+        elif op < 0.5 and live:
+            s, n = rng.choice(live), rng.randint(1, 11)
+            if int(b.length[s]) + n > 48:
+                with pytest.raises(CacheError, match="limit"):
+                    a.reserve(s, n)
+                continue
+            assert a.pages_needed(s, n) == b.pages_needed(s, n)
+            ok = a.reserve(s, n)
+            assert ok == b.reserve(s, n)
+            if ok:
+                a.commit(s, n)
+                b.commit(s, n)
+        elif op < 0.7 and live:
+            # a whole step: all of its requests or none
+            slots = rng.sample(live, rng.randint(1, len(live)))
+            ns = [rng.randint(1, 9) for _ in slots]
+            if any(int(b.length[s]) + n > 48 for s, n in zip(slots, ns)):
+                continue
+            needs = [b.pages_needed(s, n) for s, n in zip(slots, ns)]
+            short = a.reserve_step(slots, ns)
+            assert (short is None) == b.fits(needs)
+            if short is None:
+                for s, n in zip(slots, ns):
+                    assert b.reserve(s, n)
+                for s, n in zip(slots, ns):
+                    a.commit(s, n)
+                    b.commit(s, n)
+            else:
+                assert short == [sum(n[g] for n in needs) for g in range(len(specs))]
+        elif op < 0.85 and live:
+            slots = rng.sample(live, rng.randint(1, len(live)))
+            if any(int(b.length[s]) + 1 > 48 for s in slots):
+                continue
+            ga, gb = a.reserve_one_each(slots), b.reserve_one_each(slots)
+            assert (ga is None) == (gb is None)
+            if ga is not None:
+                assert ga.tolist() == gb.tolist()
+                a.commit_one_each(slots)
+                b.commit_one_each(slots)
+        elif live:
+            s = live.pop(rng.randrange(len(live)))
+            a.release(s)
+            b.release(s)
+        a.check()
+        b.check()
+        assert (a.length == b.length).all() and (a.live == b.live).all()
+        assert a.free_pages() == b.free_pages() and a.free_slots == b.free_slots
+        for ga, gb in zip(a.groups, b.groups):
+            assert (ga.table == gb.table).all()
+            assert (ga.first_live == gb.first_live).all() and (ga.next_page == gb.next_page).all()
+        if live:
+            assert a.table_width(live) == max(1, max(int(g.next_page[s]) for g in b.groups for s in live))
+
+
+def test_native_step_layout():
+    """tokens | positions | row -> request | request starts | prior lengths | slots | wanted rows |
+    a slab of block-table rows per group, as the kernels read them."""
+    import numpy as np
+    b = books(pages=12, window=6, page_tokens=4, max_seqs=3, ctx=40)
+    s0, s1 = b.admit(), b.admit()
+    assert b.reserve(s0, 7) and b.reserve(s1, 2)
+    b.commit(s0, 7)
+    b.commit(s1, 2)
+    slots = np.array([s1, s0], dtype=np.int32)
+    counts = np.array([3, 1], dtype=np.int32)
+    assert b.reserve_step(slots, counts) is None
+    tokens = np.array([10, 11, 12, 20], dtype=np.int32)
+    n_want, wants = np.array([2, 1], dtype=np.int32), np.array([0, 2, 0], dtype=np.int32)
+    width = b.table_width([s0, s1])
+    assert width == 2
+    out = np.full(64, -7, dtype=np.int32)
+    n = b.layout_step(slots, counts, tokens, n_want, wants, width, out)
+    T, R, W, G = 4, 2, 3, 2
+    assert n == 3 * T + (R + 1) + 2 * R + W + G * R * width
+    want = ([10, 11, 12, 20] + [2, 3, 4, 7] + [0, 0, 0, 1] + [0, 3, 4] + [2, 7] + [s1, s0] + [0, 2, 3]
+            + b.groups[0].table[[s1, s0], :2].reshape(-1).tolist() + b.groups[1].table[[s1, s0], :2].reshape(-1).tolist())
+    assert out[:n].tolist() == want and (out[n:] == -7).all()
+    with pytest.raises(CacheError, match="needs"):
+        b.layout_step(slots, counts, tokens, n_want, wants, width, out[:10])
+    with pytest.raises(CacheError, match="holds no request"):
+        b.layout_step(np.array([2], dtype=np.int32), counts[:1], tokens, n_want[:1], wants, width, out)
