@@ -33,7 +33,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: Qwen1.5-MoE-A2.7B sizes
+# the headline configuration: Qwen1.5-MoE-A2.7B sizes
 A27B = {
     "architectures": ["Qwen2MoeForCausalLM"], "hidden_size": 2048, "intermediate_size": 5632, "num_hidden_layers": 24,
     "num_attention_heads": 16, "num_key_value_heads": 16, "head_dim": 128, "vocab_size": 151936,
@@ -42,7 +42,7 @@ A27B = {
     "norm_topk_prob": False, "decoder_sparse_step": 1, "mlp_only_layers": [], "tie_word_embeddings": False,
     "use_sliding_window": False,
 }
-# BASELINE.json configs[3]: Qwen2-57B-A14B sizes (about 115 GB of bf16 weights); not the default run
+# the larger configuration: Qwen2-57B-A14B sizes (about 115 GB of bf16 weights); not the default run
 Q57B = {
     "architectures": ["Qwen2MoeForCausalLM"], "hidden_size": 3584, "intermediate_size": 18944, "num_hidden_layers": 28,
     "num_attention_heads": 28, "num_key_value_heads": 4, "head_dim": 128, "vocab_size": 151936,
