@@ -266,7 +266,9 @@ __global__ void __launch_bounds__(SELECT_ROWS * 32) router_select_partials_kerne
 // After the E routed groups come `extra` groups that every token belongs to (the chunks
 // of a shared expert run through the same grouped products): group E + c owns slots
 // [n + c * T, n + (c + 1) * T) and slot n + c * T + t reads token t.
-constexpr int GROUP_WARPS = 8;
+// GROUP_WARPS warps a block: 8 for the few picks of a decode step, 32 for a prompt's thousands
+// (a warp walks its stretch 32 picks at a time, so the walk is as long as the stretch).
+template <int GROUP_WARPS>
 __global__ void __launch_bounds__(GROUP_WARPS * 32) moe_group_kernel(
     const int* __restrict__ sel, int n, int k, int E, int extra, int* __restrict__ offsets,
     int* __restrict__ slot_token, int* __restrict__ slot_of_pick) {
@@ -392,6 +394,9 @@ CJ_EXPORT int cj_moe_group(const int* sel, int n_picks, int k, int E, int extra,
                            int* slot_of_pick, cudaStream_t stream) {
     if (E < 1 || k < 1 || n_picks < 0 || extra < 0) return CJ_ERR_SIZE;
     if (!sel || !offsets || !slot_token || !slot_of_pick) return CJ_ERR_ARG;
-    cj::launch(moe_group_kernel, dim3(E + extra), dim3(GROUP_WARPS * 32), 0, stream, sel, n_picks, k, E, extra, offsets, slot_token, slot_of_pick);
+    if (n_picks >= 2048)
+        cj::launch(moe_group_kernel<32>, dim3(E + extra), dim3(32 * 32), 0, stream, sel, n_picks, k, E, extra, offsets, slot_token, slot_of_pick);
+    else
+        cj::launch(moe_group_kernel<8>, dim3(E + extra), dim3(8 * 32), 0, stream, sel, n_picks, k, E, extra, offsets, slot_token, slot_of_pick);
     return launch_status();
 }

@@ -205,6 +205,29 @@ def test_gemm_swiglu_and_grouped(K, dtype):
     assert torch.allclose(hs2.double(), want2, atol=1e-5, rtol=1e-5)
 
 
+@pytest.mark.parametrize("T,k,E,extra", [(9, 2, 5, 0), (511, 4, 60, 0), (513, 4, 60, 2), (3000, 3, 7, 1)])
+def test_grouping_is_a_stable_sort_by_expert(K, T, k, E, extra):
+    """Few picks (8 warps a block) and thousands (32 warps): offsets count each expert's picks, the
+    slots of an expert keep pick order, every pick finds its slot; groups of every token follow."""
+    g = torch.Generator().manual_seed(T)
+    sel = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    n = T * k
+    offsets = torch.empty(E + extra + 1, dtype=torch.int32, device=DEV)
+    slot_token = torch.empty(n + extra * T, dtype=torch.int32, device=DEV)
+    slot_of_pick = torch.empty(n, dtype=torch.int32, device=DEV)
+    K.moe_group(sel.to(DEV), k, E, offsets, slot_token, slot_of_pick, extra_groups=extra)
+    flat = sel.flatten()
+    order = torch.sort(flat, stable=True).indices                      # slot -> pick
+    counts = torch.bincount(flat, minlength=E)
+    want_off = torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]).tolist() + [n + (c + 1) * T for c in range(extra)]
+    assert offsets.cpu().tolist() == want_off
+    assert slot_token[:n].cpu().tolist() == (order // k).tolist()
+    want_slot = torch.empty(n, dtype=torch.long)
+    want_slot[order] = torch.arange(n)
+    assert slot_of_pick.cpu().tolist() == want_slot.tolist()
+    assert slot_token[n:].cpu().tolist() == list(range(T)) * extra
+
+
 def test_router_kernel_meets_the_reference_constants(K):
     o, router, probe, gate = oracle_inputs()
     x = torch.stack([probe, -probe]).to(DEV)
