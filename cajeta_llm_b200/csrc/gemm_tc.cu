@@ -430,11 +430,17 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2,
     return cj::launch_status();
 }
 
-// stages chosen so that a block stays within ~200 KB of shared memory
+// stages chosen so that a block stays within ~200 KB of shared memory; products of few rows
+// (weights on the rows, up to 32 tokens) take all the shared memory there is: they are bound by
+// HBM, and what an SM has in flight is its ring (six stages of 34 KB instead of five: +2 %
+// decode tokens a second at batch 8; three stages, so that two kernels' blocks fit an SM
+// side by side: -7 %)
 template <int N_MMA, bool SWAP, bool DUAL, int EPI>
 int launch_auto(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2, const Args& a, cudaStream_t stream) {
     constexpr int stage = Smem<N_MMA, SWAP, DUAL, 1>::STAGE_BYTES;
-    constexpr int STAGES = (200 * 1024 / stage) > 8 ? 8 : (200 * 1024 / stage);
+    constexpr int budget = (SWAP && N_MMA <= 32 ? 222 : 200) * 1024;
+    constexpr int cap = SWAP && N_MMA <= 32 ? 12 : 8;
+    constexpr int STAGES = (budget / stage) > cap ? cap : (budget / stage);
     return launch<N_MMA, SWAP, DUAL, EPI, STAGES>(mx, mw, mw2, a, stream);
 }
 
