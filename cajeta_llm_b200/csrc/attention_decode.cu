@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ positions, const int* __restrict__ row_req,
     const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int head_batches,
     int window, float scale, float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters,
-    int max_splits) {
+    int max_splits, int merge_later) {
     cj::release_successor();
     constexpr int COLS = HD / 8;
     constexpr int WARPS = TC_THREADS / 32;
@@ -484,6 +484,10 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
         }
     }
     if (n_splits == 1) return;
+    // with many chunks in the step the merge is a kernel of its own (decode_merge_kernel): a block
+    // then ends with its partial stores, without the fence and the ticket's round trip to memory,
+    // and the SM's shared memory is free for the next chunk that much sooner
+    if (merge_later) return;
 
     // the last chunk of this (row, kv head, head batch) to finish merges all chunks, in chunk order
     __syncthreads();
@@ -516,6 +520,41 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
         }
         float inv = 1.0f / L;
         *(__nv_bfloat162*)(out + ((size_t)t * n_heads + h) * HD + 2 * d2) = __floats2bfloat162_rn(a.x * inv, a.y * inv);
+    }
+}
+
+// The merge of the chunks of every (row, head) as a kernel of its own, for steps whose attention
+// kernel left it out: a warp a (row, head), the chunks added in chunk order with the same
+// arithmetic as the in-kernel merge, so both ways give the same bits.
+template <int HD>
+__global__ void __launch_bounds__(128) decode_merge_kernel(
+    __nv_bfloat16* __restrict__ out, const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+    const int* __restrict__ positions, int T, int n_heads, int window, int max_splits) {
+    cj::release_successor();
+    const int lane = threadIdx.x & 31;
+    const long long idx = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (idx >= (long long)T * n_heads) return;
+    const int t = (int)(idx / n_heads);
+    const int p = __ldcg(positions + t);
+    const int from = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
+    const int n_splits = (p - from + TC_CHUNK) / TC_CHUNK;
+    if (n_splits == 1) return;                                  // that row's only chunk wrote the result itself
+    cj::after_predecessor();
+    const size_t slot0 = (size_t)idx * max_splits;
+    float M = -INFINITY;
+    for (int sidx = 0; sidx < n_splits; ++sidx) M = fmaxf(M, part_ml[(slot0 + sidx) * 2]);
+    for (int d2 = lane; d2 < HD / 2; d2 += 32) {
+        float L = 0.0f;
+        float2 a = make_float2(0.0f, 0.0f);
+        for (int sidx = 0; sidx < n_splits; ++sidx) {
+            float f = expf(part_ml[(slot0 + sidx) * 2] - M);
+            L += part_ml[(slot0 + sidx) * 2 + 1] * f;
+            float2 v = *(const float2*)(part_acc + (slot0 + sidx) * HD + 2 * d2);
+            a.x = fmaf(v.x, f, a.x);
+            a.y = fmaf(v.y, f, a.y);
+        }
+        float inv = 1.0f / L;
+        *(__nv_bfloat162*)(out + (size_t)idx * HD + 2 * d2) = __floats2bfloat162_rn(a.x * inv, a.y * inv);
     }
 }
 
@@ -566,7 +605,8 @@ CJ_EXPORT int cj_decode_attention(const void* q, void* out, const void* kplane, 
 CJ_EXPORT int cj_decode_attention_tc(const void* q, void* out, const void* kplane, const void* vplane, const int* positions,
                                      const int* row_req, const int* table, int table_stride, int page_tokens, int T,
                                      int n_heads, int n_kv, int hd, int window, float scale, int max_context,
-                                     float* part_acc, float* part_ml, int* counters, int max_splits, cudaStream_t stream) {
+                                     float* part_acc, float* part_ml, int* counters, int max_splits, int merge_later,
+                                     cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!q || !out || !kplane || !vplane || !positions || !row_req || !table || !part_acc || !part_ml || !counters) return CJ_ERR_ARG;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || page_tokens <= 0) return CJ_ERR_SIZE;
@@ -591,7 +631,10 @@ CJ_EXPORT int cj_decode_attention_tc(const void* q, void* out, const void* kplan
         cj::launch(decode_attention_tc_kernel<HD>, dim3(grid), dim3(TC_THREADS), smem, stream, (const __nv_bfloat16*)q, \
             (__nv_bfloat16*)out, (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane, positions, row_req, table, \
             table_stride, page_tokens, n_heads, n_kv, head_batches, window, scale, part_acc, part_ml, counters,        \
-            max_splits);                                                                                               \
+            max_splits, merge_later && splits > 1 ? 1 : 0);                                                            \
+        if (merge_later && splits > 1)                                                                                 \
+            cj::launch(decode_merge_kernel<HD>, dim3((unsigned)(((long long)T * n_heads + 3) / 4)), dim3(128), 0, stream, \
+                (__nv_bfloat16*)out, (const float*)part_acc, (const float*)part_ml, positions, T, n_heads, window, max_splits); \
     }
     if (hd == 128) LAUNCH(128) else LAUNCH(64)
 #undef LAUNCH

@@ -456,6 +456,12 @@ def test_decode_attention_split_kv(K, heads, n_kv, hd, page, window, chunk):
         qq[p] = q[i].double().cpu()
         want = P.attention(qq, ks[r].to(dtype).double()[:p + 1], vs[r].to(dtype).double()[:p + 1], window, scale)[p]
         assert torch.allclose(outs[0][i].double().cpu(), want, atol=2e-2, rtol=2e-2), (i, r, p)
+    if chunk == 0:
+        # the chunks merged by a kernel of its own (what steps with many rows do): the same bits
+        out2 = torch.full_like(q, 7.0)
+        K.decode_attention(q, out2, kp, vp, pos, req, table, page, heads, n_kv, hd, window, scale, max(lengths), scratch,
+                           merge_later=True)
+        assert torch.equal(out2, outs[0]) and int(scratch.counters.abs().sum()) == 0
     # the same row alone gives the same bits: the chunking depends on the row only
     out1 = torch.empty_like(q[3:4])
     K.decode_attention(q[3:4].contiguous(), out1, kp, vp, pos[3:4].contiguous(), req[3:4].contiguous(), table, page, heads,
