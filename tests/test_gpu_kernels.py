@@ -93,7 +93,7 @@ def test_rmsnorm_partial_sums_and_three_term_form(K, H):
 
 
 @pytest.mark.parametrize("dtype,H", [(torch.bfloat16, 2048), (torch.bfloat16, 72), (torch.float32, 100), (torch.bfloat16, 67)])
-@pytest.mark.parametrize("rows", [5, 300])
+@pytest.mark.parametrize("rows", [5, 300, 700])
 def test_gather_rows(K, dtype, H, rows):
     """Few rows: a block a row; many rows of a multiple of 16 bytes: a warp a row."""
     x = rnd(41, H, seed=11, dtype=dtype)
