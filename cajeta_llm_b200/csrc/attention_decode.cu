@@ -533,13 +533,18 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(
     cj::release_successor();
     const int lane = threadIdx.x & 31;
     const long long idx = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (idx >= (long long)T * n_heads) return;
-    const int t = (int)(idx / n_heads);
-    const int p = __ldcg(positions + t);
-    const int from = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
-    const int n_splits = (p - from + TC_CHUNK) / TC_CHUNK;
-    if (n_splits == 1) return;                                  // that row's only chunk wrote the result itself
+    const bool in_range = idx < (long long)T * n_heads;
+    int n_splits = 1;
+    if (in_range) {
+        const int p = __ldcg(positions + (int)(idx / n_heads));     // the step's metadata: settled before the step's first kernel
+        const int from = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
+        n_splits = (p - from + TC_CHUNK) / TC_CHUNK;
+    }
+    // Every warp waits, also one with nothing to merge: a grid none of whose blocks waited could
+    // complete while the attention kernel still runs, and the kernel after this one - which
+    // waits for this grid only - would then read `out` too early.
     cj::after_predecessor();
+    if (n_splits == 1) return;                                  // out of range, or that row's only chunk wrote the result itself
     const size_t slot0 = (size_t)idx * max_splits;
     float M = -INFINITY;
     for (int sidx = 0; sidx < n_splits; ++sidx) M = fmaxf(M, part_ml[(slot0 + sidx) * 2]);

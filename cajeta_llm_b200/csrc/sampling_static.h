@@ -26,6 +26,8 @@
 //     nothing in it has to start at zero, because the kernel writes every element of a row
 //     before it reads it.  Two calls whose kernels overlap on the GPU (different streams
 //     without an ordering between them) race on the array: order them.
+//   * Two host threads that make the first call on a device at the same moment both look the
+//     address up and both store the same value: harmless, so the look-up takes no lock.
 //   * It calls no cudaMalloc, cudaFree or any other allocating routine.
 //
 // Arguments and result are those of cj_sample without `scratch`: per row r, temperature[r]
@@ -38,7 +40,7 @@
 #include <cuda_runtime.h>
 
 #define CJ_SAMPLE_STATIC_MAX_FLOATS (1 << 20)
-#define CJ_SAMPLE_STATIC_TOO_LARGE (-3)
+#define CJ_SAMPLE_STATIC_TOO_LARGE (-6)     // its own code: -3 is the kernels' general "a size this kernel does not take"
 
 #ifdef __cplusplus
 extern "C" {

@@ -238,6 +238,10 @@ class ModelRunner:
         ``step`` once).  Raises :class:`OutOfPages` like ``step``."""
         if not self.cuda_graphs or self.cache.state:
             return None
+        # chained steps are steps like any other: the kernels' wait flags are looked at as often
+        self._calls = getattr(self, "_calls", 0) + 1
+        if self._calls % WAIT_CHECK_EVERY == 0:
+            self.check_waits()
         entries = [StepEntry(s, [0], [0]) for s in slots]
         return self._step_captured(entries, device_tokens=device_tokens)
 

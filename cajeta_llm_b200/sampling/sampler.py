@@ -72,8 +72,12 @@ class BatchSampler:
         top_k = np.array([p.top_k for p in params], dtype=np.int32)
         top_p = np.array([p.top_p for p in params], dtype=np.float32)
         pen = np.array([p.repeat_penalty for p in params], dtype=np.float32)
-        # only a row that actually draws consumes a number of its stream
-        u = np.array([r.unit_float() if p.temperature != 0.0 else 0.0 for p, r in zip(params, rngs)], dtype=np.float32)
+        # only a row that actually draws consumes a number of its stream: not a greedy row, and not
+        # a row whose top-k leaves one survivor (the reference returns that survivor without
+        # touching the stream, gen/Sampler.cajeta:190-194; a top-p that the first token already
+        # reaches is not seen on the host and does consume one)
+        u = np.array([r.unit_float() if p.temperature != 0.0 and p.top_k != 1 else 0.0 for p, r in zip(params, rngs)],
+                     dtype=np.float32)
         hist_off = np.zeros(n + 1, dtype=np.int32)
         flat: List[int] = []
         for i, (p, h) in enumerate(zip(params, histories)):

@@ -68,8 +68,34 @@ REAL_SIZES = {
     "decoder_sparse_step": 1, "mlp_only_layers": [], "tie_word_embeddings": False,
     "use_sliding_window": False,
 }
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "M": MEDIUM}
-SEEDS = {"A": 11, "B": 23, "C": 37, "M": 41}
+# Windowed layers on the fast bfloat16 kernels: head sizes 128 and 64 (split-KV decode, the
+# tcgen05 and the mma.sync prompt kernels), windows that are no multiple of a page (16) or of
+# a key chunk (128), one group of full layers beside one of windowed layers, every product
+# wide enough for the tensor cores.  Replayed with requests several windows long, so that the
+# windowed group gives pages back (table entries turn -1) while the request goes on.
+WINDOW_128 = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "hidden_size": 256, "intermediate_size": 384, "num_hidden_layers": 3,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 520,
+    "max_position_embeddings": 4096, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "num_experts": 6, "num_experts_per_tok": 2, "moe_intermediate_size": 128,
+    "shared_expert_intermediate_size": 256, "norm_topk_prob": True,
+    "decoder_sparse_step": 1, "mlp_only_layers": [1], "tie_word_embeddings": False,
+    "use_sliding_window": True, "sliding_window": 40, "max_window_layers": 1,
+}
+WINDOW_64 = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "hidden_size": 320, "intermediate_size": 256, "num_hidden_layers": 3,
+    "num_attention_heads": 6, "num_key_value_heads": 3, "head_dim": 64, "vocab_size": 777,
+    "max_position_embeddings": 4096, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+    "num_experts": 5, "num_experts_per_tok": 3, "moe_intermediate_size": 192,
+    "shared_expert_intermediate_size": 192, "norm_topk_prob": False,
+    "decoder_sparse_step": 1, "mlp_only_layers": [], "tie_word_embeddings": True,
+    "use_sliding_window": True, "sliding_window": 150, "max_window_layers": 2,
+}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "M": MEDIUM, "W": WINDOW_128, "X": WINDOW_64}
+SEEDS = {"A": 11, "B": 23, "C": 37, "M": 41, "W": 43, "X": 47}
+LONG_REQUESTS = ("W", "X")     # configurations replayed with requests of 200-400 tokens
 
 
 def write_model(model_dir: str, raw_config: dict, seed: int, store_dtype=torch.bfloat16) -> None:

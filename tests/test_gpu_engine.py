@@ -263,6 +263,66 @@ def test_captured_steps_with_prompt_portions_give_the_same_logits_as_uncaptured_
     helpers.assert_close(outs[True][-3:], want, "bfloat16", "captured mixed steps", margins)
 
 
+@pytest.mark.parametrize("name", ["W", "X"])
+def test_windowed_layers_on_the_fast_kernels_give_pages_back_and_match_the_plain_implementation(name, model_dirs):
+    """Head sizes 128 and 64 with a window (40 and 150 tokens: no multiple of a page or of a
+    128-key chunk), bfloat16: two requests are fed in portions that cross the window, then
+    decode side by side past several page trims - launched kernel by kernel and replayed from
+    graphs, with the same bits - and every position is held to the plain implementation.  The
+    windowed group must have given back all pages behind the window, and get them again."""
+    from cajeta_llm_b200.engine.step import StepEntry
+    cfg = helpers.CONFIGS[name]
+    vocab, w, page = cfg["vocab_size"], cfg["sliding_window"], 16
+    seqs = [helpers.random_tokens(vocab, n, seed=400 + n) for n in (330, 241)]
+    portions = [(57, 100, 73), (130, 31)]                      # then one by one
+    outs = {}
+    for graphs in (False, True):
+        r = runner_for(model_dirs[name], "bfloat16", page_tokens=page, max_seqs=2, max_tokens_per_seq=336,
+                       num_pages=2 * 21, cuda_graphs=graphs)
+        slots = [r.admit(), r.admit()]
+        at, got = [0, 0], [[], []]
+        for k in range(3):
+            entries = []
+            for i in range(2):
+                if k < len(portions[i]):
+                    n = portions[i][k]
+                    entries.append((i, StepEntry(slots[i], seqs[i][at[i]:at[i] + n], list(range(n)))))
+                    at[i] += n
+            out = r.step([e for _, e in entries])
+            lo = 0
+            for i, e in entries:
+                got[i].append(out[lo:lo + len(e.tokens)].clone())
+                lo += len(e.tokens)
+        books = r.cache.books
+        full = [g for g, spec in enumerate(r.cache.group_specs) if spec.window == 0]
+        windowed = [g for g, spec in enumerate(r.cache.group_specs) if spec.window > 0]
+        assert len(full) == 1 and len(windowed) == 1
+        while at[1] < len(seqs[1]):                            # both decode, then the longer one alone
+            out = r.step([StepEntry(slots[i], [seqs[i][at[i]]], [0]) for i in range(2)])
+            for i in range(2):
+                got[i].append(out[i:i + 1].clone())
+                at[i] += 1
+            for i in range(2):
+                held = books.groups[windowed[0]].held_pages(slots[i])
+                assert len(held) <= -(-w // page) + 1, (at[i], len(held))
+                assert len(books.groups[full[0]].held_pages(slots[i])) == -(-at[i] // page)
+        r.release(slots[1])
+        while at[0] < len(seqs[0]):
+            got[0].append(r.step([StepEntry(slots[0], [seqs[0][at[0]]], [0])]).clone())
+            at[0] += 1
+        books.check()
+        table = books.groups[windowed[0]].table[slots[0]]
+        first_live = (len(seqs[0]) + 1 - w) // page
+        assert (table[:first_live] == -1).all() and (table[first_live:-(-len(seqs[0]) // page)] >= 0).all()
+        outs[graphs] = [torch.cat(g).cpu() for g in got]
+        if graphs:
+            assert r.graph_replays >= 90
+    for i in range(2):
+        assert torch.equal(outs[True][i], outs[False][i])
+        helpers.assert_close(outs[True][i], helpers.plain_logits(model_dirs[name], seqs[i]), "bfloat16",
+                             f"{name} windowed request {i}", helpers.plain_margins(model_dirs[name], seqs[i]))
+
+
 def test_real_layer_sizes_match_the_plain_implementation(tmp_path):
     """Layers of the benchmark's sizes (fewer of them): a prompt in one step, in portions
     beside another request's decode tokens, and token by token, in float32 and bfloat16."""

@@ -259,16 +259,24 @@ def test_router_kernel_against_plain(K, E, k, H):
         assert sel[3].cpu().tolist() == list(range(k))
 
 
-def paged_setup(lengths, n_kv, hd, page, dtype, seed, scramble=True):
-    """K/V of several requests laid into scrambled pages; returns planes, table, dense copies."""
+def paged_setup(lengths, n_kv, hd, page, dtype, seed, scramble=True, live_from=None):
+    """K/V of several requests laid into scrambled pages; returns planes, table, dense copies.
+
+    ``live_from[r]``: request r has given back every page that lies wholly below that position
+    (what a windowed group does once the window has passed a page): the table entry is -1 and
+    the page itself, like every page no table names, holds NaN - another request may own it by
+    now, and nothing of it may reach a result.  The planes are views behind a guard page of NaN,
+    so that a kernel that did follow a -1 entry would show in the result instead of reading
+    outside the allocation."""
     g = torch.Generator().manual_seed(seed)
     pages_per = [-(-L // page) for L in lengths]
     total = sum(pages_per) + 3
     perm = torch.randperm(total, generator=g).tolist() if scramble else list(range(total))
     width = max(pages_per) + 2
     table = torch.full((len(lengths), width), -1, dtype=torch.int32)
-    kp = torch.zeros(total, n_kv, page, hd)
-    vp = torch.zeros(total, n_kv, page, hd)
+    fill = float("nan") if live_from is not None else 0.0
+    kp = torch.full((total + 1, n_kv, page, hd), fill)
+    vp = torch.full((total + 1, n_kv, page, hd), fill)
     ks, vs = [], []
     nxt = 0
     for r, L in enumerate(lengths):
@@ -278,11 +286,20 @@ def paged_setup(lengths, n_kv, hd, page, dtype, seed, scramble=True):
         for j in range(pages_per[r]):
             pg = perm[nxt]
             nxt += 1
+            if live_from is not None and (j + 1) * page <= live_from[r]:
+                continue                                   # given back: -1 in the table, NaN in the page
             table[r, j] = pg
             n = min(page, L - j * page)
-            kp[pg, :, :n] = k[j * page: j * page + n].transpose(0, 1)
-            vp[pg, :, :n] = v[j * page: j * page + n].transpose(0, 1)
-    return kp.to(dtype).to(DEV), vp.to(dtype).to(DEV), table.to(DEV), ks, vs
+            kp[1 + pg, :, :n] = k[j * page: j * page + n].transpose(0, 1)
+            vp[1 + pg, :, :n] = v[j * page: j * page + n].transpose(0, 1)
+            if live_from is not None:
+                kp[1 + pg, :, n:] = 1000.0                 # what an earlier owner left behind the request's end
+                vp[1 + pg, :, n:] = 1000.0
+    return kp.to(dtype).to(DEV)[1:], vp.to(dtype).to(DEV)[1:], table.to(DEV), ks, vs
+
+
+def window_start(p, window):
+    return p + 1 - window if window > 0 and p + 1 > window else 0
 
 
 @pytest.mark.parametrize("heads,n_kv,hd,page,window", [(4, 2, 16, 16, 0), (4, 1, 24, 16, 8), (6, 3, 40, 4, 0),
@@ -427,15 +444,18 @@ def test_sampler_distribution_and_draws_follow_the_plain_sampler(K, V):
 
 
 @pytest.mark.parametrize("heads,n_kv,hd,page,window", [(16, 16, 128, 16, 0), (14, 2, 128, 16, 0), (6, 3, 64, 8, 0),
-                                                         (8, 4, 64, 16, 200), (4, 1, 128, 16, 130), (24, 2, 64, 16, 0)])
+                                                         (8, 4, 64, 16, 200), (4, 1, 128, 16, 130), (24, 2, 64, 16, 0),
+                                                         (4, 2, 128, 16, 40), (6, 3, 64, 16, 150)])
 @pytest.mark.parametrize("chunk", [64, 128, 0])
 def test_decode_attention_split_kv(K, heads, n_kv, hd, page, window, chunk):
     """Rows of very different lengths (1 key, exactly one chunk, several chunks and a
     remainder) against the plain attention, on the FMA pipe (chunks of 64 or 128) and on the
-    tensor cores (chunk 0); run twice to see the arrival counters reset."""
+    tensor cores (chunk 0); run twice to see the arrival counters reset.  With a window the
+    pages behind it have been given back (-1 in the table, NaN where they were)."""
     lengths = [1, 128, 129, 700, 300, 17, 64, 65]
     dtype = torch.bfloat16
-    kp, vp, table, ks, vs = paged_setup(lengths, n_kv, hd, page, dtype, seed=70)
+    live_from = [window_start(L - 1, window) for L in lengths] if window > 0 else None
+    kp, vp, table, ks, vs = paged_setup(lengths, n_kv, hd, page, dtype, seed=70, live_from=live_from)
     rows = [(r, L - 1) for r, L in enumerate(lengths)]
     g = torch.Generator().manual_seed(71)
     q = torch.randn(len(rows), heads, hd, generator=g).to(dtype).to(DEV)
@@ -469,15 +489,44 @@ def test_decode_attention_split_kv(K, heads, n_kv, hd, page, window, chunk):
     assert torch.equal(out1[0], outs[0][3])
 
 
+def test_decode_merge_kernel_with_nothing_to_merge(K):
+    """Many short rows under a large context bound (what a captured decode step of a long
+    bucket sees early on): the launch has several chunks a row, the separate merge kernel is
+    launched, and no row has anything to merge.  The merge kernel must still order itself
+    behind the attention kernel, or the kernel after it could read the output too early; the
+    result must equal the in-kernel merge's, also when another kernel follows at once."""
+    heads, n_kv, hd, page = 16, 16, 128, 16
+    lengths = [1 + (7 * i) % 127 for i in range(64)]             # 64 rows x 16 heads = 1024 pairs, all below 128 keys
+    dtype = torch.bfloat16
+    kp, vp, table, ks, vs = paged_setup(lengths, n_kv, hd, page, dtype, seed=75)
+    g = torch.Generator().manual_seed(76)
+    q = torch.randn(len(lengths), heads, hd, generator=g).to(dtype).to(DEV)
+    pos = torch.tensor([L - 1 for L in lengths], dtype=torch.int32, device=DEV)
+    req = torch.arange(len(lengths), dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    scratch = K.DecodeScratch()
+    ref = torch.full_like(q, 7.0)
+    K.decode_attention(q, ref, kp, vp, pos, req, table, page, heads, n_kv, hd, 0, scale, 1024, scratch, merge_later=False)
+    for _ in range(5):
+        out = torch.full_like(q, 7.0)
+        copy = torch.empty_like(out)
+        K.decode_attention(q, out, kp, vp, pos, req, table, page, heads, n_kv, hd, 0, scale, 1024, scratch, merge_later=True)
+        K.gather_rows(out.view(len(lengths), -1), req, copy.view(len(lengths), -1))     # a kernel of this library right behind
+        assert torch.equal(out, ref) and torch.equal(copy, ref)
+
+
 @pytest.mark.parametrize("block_rows", [64, 128])
-@pytest.mark.parametrize("heads,n_kv,hd,page,window", [(4, 4, 128, 16, 0), (6, 2, 64, 16, 0), (8, 1, 128, 8, 70), (4, 2, 64, 16, 17)])
+@pytest.mark.parametrize("heads,n_kv,hd,page,window", [(4, 4, 128, 16, 0), (6, 2, 64, 16, 0), (8, 1, 128, 8, 70), (4, 2, 64, 16, 17),
+                                                         (6, 3, 64, 16, 150), (4, 2, 128, 16, 40)])
 def test_prefill_attention_tiles(K, heads, n_kv, hd, page, window, block_rows):
     """Requests with and without earlier tokens, portions that end inside a tile, a single
     token riding along; every row against the plain attention."""
     dtype = torch.bfloat16
     totals = [200, 64, 131, 40, 300]
     new = [200, 1, 67, 40, 130]                       # rows this step brings; the rest is already cached
-    kp, vp, table, ks, vs = paged_setup(totals, n_kv, hd, page, dtype, seed=90)
+    # with a window, what lies behind the window of a request's first new row has been given back
+    live_from = [window_start(t - n, window) for t, n in zip(totals, new)] if window > 0 else None
+    kp, vp, table, ks, vs = paged_setup(totals, n_kv, hd, page, dtype, seed=90, live_from=live_from)
     starts = [0]
     for n in new:
         starts.append(starts[-1] + n)

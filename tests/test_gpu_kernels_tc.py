@@ -105,12 +105,15 @@ def test_prefill_attention_tcgen05(K, heads, n_kv, window):
     that end inside a tile, a single token riding along, several key tiles (so the running
     maximum moves and the output is rescaled), a window that starts inside a tile; every
     row against the plain attention.  One far key is made to stand out for the last rows."""
-    from test_gpu_kernels import paged_setup
+    from test_gpu_kernels import paged_setup, window_start
     import math
     dtype, hd, page = torch.bfloat16, 128, 16
     totals = [700, 64, 131, 300, 513]
     new = [700, 1, 67, 130, 257]                      # rows this step brings; the rest is already cached
-    kp, vp, table, ks, vs = paged_setup(totals, n_kv, hd, page, dtype, seed=190)
+    # with a window, the pages behind the window of a request's first new row have been given
+    # back: -1 in the table, NaN where they were
+    live_from = [window_start(t - n, window) for t, n in zip(totals, new)] if window > 0 else None
+    kp, vp, table, ks, vs = paged_setup(totals, n_kv, hd, page, dtype, seed=190, live_from=live_from)
     # stale data in a page's unused tail must not reach the result
     tail = totals[2] % page
     kp[table[2, totals[2] // page].item(), :, tail:] = 3.0

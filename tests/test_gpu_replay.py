@@ -68,23 +68,23 @@ def add_chunks(tb, rid, toks, sizes):
     raise AssertionError("sizes do not cover the request")
 
 
-def add_mixed(tb, requests, seed, max_live=4):
+def add_mixed(tb, requests, seed, max_live=4, portion=(2, 11), tail=(3, 12)):
     """Up to ``max_live`` requests at a time; each first gets its prompt in portions of
-    2..11 tokens, then its last tokens one by one; a request may sit a step out."""
+    ``portion`` tokens, then its last ``tail`` tokens one by one; a request may sit a step out."""
     rng = random.Random(seed)
     waiting = list(requests.items())
     live = {}
     while waiting or live:
         while waiting and len(live) < max_live:
             rid, toks = waiting.pop(0)
-            live[rid] = [toks, 0, max(2, len(toks) - rng.randint(3, 12))]     # tokens, fed, where single tokens begin
+            live[rid] = [toks, 0, max(2, len(toks) - rng.randint(*tail))]     # tokens, fed, where single tokens begin
         parts, ending = [], []
         for rid, st in list(live.items()):
             toks, fed, single_from = st
             if len(live) > 1 and rng.random() < 0.2:
                 continue                                                       # left out of this step
             if fed < single_from:
-                n = min(rng.randint(2, 11), single_from - fed)
+                n = min(rng.randint(*portion), single_from - fed)
                 if single_from - fed - n == 1:
                     n += 1                                                     # never leave a portion of one prompt token
             else:
@@ -116,12 +116,33 @@ def build_trace(vocab, seed):
     return tb, toks
 
 
+def build_long_trace(vocab, seed):
+    """The same four ways of cutting with requests of 200-400 tokens: several windows long, so
+    that windowed layers give pages back while a request goes on, portions start and end in
+    the middle of a window, of a page and of a 128-key chunk, and decoding crosses page trims."""
+    tb = TraceBuilder()
+    lens = {"w0": 203, "d0": 290, "c0": 331, "c1": 397}
+    toks = {rid: helpers.random_tokens(vocab, n, seed + i) for i, (rid, n) in enumerate(lens.items())}
+    add_whole(tb, "w0", toks["w0"])
+    add_decode_tail(tb, "d0", toks["d0"])
+    add_chunks(tb, "c0", toks["c0"], [33, 2, 130, 7, 41, 2, 16, 100])
+    add_chunks(tb, "c1", toks["c1"], [150, 151, 2, 61, 33])
+    mixed = {f"m{i}": helpers.random_tokens(vocab, n, seed + 100 + i) for i, n in enumerate([210, 377, 64, 256, 301, 45])}
+    add_mixed(tb, mixed, seed, portion=(2, 70), tail=(20, 45))
+    toks.update(mixed)
+    return tb, toks
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "M"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "M", "W", "X"])
 def test_replay_every_way_of_cutting_matches_the_plain_implementation(name, dtype, model_dirs, tmp_path):
     vocab = helpers.CONFIGS[name]["vocab_size"]
-    tb, toks = build_trace(vocab, seed=5 + ord(name))
-    assert tb.peak <= 4 * 64 + 64
+    if name in helpers.LONG_REQUESTS:
+        tb, toks = build_long_trace(vocab, seed=5 + ord(name))
+        assert tb.peak <= 4 * 448
+    else:
+        tb, toks = build_trace(vocab, seed=5 + ord(name))
+        assert tb.peak <= 4 * 64 + 64
     # the pool holds exactly the peak: the mixed part frees and reuses pages all the time
     out = helpers.run_trace(model_dirs[name], dtype, tb.steps, str(tmp_path), max_tokens=tb.peak)
     worst = 0.0

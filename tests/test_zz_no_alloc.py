@@ -76,5 +76,5 @@ def test_static_scratch_sampler_refuses_what_does_not_fit():
     st = lib.cj_sample_static(_p(logits), rows, V, _p(temperature), _p(top_k), _p(top_p), _p(penalty), _p(uniform),
                               _p(history), _p(offsets), _p(out), stream)
     torch.cuda.synchronize()
-    assert st == -3                                               # CJ_SAMPLE_STATIC_TOO_LARGE
+    assert st == -6                                               # CJ_SAMPLE_STATIC_TOO_LARGE
     assert out.cpu().tolist() == [-1] * rows                      # nothing was launched
