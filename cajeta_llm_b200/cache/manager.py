@@ -29,10 +29,12 @@ from .pages import CacheBooks, CacheError, GroupSpec
 class CacheManager:
     def __init__(self, kv_needs: Sequence[Optional[KvNeed]], state_needs: Sequence[Optional[StateNeed]],
                  cache_from: Sequence[Optional[int]], page_tokens: int, max_seqs: int, max_tokens_per_seq: int,
-                 num_pages: int, cache_dtype: torch.dtype, device: torch.device | str | None):
+                 num_pages, cache_dtype: torch.dtype, device: torch.device | str | None):
         """``kv_needs[i]`` / ``state_needs[i]`` belong to schedule entry ``i``;
         ``cache_from[i]`` names the entry whose plane entry ``i`` reads instead of owning
-        one.  ``num_pages`` is the pool size of every group.  ``device=None`` keeps only
+        one.  ``num_pages`` is the pool size of every group, or a function
+        ``GroupSpec -> pages`` that sizes each group by its own need (a windowed group holds
+        far fewer pages a request than one that keeps every key).  ``device=None`` keeps only
         the books (no tensors), for tests of the bookkeeping."""
         n = len(kv_needs)
         self.page_tokens = page_tokens
@@ -70,13 +72,15 @@ class CacheManager:
             self.entry_group[i] = self.entry_group[src]
             self.entry_plane[i] = self.entry_plane[src]
         self.group_specs = specs
-        self.books = CacheBooks(specs, [num_pages] * len(specs), page_tokens, max_seqs, max_tokens_per_seq)
+        counts = [int(num_pages(spec)) if callable(num_pages) else int(num_pages) for spec in specs]
+        self.group_pages = counts
+        self.books = CacheBooks(specs, counts, page_tokens, max_seqs, max_tokens_per_seq)
         self.k: List[torch.Tensor] = []
         self.v: List[torch.Tensor] = []
         self.state: Dict[int, torch.Tensor] = {}
         if self.device is not None:
-            for spec, planes in zip(specs, plane_count):
-                shape = (planes, num_pages, spec.kv_heads, page_tokens, spec.head_dim)
+            for spec, planes, pages in zip(specs, plane_count, counts):
+                shape = (planes, pages, spec.kv_heads, page_tokens, spec.head_dim)
                 self.k.append(torch.zeros(shape, dtype=cache_dtype, device=self.device))
                 self.v.append(torch.zeros(shape, dtype=cache_dtype, device=self.device))
             for i, need in enumerate(state_needs):
@@ -99,6 +103,9 @@ class CacheManager:
 
     def pages_needed(self, slot: int, n_new: int) -> List[int]:
         return self.books.pages_needed(slot, n_new)
+
+    def pages_to_hold(self, slot: int, n_new: int, step_tokens: int = 0) -> List[int]:
+        return self.books.pages_to_hold(slot, n_new, step_tokens)
 
     def free_pages(self) -> List[int]:
         return self.books.free_pages()

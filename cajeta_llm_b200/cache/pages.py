@@ -232,6 +232,24 @@ class CacheBooks:
             self._fail()
         return self._needs[:len(self.groups)].tolist()
 
+    def pages_to_hold(self, slot: int, n_new: int, step_tokens: int = 0) -> List[int]:
+        """Pages per group that the request in ``slot`` will hold at most, beyond those it holds
+        now, while its next ``n_new`` tokens are fed in steps of at most ``step_tokens`` each
+        (0: in one step).  A group that keeps every key needs them all; a windowed group gives
+        pages back as it goes and never holds more than its window plus one step's tokens span,
+        ``ceil((window + step_tokens) / page_tokens) + 1``.  What admission counts with."""
+        raw = self.pages_needed(slot, n_new)
+        if step_tokens <= 0:
+            return raw
+        out = []
+        for g, need in zip(self.groups, raw):
+            if g.spec.window > 0:
+                most = -(-(g.spec.window + step_tokens) // self.page_tokens) + 1
+                held = int(g.next_page[slot]) - int(g.first_live[slot])
+                need = min(need, max(0, most - held))
+            out.append(need)
+        return out
+
     def free_pages(self) -> List[int]:
         return [g.allocator.free_count for g in self.groups]
 

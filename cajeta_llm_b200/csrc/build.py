@@ -41,6 +41,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_decode": "attention_decode.cu",
     "attention_prefill": "attention_prefill.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",
+    "random_fill": "random_fill.cu",
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "sampling_static.h"]
 

@@ -95,12 +95,13 @@ _ll = ctypes.c_longlong
 _f = ctypes.c_float
 
 
-def embed_gather(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
-    """out[t, :] = table[ids[t], :] widened to float32.  out: [T, H] float32."""
+def embed_gather(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float = 0.0) -> None:
+    """out[t, :] = table[ids[t], :] widened to float32 (times ``scale`` unless that is 0).  out: [T, H] float32."""
     _need(out, "out", torch.float32), _need(table, "table"), _need(ids, "ids", torch.int32)
     T, H = out.shape
     V = table.shape[0]
-    st = library("rowwise").cj_embed_gather(_ptr(out), _ptr(table), _i(_code(table)), _ptr(ids), _i(T), _i(H), _i(V), _stream())
+    st = library("rowwise").cj_embed_gather(_ptr(out), _ptr(table), _i(_code(table)), _ptr(ids), _i(T), _i(H), _i(V), _f(scale),
+                                            _stream())
     _check(st, "embed_gather")
 
 
@@ -207,13 +208,29 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v
     _check(st, "paged_attention")
 
 
+def _pin_and_gap(pin: Optional[torch.Tensor], gap: Optional[torch.Tensor], T: int, top_k: int) -> None:
+    if pin is not None:
+        _need(pin, "pin", torch.int32)
+        if pin.numel() != T * top_k or gap is not None:
+            raise KernelError(f"router: pin must hold {T} x {top_k} experts and excludes gap")
+    if gap is not None:
+        _need(gap, "gap", torch.float32)
+        if gap.numel() != T:
+            raise KernelError(f"router: gap must hold {T} margins")
+
+
 def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[torch.Tensor], top_k: int,
-                norm_topk: bool, sel: torch.Tensor, weights: torch.Tensor, shared_scale: Optional[torch.Tensor]) -> None:
-    """Router logits, softmax over all experts, top-k and the shared expert's sigmoid gate."""
+                norm_topk: bool, sel: torch.Tensor, weights: torch.Tensor, shared_scale: Optional[torch.Tensor],
+                pin: Optional[torch.Tensor] = None, gap: Optional[torch.Tensor] = None) -> None:
+    """Router logits, softmax over all experts, top-k and the shared expert's sigmoid gate.
+    ``pin`` (int32 [T, k]): the experts are given, not chosen; the weights are still the row's own
+    probabilities of them.  ``gap`` (float32 [T], not with ``pin``): each row's routing margin
+    (p_k - p_{k+1}) / p_k out."""
     _need(x, "x", torch.float32), _need(router_w, "router_w", torch.float32)
     _need(sel, "sel", torch.int32), _need(weights, "weights", torch.float32)
     T, H = x.shape
     E = router_w.shape[0]
+    _pin_and_gap(pin, gap, T, top_k)
     if E > 1024:
         raise KernelError(f"router_topk: {E} experts; this kernel takes at most 1024")
     if shared_gate is not None:
@@ -224,7 +241,7 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
         tickets = _router_tickets[x.device] = torch.zeros((4,), dtype=torch.int32, device=x.device)
     st = library("moe_route").cj_router_topk(_ptr(x), _ptr(router_w), _ptr(shared_gate), _i(T), _i(H), _i(E), _i(top_k),
                                              _i(1 if norm_topk else 0), _ptr(sel), _ptr(weights), _ptr(shared_scale),
-                                             _ptr(logits), _ptr(tickets), _stream())
+                                             _ptr(logits), _ptr(tickets), _ptr(pin), _ptr(gap), _stream())
     _check(st, "router_topk")
     if T > 32:
         global launches
@@ -232,7 +249,8 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
 
 
 def router_select(partials: torch.Tensor, num_experts: int, top_k: int, norm_topk: bool, sel: torch.Tensor,
-                  weights: torch.Tensor, shared_scale: Optional[torch.Tensor]) -> None:
+                  weights: torch.Tensor, shared_scale: Optional[torch.Tensor], pin: Optional[torch.Tensor] = None,
+                  gap: Optional[torch.Tensor] = None) -> None:
     """Softmax over all experts, top-k and the shared gate's sigmoid from router logits given
     as partial sums ``[S, T, ld]`` (float32; column ``num_experts`` holds the gate's dot when
     ``shared_scale`` is given); the partials of a row are added in order first."""
@@ -242,11 +260,12 @@ def router_select(partials: torch.Tensor, num_experts: int, top_k: int, norm_top
     if num_experts > 1024:
         raise KernelError(f"router_select: {num_experts} experts; this kernel takes at most 1024")
     S, T, ld = partials.shape
+    _pin_and_gap(pin, gap, T, top_k)
     if shared_scale is not None:
         _need(shared_scale, "shared_scale", torch.float32)
     st = library("moe_route").cj_router_select(_ptr(partials), _i(S), _ll(partials.stride(0)), _i(ld), _i(T), _i(num_experts),
                                                _i(top_k), _i(1 if norm_topk else 0), _ptr(sel), _ptr(weights),
-                                               _ptr(shared_scale), _stream())
+                                               _ptr(shared_scale), _ptr(pin), _ptr(gap), _stream())
     _check(st, "router_select")
 
 
@@ -311,6 +330,15 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
                                        _ptr(repeat_penalty), _ptr(uniform), _ptr(history), _ptr(history_offsets),
                                        _ptr(scratch), _ptr(out), _stream())
     _check(st, "sample")
+
+
+def random_fill(out: torch.Tensor, key: int, scale: float) -> None:
+    """out.flat[i] = float32(n(key, i)) * scale, n a centred sum of eight 16-bit integers hashed
+    from (key, i); float32 or bfloat16 (see weights/random_fill.py for the same on the host)."""
+    _need(out, "out")
+    st = library("random_fill").cj_random_fill(_ptr(out), _i(_code(out)), _ll(out.numel()), ctypes.c_ulonglong(key & (2 ** 64 - 1)),
+                                               _f(scale), _stream())
+    _check(st, "random_fill")
 
 
 EPI_STORE_F32, EPI_ACC_F32, EPI_SWIGLU_BF16, EPI_STORE_BF16 = 0, 1, 2, 3

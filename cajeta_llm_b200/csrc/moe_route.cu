@@ -99,8 +99,14 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_logits_kernel(
 
 // softmax over all experts, top-k, optional renormalisation, the shared gate's sigmoid: one
 // warp per row; probs is the warp's scratch of E floats in shared memory
+// pin (int32 [T, k], may be null): the experts are not chosen here but given - the weights are
+// still this row's own probabilities of them (how the reference replays recorded selections,
+// model/MoeFfn.cajeta:626-706).  gap (float32 [T], may be null; not with pin): the row's
+// routing margin (p_k - p_{k+1}) / p_k, 1 when every expert is picked - how far the row is
+// from another choice (model/MoeFfn.cajeta:135-149).
 __device__ __forceinline__ void select_row(const float* row, int t, int E, int k, int norm_topk, int* __restrict__ sel,
-                                           float* __restrict__ w, float* __restrict__ shared_scale, float* probs, int lane) {
+                                           float* __restrict__ w, float* __restrict__ shared_scale, float* probs, int lane,
+                                           const int* __restrict__ pin, float* __restrict__ gap) {
     if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-row[E]));
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
@@ -115,7 +121,24 @@ __device__ __forceinline__ void select_row(const float* row, int t, int E, int k
     for (int e = lane; e < E; e += 32) probs[e] = probs[e] / sum;
     __syncwarp();
 
-    float wsum = 0.0f;
+    if (pin) {
+        if (lane == 0) {
+            float total = 0.0f;
+            for (int j = 0; j < k; ++j) {
+                int e = pin[t * k + j];
+                float p = (e >= 0 && e < E) ? probs[e] : __int_as_float(0x7fc00000);   // a pick outside the experts shows as NaN
+                sel[t * k + j] = (e >= 0 && e < E) ? e : 0;
+                w[t * k + j] = p;
+                total += p;
+            }
+            if (norm_topk) {
+                if (total < 0.00006103515625f) total = 0.00006103515625f;
+                for (int j = 0; j < k; ++j) w[t * k + j] = w[t * k + j] / total;
+            }
+        }
+        return;
+    }
+    float wsum = 0.0f, last = 0.0f;
     for (int j = 0; j < k; ++j) {
         float bp = -1.0f;
         int best = -1;
@@ -136,7 +159,14 @@ __device__ __forceinline__ void select_row(const float* row, int t, int E, int k
         else if (lane == 0) probs[best] = -1.0f;
         if (lane == 0) { sel[t * k + j] = best; w[t * k + j] = bp; }
         wsum += bp;
+        last = bp;
         __syncwarp();
+    }
+    if (gap) {
+        float next = -1.0f;                          // the largest probability left
+        for (int e = lane; e < E; e += 32) next = fmaxf(next, probs[e]);
+        next = warp_max(next);
+        if (lane == 0) gap[t] = (k < E && last > 0.0f) ? (last - next) / last : 1.0f;
     }
     if (norm_topk && lane == 0) {
         if (wsum < 0.00006103515625f) wsum = 0.00006103515625f;
@@ -155,7 +185,7 @@ constexpr int SMALL_ROWS = 8;
 __global__ void __launch_bounds__(SMALL_ROWS * 32) router_small_kernel(
     const float* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ shared_gate, int T, int H,
     int E, int k, int norm_topk, float* __restrict__ logits, int* __restrict__ sel, float* __restrict__ w,
-    float* __restrict__ shared_scale, int* __restrict__ tickets) {
+    float* __restrict__ shared_scale, int* __restrict__ tickets, const int* __restrict__ pin, float* __restrict__ gap) {
     cj::release_successor();
     __shared__ float probs[SMALL_ROWS][MAX_EXPERTS];
     __shared__ int is_last;
@@ -221,17 +251,17 @@ __global__ void __launch_bounds__(SMALL_ROWS * 32) router_small_kernel(
     if (!is_last) return;
     __threadfence();
     if (t < T) {
-        select_row(logits + (size_t)t * n_cols, t, E, k, norm_topk, sel, w, shared_scale, probs[warp], lane);
+        select_row(logits + (size_t)t * n_cols, t, E, k, norm_topk, sel, w, shared_scale, probs[warp], lane, pin, gap);
     }
 }
 
 __global__ void __launch_bounds__(32) router_select_kernel(
     const float* __restrict__ logits, int E, int n_cols, int k, int norm_topk, int* __restrict__ sel,
-    float* __restrict__ w, float* __restrict__ shared_scale) {
+    float* __restrict__ w, float* __restrict__ shared_scale, const int* __restrict__ pin, float* __restrict__ gap) {
     cj::after_predecessor();
     cj::release_successor();
     __shared__ float probs[MAX_EXPERTS];
-    select_row(logits + (size_t)blockIdx.x * n_cols, blockIdx.x, E, k, norm_topk, sel, w, shared_scale, probs, threadIdx.x);
+    select_row(logits + (size_t)blockIdx.x * n_cols, blockIdx.x, E, k, norm_topk, sel, w, shared_scale, probs, threadIdx.x, pin, gap);
 }
 
 // The selection from logits that a product split along K left as partial sums
@@ -240,7 +270,8 @@ __global__ void __launch_bounds__(32) router_select_kernel(
 constexpr int SELECT_ROWS = 4;
 __global__ void __launch_bounds__(SELECT_ROWS * 32) router_select_partials_kernel(
     const float* __restrict__ partials, int n_partials, long long partial_stride, int ld, int T, int E, int k,
-    int norm_topk, int* __restrict__ sel, float* __restrict__ w, float* __restrict__ shared_scale) {
+    int norm_topk, int* __restrict__ sel, float* __restrict__ w, float* __restrict__ shared_scale,
+    const int* __restrict__ pin, float* __restrict__ gap) {
     cj::after_predecessor();
     cj::release_successor();
     __shared__ float probs[SELECT_ROWS][MAX_EXPERTS];
@@ -255,7 +286,7 @@ __global__ void __launch_bounds__(SELECT_ROWS * 32) router_select_partials_kerne
         row[warp][e] = v;
     }
     __syncwarp();
-    select_row(row[warp], t, E, k, norm_topk, sel, w, shared_scale, probs[warp], lane);
+    select_row(row[warp], t, E, k, norm_topk, sel, w, shared_scale, probs[warp], lane, pin, gap);
 }
 
 // Counting sort of the picks (token t, choice j) by expert, stable.  One block per
@@ -336,9 +367,10 @@ __global__ void __launch_bounds__(GROUP_WARPS * 32) moe_group_kernel(
 
 // logits: scratch [T, E + 1] float32 (column E holds the shared gate's dot when a gate is given).
 // tickets: int32 [4], zero before the first use (the kernel leaves them zero); may be null, the two-launch form is then used.
+// pin: int32 [T, k] experts given instead of chosen, or null.  gap: float32 [T] routing margins out, or null.
 CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* shared_gate, int T, int H, int E, int k,
                              int norm_topk, int* sel, float* w, float* shared_scale, float* logits, int* tickets,
-                             cudaStream_t stream) {
+                             const int* pin, float* gap, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!x || !Wr || !sel || !w || !logits || H <= 0) return CJ_ERR_ARG;
     if (shared_gate && !shared_scale) return CJ_ERR_ARG;
@@ -347,7 +379,7 @@ CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* share
     if (T <= 32 && tickets) {
         dim3 grid_small(n_cols, (T + SMALL_ROWS - 1) / SMALL_ROWS);
         cj::launch(router_small_kernel, dim3(grid_small), dim3(SMALL_ROWS * 32), 0, stream, x, Wr, shared_gate, T, H, E, k, norm_topk, logits, sel, w,
-                                                                         shared_gate ? shared_scale : nullptr, tickets);
+                                                                         shared_gate ? shared_scale : nullptr, tickets, pin, gap);
         return launch_status();
     }
     // rows of x staged per block: as many as fit 200 KB of shared memory, at most 8
@@ -373,18 +405,20 @@ CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* share
 #undef LAUNCH
     int st = launch_status();
     if (st) return st;
-    cj::launch(router_select_kernel, dim3(T), dim3(32), 0, stream, logits, E, n_cols, k, norm_topk, sel, w, shared_gate ? shared_scale : nullptr);
+    cj::launch(router_select_kernel, dim3(T), dim3(32), 0, stream, logits, E, n_cols, k, norm_topk, sel, w, shared_gate ? shared_scale : nullptr,
+               pin, gap);
     return launch_status();
 }
 
 // partials: [n_partials][T][ld] float32 logits (column E the shared gate's dot when shared_scale is given).
 CJ_EXPORT int cj_router_select(const float* partials, int n_partials, long long partial_stride, int ld, int T, int E, int k,
-                               int norm_topk, int* sel, float* w, float* shared_scale, cudaStream_t stream) {
+                               int norm_topk, int* sel, float* w, float* shared_scale, const int* pin, float* gap,
+                               cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!partials || !sel || !w || n_partials < 1) return CJ_ERR_ARG;
     if (E < 1 || E > MAX_EXPERTS || k < 1 || k > E || ld < E + (shared_scale ? 1 : 0)) return CJ_ERR_SIZE;
     cj::launch(router_select_partials_kernel, dim3((T + SELECT_ROWS - 1) / SELECT_ROWS), dim3(SELECT_ROWS * 32), 0, stream, 
-        partials, n_partials, partial_stride, ld, T, E, k, norm_topk, sel, w, shared_scale);
+        partials, n_partials, partial_stride, ld, T, E, k, norm_topk, sel, w, shared_scale, pin, gap);
     return launch_status();
 }
 

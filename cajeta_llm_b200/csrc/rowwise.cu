@@ -6,12 +6,13 @@
 using namespace cj;
 
 // ---------------------------------------------------------------------------------
-// embedding: hs[t, :] = table[id_t, :] widened to float32 (the residual stream)
+// embedding: hs[t, :] = table[id_t, :] widened to float32 (the residual stream), times
+// `scale` when that is not 0 (the reference's embedScale, 0 = none)
 // reference: model/Embedding.cajeta:73-81, gather kernel io/QuantKernel.cajeta:40720
 // ---------------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_gather_kernel(float* __restrict__ out, const TW* __restrict__ table,
-                                    const int* __restrict__ ids, int H, int V) {
+                                    const int* __restrict__ ids, int H, int V, float scale) {
     cj::after_predecessor();
     cj::release_successor();
     int t = blockIdx.x;
@@ -19,18 +20,19 @@ __global__ void embed_gather_kernel(float* __restrict__ out, const TW* __restric
     bool ok = id >= 0 && id < V;   // the host checks ids; an id out of range reads nothing
     const TW* src = table + (size_t)(ok ? id : 0) * H;
     float* dst = out + (size_t)t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ok ? to_f32(src[i]) : 0.0f;
+    const float f = scale != 0.0f ? scale : 1.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ok ? to_f32(src[i]) * f : 0.0f;
 }
 
 CJ_EXPORT int cj_embed_gather(float* out, const void* table, int table_dtype, const int* ids,
-                              int T, int H, int V, cudaStream_t stream) {
+                              int T, int H, int V, float scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!out || !table || !ids || H <= 0 || V <= 0) return CJ_ERR_ARG;
     int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == CJ_F32)
-        cj::launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, out, (const float*)table, ids, H, V);
+        cj::launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, out, (const float*)table, ids, H, V, scale);
     else if (table_dtype == CJ_BF16)
-        cj::launch(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, out, (const __nv_bfloat16*)table, ids, H, V);
+        cj::launch(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, out, (const __nv_bfloat16*)table, ids, H, V, scale);
     else
         return CJ_ERR_DTYPE;
     return launch_status();

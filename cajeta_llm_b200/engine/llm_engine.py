@@ -36,7 +36,8 @@ class LlmEngine:
         self.runner = ModelRunner(model, page_tokens=options.block_tokens, max_seqs=options.max_seqs,
                                   max_tokens_per_seq=options.ctx,
                                   num_pages=options.num_blocks if options.num_blocks > 0 else None,
-                                  cuda_graphs=options.cuda_graphs)
+                                  cuda_graphs=options.cuda_graphs,
+                                  max_step_tokens=min(options.max_batch_tokens, options.chunk or options.max_batch_tokens))
         self.sampler = BatchSampler(model.runtime.device, model.vocab)
         self._scheduler = Scheduler(self.runner, self.sampler, max_batch_tokens=options.max_batch_tokens,
                                     chunk=options.chunk, eog_token_ids=self._eog, lookahead=options.lookahead)

@@ -14,9 +14,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..config.base import ModelConfig, get_architecture, load_config
-from ..csrc import kernels as K
 from ..parts.base import KvNeed, Runtime, StateNeed, make_part
-from ..parts.linear import project
 from ..parts.plan import ModelPlan, ParamSpec
 from ..weights.sources import RandomWeights, SafetensorsWeights
 
@@ -28,45 +26,44 @@ class Model:
         self.runtime = runtime
         self.hidden = plan.hidden_size
         self.vocab = plan.vocab_size
+        # both ends are parts like the layers' parts: the plan names their kinds
+        self.embedding_part = make_part("embedding", plan.embedding, "", runtime, vocab_size=self.vocab,
+                                        hidden_size=self.hidden, weight_name=plan.embedding_name)
         self.blocks = [make_part("block", layer.block, layer.prefix, runtime, layer=layer) for layer in plan.layers]
         self.final_norm = make_part("norm", plan.final_norm, plan.final_norm_prefix, runtime)
-        self.embedding: Optional[torch.Tensor] = None
-        self.lm_head: Optional[torch.Tensor] = None
+        self.head_part = make_part("head", plan.head, "", runtime, vocab_size=self.vocab, hidden_size=self.hidden,
+                                   weight_name=plan.lm_head_name, embedding=self.embedding_part)
+
+    def parts(self):
+        return [self.embedding_part] + list(self.blocks) + [self.final_norm, self.head_part]
+
+    @property
+    def embedding(self) -> Optional[torch.Tensor]:
+        """The embedding table (a tied head reads the same tensor)."""
+        return getattr(self.embedding_part, "table", None)
+
+    @property
+    def lm_head(self) -> Optional[torch.Tensor]:
+        return getattr(self.head_part, "weight", None)
 
     # -- tensors ---------------------------------------------------------------------
     def params(self) -> Dict[str, ParamSpec]:
-        out: Dict[str, ParamSpec] = {self.plan.embedding_name: ParamSpec((self.vocab, self.hidden))}
-        for b in self.blocks:
-            out.update(b.params())
-        out.update(self.final_norm.params())
-        if self.plan.lm_head_name is not None:
-            out[self.plan.lm_head_name] = ParamSpec((self.vocab, self.hidden))
+        out: Dict[str, ParamSpec] = {}
+        for p in self.parts():
+            out.update(p.params())
         return out
 
     def libraries(self) -> set:
         """The kernel libraries this model's steps will call (embedding, norms and head included)."""
         out = {"rowwise", "gemm_simt", "sampling"}
-        for b in self.blocks:
-            out |= b.libraries()
-        out |= self.final_norm.libraries()
-        if self.runtime.fast_kernels and self.hidden >= 128:
-            out.add("gemm_tc")
+        for p in self.parts():
+            out |= p.libraries()
         return out
 
     def load(self, source) -> None:
-        schema = self.params()
-        source.check(schema)
-        rt = self.runtime
-        name = self.plan.embedding_name
-        self.embedding = rt.place(source.get(name, schema[name]), schema[name])
-        for b in self.blocks:
-            b.load(source)
-        self.final_norm.load(source)
-        if self.plan.lm_head_name is not None:
-            name = self.plan.lm_head_name
-            self.lm_head = rt.place(source.get(name, schema[name]), schema[name])
-        else:
-            self.lm_head = self.embedding
+        source.check(self.params())
+        for p in self.parts():
+            p.load(source)
 
     # -- what the cache manager must provide, per schedule entry ---------------------
     def kv_needs(self) -> List[Optional[KvNeed]]:
@@ -80,17 +77,13 @@ class Model:
 
     # -- the pieces of a step outside the blocks -------------------------------------
     def embed(self, token_ids: torch.Tensor) -> torch.Tensor:
-        hs = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
-        K.embed_gather(hs, self.embedding, token_ids)
-        return hs
+        return self.embedding_part.forward(token_ids)
 
     def logits(self, hs: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """Final norm and head on the wanted rows only; float32 ``[len(rows), vocab]``
         (model/CausalLM.cajeta:1712-1718)."""
         x, _ = self.final_norm.forward(hs, row_index=rows)
-        out = torch.empty((rows.numel(), self.vocab), dtype=torch.float32, device=hs.device)
-        project(self.runtime, x, self.lm_head, out)
-        return out
+        return self.head_part.forward(x)
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
@@ -101,15 +94,13 @@ class Model:
         return total
 
     def _tensors(self):
-        yield self.embedding
-        yield self.lm_head
-        stack = list(self.blocks) + [self.final_norm]
+        stack = self.parts()
         while stack:
             p = stack.pop()
             for v in vars(p).values():
                 if isinstance(v, torch.Tensor):
                     yield v
-                elif hasattr(v, "params") and hasattr(v, "runtime"):
+                elif hasattr(v, "params") and hasattr(v, "runtime") and v is not getattr(p, "embedding", None):
                     stack.append(v)
 
 

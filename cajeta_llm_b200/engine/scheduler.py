@@ -7,8 +7,9 @@ Policy, after the reference's scheduler (sched/Scheduler.cajeta:414-605):
 * admission at the start and at the end of every iteration: preempted requests first
   (oldest preemption first), then waiters in submission order; a request needs a free
   slot and pages for its whole uncached suffix plus one page of decode headroom per
-  cache group, counted against the free pages that running requests have not yet
-  claimed for their own prompts; admission stops at the first request that does not
+  cache group (in a windowed group: for no more than the window plus one step's tokens,
+  since such a group gives pages back as the request goes on), counted against the free
+  pages that running requests have not yet claimed for their own prompts; admission stops at the first request that does not
   fit, nothing is skipped (sched/Scheduler.cajeta:1068-1151);
 * every iteration is ONE mixed step under a token budget: the single decode tokens of
   all running requests first, then prompt portions in admission order until the budget
@@ -160,9 +161,13 @@ class Scheduler:
         cache = self.runner.cache
         total = [0] * len(cache.free_pages())
         for r in self.running:
-            need = cache.pages_needed(r.slot, r.total_len - r.cached_len)
+            need = cache.pages_to_hold(r.slot, r.total_len - r.cached_len, self._step_tokens())
             total = [a + b for a, b in zip(total, need)]
         return total
+
+    def _step_tokens(self) -> int:
+        """The most tokens one request brings in one step (what a windowed cache group is sized by)."""
+        return min(self.max_batch_tokens, self.chunk) if self.chunk > 0 else self.max_batch_tokens
 
     def _admit_phase(self) -> None:
         cache = self.runner.cache
@@ -174,7 +179,7 @@ class Scheduler:
             slot = self.runner.admit()
             if slot is None:
                 return
-            need = cache.pages_needed(slot, r.total_len)
+            need = cache.pages_to_hold(slot, r.total_len, self._step_tokens())
             free = cache.free_pages()
             claimed = self._claimed()
             fits = all(n + 1 + c <= f for n, c, f in zip(need, claimed, free))

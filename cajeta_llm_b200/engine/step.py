@@ -79,6 +79,8 @@ class StepContext:
     max_context: int = 0           # longest prior + new over the step's requests
     all_single: bool = False       # every request brings exactly one token
     decode_scratch: Optional[object] = None    # scratch of the split-KV decode attention for this step (None: the runtime's)
+    routing_pin: Optional[Dict[str, torch.Tensor]] = None     # a routed feed-forward's prefix -> int32 [rows, k]: experts given, not chosen
+    routing_dump: Optional[Dict[str, tuple]] = None           # filled by routed feed-forwards: prefix -> (experts [rows, k], margins [rows])
 
 
 @dataclass
@@ -118,11 +120,22 @@ class ModelRunner:
     """
 
     def __init__(self, model: Model, page_tokens: int = 16, max_seqs: int = 4, max_tokens_per_seq: int = 4096,
-                 num_pages: Optional[int] = None, cuda_graphs: bool = True):
+                 num_pages: Optional[int] = None, cuda_graphs: bool = True, max_step_tokens: int = 0):
+        """``num_pages``: the pool size of every cache group; None sizes each group by its own
+        need: ``max_seqs`` requests of ``max_tokens_per_seq`` tokens for a group that keeps every
+        key, and for a windowed group ``max_seqs`` times what a window plus one step's tokens of a
+        request span (``max_step_tokens``, the most tokens a request brings in one step; 0 = up to
+        a whole request, which sizes the windowed group like the others)."""
         self.model = model
         self.runtime = model.runtime
         if num_pages is None:
-            num_pages = max_seqs * (-(-max_tokens_per_seq // page_tokens))
+            whole = -(-max_tokens_per_seq // page_tokens)
+
+            def num_pages(spec):
+                if spec.window > 0 and max_step_tokens > 0:
+                    return max_seqs * min(whole, -(-(spec.window + max_step_tokens) // page_tokens) + 1)
+                return max_seqs * whole
+        self.max_step_tokens = max_step_tokens
         self.cache = CacheManager(model.kv_needs(), model.state_needs(), model.cache_from(), page_tokens, max_seqs,
                                   max_tokens_per_seq, num_pages, self.runtime.cache_dtype, self.runtime.device)
         self.page_tokens = page_tokens
@@ -150,19 +163,31 @@ class ModelRunner:
         self.cache.release(slot)
 
     # -- the step --------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], routing_pin: Optional[Dict[str, torch.Tensor]] = None,
+             routing_dump: Optional[Dict[str, tuple]] = None) -> torch.Tensor:
         """Run one batch; returns float32 logits ``[wanted, vocab]`` in the order of the
         entries and of each entry's ``want``.  Raises :class:`OutOfPages` (cache
-        unchanged) when the pages for the new tokens are not there."""
+        unchanged) when the pages for the new tokens are not there.
+
+        ``routing_pin``: for routed feed-forwards, by the part's tensor-name prefix, the experts
+        of every row of this step (int32 ``[rows, k]`` on the device, rows in the step's order):
+        they are taken as given instead of chosen - the way to replay recorded selections, as
+        the reference does (model/MoeFfn.cajeta:626-706).  ``routing_dump``: a dict that receives,
+        by prefix, the experts each row picked and its routing margin (p_k - p_{k+1}) / p_k
+        (margins are None under a pin).  A step with either is launched kernel by kernel."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.runtime.device)
         self._calls = getattr(self, "_calls", 0) + 1
         if self._calls % WAIT_CHECK_EVERY == 0:
             self.check_waits()
-        if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and not self.cache.state:
+        if routing_pin is not None or routing_dump is not None:
+            ctx = self._prepare(entries)
+            ctx.routing_pin, ctx.routing_dump = routing_pin, routing_dump
+            logits = self._forward(ctx)
+        elif self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and not self.cache.state:
             return self._step_captured(entries)
-        if self.cuda_graphs and not self.cache.state:
+        elif self.cuda_graphs and not self.cache.state:
             logits = self._step_mixed(entries)
         else:
             logits = self._forward(self._prepare(entries))

@@ -13,6 +13,8 @@ Categories and what each must offer
 ``mixer``         ``cache_need()``, ``state_need()``, ``forward(x, residual, ctx, entry) -> None | pending``
 ``feed_forward``  ``needs_f32_input``, ``forward(x, x_f32, residual, ctx)``
 ``block``         ``forward(hs, ctx, entry)`` over its mixer, feed-forward and norms
+``embedding``     ``forward(token_ids) -> float32 [T, hidden]``, ``table``
+``head``          ``forward(x [rows, hidden]) -> float32 [rows, vocab]``
 
 ``x`` is the normed input in the activation dtype, ``residual`` the float32 residual
 stream the part adds its result into (the residual sum is always 32-bit; a mixer may
@@ -52,6 +54,16 @@ class Runtime:
         self.device = torch.device(device)
         self.fast_kernels = fast_kernels and dtype == "bfloat16"
         self._decode_scratch = None
+        self._sm_count = None
+
+    @property
+    def sm_count(self) -> int:
+        """Streaming multiprocessors of the device (148 on a B200), asked of the device once;
+        tile and split choices that aim at filling the machine use this, never a constant."""
+        if self._sm_count is None:
+            self._sm_count = (torch.cuda.get_device_properties(self.device).multi_processor_count
+                              if self.device.type == "cuda" else 1)
+        return self._sm_count
 
     @property
     def decode_scratch(self):
@@ -135,7 +147,7 @@ class Part:
 
 
 _REGISTRY: Dict[Tuple[str, str], Type[Part]] = {}
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
 
 
 def register_part(category: str, kind: str, cls: Optional[Type[Part]] = None, replace: bool = False):

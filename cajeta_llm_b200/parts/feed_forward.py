@@ -190,7 +190,7 @@ class SparseMoE(Part):
     def wants_split_input(self, rows: int) -> bool:
         return self.router_split is not None and rows >= self.SPLIT_ROUTER_MIN_ROWS
 
-    def _route(self, x_exact: torch.Tensor, sel, wts, shared_scale) -> None:
+    def _route(self, x_exact: torch.Tensor, sel, wts, shared_scale, pin=None, gap=None) -> None:
         k = self.top_k
         if x_exact.dtype == torch.bfloat16:
             # the three-term form: one tensor-core product, cut along K so that the machine is
@@ -199,13 +199,14 @@ class SparseMoE(Part):
             cols, Kd = self.router_split.shape
             k_blocks = Kd // 64
             tiles = -(-T // 128) * -(-cols // 128)
-            splits = max(1, min(8, k_blocks // 8, -(-148 // tiles)))
+            rt_sms = self.runtime.sm_count
+            splits = max(1, min(8, k_blocks // 8, -(-rt_sms // tiles)))
             logits = torch.empty((splits, T, cols), dtype=torch.float32, device=x_exact.device)
             K.gemm_tc(x_exact, self.router_split, logits if splits > 1 else logits[0], K.EPI_STORE_F32, False, 128,
                       k_splits=splits)
-            K.router_select(logits, self.num_experts, k, self.norm_topk, sel, wts, shared_scale)
+            K.router_select(logits, self.num_experts, k, self.norm_topk, sel, wts, shared_scale, pin=pin, gap=gap)
         else:
-            K.router_topk(x_exact, self.router, self.shared_gate_w, k, self.norm_topk, sel, wts, shared_scale)
+            K.router_topk(x_exact, self.router, self.shared_gate_w, k, self.norm_topk, sel, wts, shared_scale, pin=pin, gap=gap)
 
     def forward(self, x: torch.Tensor, x_exact: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         rt = self.runtime
@@ -215,7 +216,15 @@ class SparseMoE(Part):
         sel = torch.empty((T, k), dtype=torch.int32, device=dev)
         wts = torch.empty((T, k), dtype=torch.float32, device=dev)
         shared_scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.shared_gate else None
-        self._route(x_exact, sel, wts, shared_scale)
+        # a step may bring the experts of its rows with it (``ctx.routing_pin``: this part's tensor-name
+        # prefix -> int32 [rows, k]; the weights stay the rows' own probabilities), or ask for what was
+        # picked and how narrowly (``ctx.routing_dump``: prefix -> (experts, margins))
+        pins, dump = getattr(ctx, "routing_pin", None), getattr(ctx, "routing_dump", None)
+        pin = pins.get(self.prefix) if pins else None
+        gap = torch.empty((T,), dtype=torch.float32, device=dev) if dump is not None and pin is None else None
+        self._route(x_exact, sel, wts, shared_scale, pin, gap)
+        if dump is not None:
+            dump[self.prefix] = (sel, gap)
 
         shared_dense = self.ws_down is not None and self.shared_chunks > 0 and T >= self.SHARED_DENSE_MIN_ROWS
         C = 0 if shared_dense else self.shared_chunks

@@ -54,7 +54,7 @@ PAIR_MIN_ROWS = 512          # dense products with at least this many rows run o
 PAIR_MIN_GROUP_ROWS = 96     # grouped products whose groups average at least this many rows do
 
 
-def _pair_tile(rows: int, w: torch.Tensor, swiglu: bool, grouped: bool) -> int:
+def _pair_tile(runtime, rows: int, w: torch.Tensor, swiglu: bool, grouped: bool) -> int:
     """Token tile (128 or 256) of the two-SM product when the shape calls for it, else 0."""
     features = w.shape[-2]
     if features < 256:
@@ -72,7 +72,8 @@ def _pair_tile(rows: int, w: torch.Tensor, swiglu: bool, grouped: bool) -> int:
     if rows < PAIR_MIN_ROWS:
         return 0
     feature_tiles = -(-features // 256)
-    return 256 if feature_tiles * -(-rows // 256) >= 74 else 128
+    # the wider tile only when its tiles still give every pair of SMs one
+    return 256 if feature_tiles * -(-rows // 256) >= runtime.sm_count // 2 else 128
 
 
 def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
@@ -111,7 +112,7 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
         # (the SwiGLU form keeps two accumulators per stage: beyond 128 tokens tensor memory
         # holds one stage only and the epilogue no longer overlaps the next tile)
         tile = min(128, _group_tile(rows, w.shape[0])) if w_up is not None else _group_tile(rows, w.shape[0])
-    pair_tile = 0 if tile and group_offsets is None else _pair_tile(rows, w, w_up is not None, group_offsets is not None)
+    pair_tile = 0 if tile and group_offsets is None else _pair_tile(runtime, rows, w, w_up is not None, group_offsets is not None)
     if pair_tile:
         # many rows: tiles of 256 features on pairs of SMs, each loading half of the token rows
         K.gemm_tc2(x, w, out, epi, pair_tile, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows)
@@ -138,7 +139,9 @@ def project_split(runtime, x: torch.Tensor, w: torch.Tensor, bias: Optional[torc
     features, Kd = w.shape[-2], w.shape[-1]
     feature_tiles = -(-features // 128) * -(-rows // tile)
     k_blocks = -(-Kd // 64)
-    splits = min(8, max(1, 128 // feature_tiles), max(1, k_blocks // 4))
+    # as many pieces as it takes to give (nearly) every SM a block; 7/8 of them, so that a
+    # product of 16 tiles is cut into 8 pieces of equal length rather than 9 ragged ones
+    splits = min(8, max(1, (runtime.sm_count * 7 // 8) // feature_tiles), max(1, k_blocks // 4))
     if splits < 2:
         return None
     parts = torch.empty((splits, rows, features), dtype=torch.float32, device=x.device)

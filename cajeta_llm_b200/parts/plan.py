@@ -102,6 +102,8 @@ class ModelPlan:
     lm_head_name: Optional[str]          # None: tied to the embedding table
     eog_token_ids: Tuple[int, ...] = ()
     max_position: Optional[int] = None
+    embedding: PartSpec = PartSpec("token_embedding")     # how token ids become rows of the residual stream
+    head: PartSpec = PartSpec("linear_head")              # how the normed wanted rows become logits
 
     def validate(self) -> None:
         for i, e in enumerate(self.schedule):

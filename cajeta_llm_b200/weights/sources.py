@@ -7,14 +7,13 @@ source holds and raises ONE error that lists every missing tensor, every unexpec
 tensor and every wrong shape (the reference names one tensor at a time:
 io/Checkpoint.cajeta:495-499, model/Linear.cajeta:1857-1867, model/RMSNorm.cajeta:45-48).
 
-The random-weights mode draws N(0, std) for matrices, biases and router rows, ones
-for norm weights (the reference has such weights only as test fixtures,
-selftest/ToyModel.cajeta:116-120); a tensor's values depend on (seed, tensor name)
-only, so the order of generation does not matter.
+The random-weights mode draws bell-shaped values of mean 0 and a given standard deviation
+for matrices, biases and router rows, ones for norm weights (the reference has such weights
+only as test fixtures, selftest/ToyModel.cajeta:116-120); a value depends on (seed, tensor
+name, element index) only, so neither the order of generation nor the device matters.
 """
 from __future__ import annotations
 
-import hashlib
 import json
 import os
 from typing import Dict, Mapping, Tuple
@@ -22,6 +21,7 @@ from typing import Dict, Mapping, Tuple
 import torch
 
 from ..parts.plan import ParamSpec
+from . import random_fill
 from .safetensors_io import Checkpoint, write_safetensors
 
 
@@ -67,18 +67,15 @@ class SafetensorsWeights:
         self.checkpoint.close()
 
 
-def _tensor_seed(seed: int, name: str) -> int:
-    h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
-    return int.from_bytes(h[:8], "little") & 0x7FFFFFFFFFFFFFFF
-
-
 class RandomWeights:
     """Seeded random tensors by name.
 
-    ``device`` chooses where the values are drawn: the CPU generator when a model
-    folder is written (the file is then the truth for every reader), or the CUDA
-    generator to fill a large model in place without a file.  ``store_dtype`` is the
-    dtype a file of these weights would store (values are rounded to it).
+    A value depends on (seed, tensor name, element index) only
+    (:mod:`cajeta_llm_b200.weights.random_fill`): ``device`` chooses where the values are
+    computed - on the host when a model folder is written, by a kernel to fill a large model
+    in place without a file - and both give the same bits, so that whoever knows the seed can
+    rebuild any tensor of a model drawn on the device.  ``store_dtype`` is the dtype a file of
+    these weights would store (values are rounded to it, to nearest even).
     """
 
     def __init__(self, seed: int, store_dtype: torch.dtype = torch.bfloat16, device: str = "cpu"):
@@ -99,10 +96,17 @@ class RandomWeights:
         elif spec.init == "zeros":
             t = torch.zeros(spec.shape, dtype=torch.float32, device=self.device)
         elif spec.init == "normal":
-            g = torch.Generator(device=self.device)
-            g.manual_seed(_tensor_seed(self.seed, name))
-            t = torch.empty(spec.shape, dtype=torch.float32, device=self.device)
-            t.normal_(0.0, spec.std, generator=g)
+            key = random_fill.tensor_key(self.seed, name)
+            count = 1
+            for n in spec.shape:
+                count *= int(n)
+            if self.device.type == "cuda":
+                from ..csrc import kernels as K
+                t = torch.empty(spec.shape, dtype=self.store_dtype, device=self.device)
+                with torch.cuda.device(self.device):
+                    K.random_fill(t, key, float(random_fill.scale_for(spec.std)))
+                return t
+            t = torch.from_numpy(random_fill.fill(count, key, spec.std)).reshape(spec.shape)
         else:
             raise WeightError(f"tensor '{name}': unknown init '{spec.init}'")
         return t.to(self.store_dtype)

@@ -180,10 +180,12 @@ def routing_margin(logits: torch.Tensor, top_k: int) -> float:
 
 
 def sparse_moe(x: torch.Tensor, weights: Dict[str, torch.Tensor], prefix: str, num_experts: int, top_k: int,
-               norm_topk: bool, has_shared: bool, margins: Optional[List[float]] = None) -> torch.Tensor:
+               norm_topk: bool, has_shared: bool, margins: Optional[List[float]] = None,
+               picked: Optional[List[List[int]]] = None) -> torch.Tensor:
     """Per row: router, selected experts accumulated in selection order, then the
     sigmoid-gated shared expert (model/MoeFfn.cajeta:1849-1916 and :1925-1964).
-    ``margins`` (one entry per row, updated in place) keeps the smallest routing margin."""
+    ``margins`` (one entry per row, updated in place) keeps the smallest routing margin;
+    ``picked`` (a list) receives each row's experts in selection order."""
     out = torch.zeros_like(x)
     router_w = weights[f"{prefix}.gate.weight"]
     for t in range(x.shape[0]):
@@ -192,6 +194,8 @@ def sparse_moe(x: torch.Tensor, weights: Dict[str, torch.Tensor], prefix: str, n
         if margins is not None:
             margins[t] = min(margins[t], routing_margin(logits, top_k))
         sel, wt = route(logits, top_k, norm_topk)
+        if picked is not None:
+            picked.append(list(sel))
         acc = torch.zeros_like(row)
         for j, e in enumerate(sel):
             y = swiglu_mlp(row, weights[f"{prefix}.experts.{e}.gate_proj.weight"],
@@ -227,10 +231,12 @@ def layer_window(config: dict, layer: int) -> int:
 # the whole model
 # ----------------------------------------------------------------------------------
 def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int],
-            dtype: torch.dtype = torch.float64, margins: Optional[List[float]] = None) -> torch.Tensor:
+            dtype: torch.dtype = torch.float64, margins: Optional[List[float]] = None,
+            selections: Optional[Dict[int, List[List[int]]]] = None) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence (model/CausalLM.cajeta:1424-1608 per
     layer, :1712-1718 for the head).  ``margins``: a list of T ones that receives each
-    row's smallest routing margin over the layers."""
+    row's smallest routing margin over the layers.  ``selections``: a dict that receives,
+    per sparse layer, each row's picked experts."""
     W = {k: v.to(dtype) for k, v in weights.items()}
     heads = config["num_attention_heads"]
     kv_heads = config.get("num_key_value_heads", heads)
@@ -252,9 +258,12 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int
         hs = hs + linear(ao, W[f"{p}.self_attn.o_proj.weight"])
         xn = rmsnorm(hs, W[f"{p}.post_attention_layernorm.weight"], eps)
         if layer_is_sparse(config, l):
+            picked = [] if selections is not None else None
             ff = sparse_moe(xn, W, f"{p}.mlp", config["num_experts"], config["num_experts_per_tok"],
                             config.get("norm_topk_prob", False),
-                            config.get("shared_expert_intermediate_size", 0) > 0, margins)
+                            config.get("shared_expert_intermediate_size", 0) > 0, margins, picked)
+            if selections is not None:
+                selections[l] = picked
         else:
             ff = swiglu_mlp(xn, W[f"{p}.mlp.gate_proj.weight"], W[f"{p}.mlp.up_proj.weight"],
                             W[f"{p}.mlp.down_proj.weight"])

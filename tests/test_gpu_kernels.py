@@ -39,6 +39,8 @@ def test_embed_gather(K, dtype):
     out = torch.empty(5, 72, device=DEV)
     K.embed_gather(out, table, ids)
     assert torch.equal(out, table[ids.long()].float())
+    K.embed_gather(out, table, ids, 1.75)                      # an embedding scale (0 = none)
+    assert torch.equal(out, table[ids.long()].float() * 1.75)
 
 
 # four elements a load: 72, 1000, 2048, 3584 (two loads a thread), 5000 (four); one at a time: 1002, 10000
@@ -544,3 +546,23 @@ def test_prefill_attention_tiles(K, heads, n_kv, hd, page, window, block_rows):
         want = P.attention(qq, ks[r].to(dtype).double(), vs[r].to(dtype).double(), window, scale)[T - n:]
         got = out[starts[r]:starts[r + 1]].double().cpu()
         assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), (r, float((got - want).abs().max()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_random_fill_on_the_device_equals_the_host_generator(K, dtype):
+    """A tensor drawn by the kernel holds the same bits as the same tensor drawn by the numpy
+    generator (more elements than one pass of the grid covers, a count that is no multiple of
+    anything), and a few of them are held to the restatement with Python integers."""
+    import plain_random as PR
+    from cajeta_llm_b200.parts.plan import ParamSpec
+    from cajeta_llm_b200.weights.sources import RandomWeights
+    name, seed = "model.layers.0.self_attn.q_proj.weight", 31
+    spec = ParamSpec((1531, 1013), std=0.02)
+    on_host = RandomWeights(seed, dtype, device="cpu").get(name, spec)
+    on_device = RandomWeights(seed, dtype, device=DEV).get(name, spec)
+    assert on_device.is_cuda and on_device.dtype == dtype
+    assert torch.equal(on_device.cpu(), on_host)
+    flat = on_device.flatten().cpu().float()
+    for i in (0, 1, 1012, 1013, 1_550_902):
+        want = PR.value(seed, name, i, 0.02)
+        assert float(flat[i]) == (PR.to_bfloat16(want) if dtype == torch.bfloat16 else want), i

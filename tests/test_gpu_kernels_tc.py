@@ -249,3 +249,30 @@ def test_pair_product_refuses(K):
         K.gemm_tc2(x, w, torch.empty(64, 200, device=DEV), K.EPI_STORE_F32, 64)          # token tiles of 128 or 256
     with pytest.raises(K.KernelError):
         K.gemm_tc2(x, w, out, K.EPI_STORE_F32, 128)                                     # float32 epilogue, bf16 out
+
+
+@pytest.mark.parametrize("rows", [1, 8, 64, 200])
+def test_language_model_head_at_the_real_vocabulary(K, rows):
+    """The head's product at 151,936 features x 2,048 (1,187 feature tiles; an output row of
+    151,936 floats) through the engine's own dispatch, every logit against a float64 product
+    of the same bfloat16 operands.  A slip in the tile table or in the output index at this
+    width would show as a wrong or an unwritten stretch of the row."""
+    from cajeta_llm_b200.parts.base import Runtime
+    from cajeta_llm_b200.parts.linear import project
+    V, H = 151_936, 2048
+    from cajeta_llm_b200.parts.plan import ParamSpec
+    from cajeta_llm_b200.weights.sources import RandomWeights
+    w = RandomWeights(5, torch.bfloat16, device=DEV).get("lm_head.weight", ParamSpec((V, H), std=0.02))
+    x = rnd(rows, H, seed=500 + rows)
+    out = torch.full((rows, V), float("nan"), device=DEV)
+    project(Runtime("bfloat16", device=DEV), x, w, out)
+    xd = x.double()
+    worst = 0.0
+    for lo in range(0, V, 16384):
+        want = xd @ w[lo:lo + 16384].double().t()
+        got = out[:, lo:lo + 16384].double()
+        assert bool(torch.isfinite(got).all()), f"unwritten logits in columns {lo}.."
+        d = (got - want).abs()
+        assert bool((d <= 2e-3 + 2e-3 * want.abs()).all()), (lo, float(d.max()))
+        worst = max(worst, float(d.max()))
+    print(f"\nhead {rows} rows: worst |diff| {worst:.3e}")

@@ -56,6 +56,35 @@ def test_position_parts():
         make_part("position", PartSpec("alibi", {}), "", runtime("float32"))
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tied,bias,scale", [(True, False, 0.0), (False, True, 12.0), (False, False, 0.0)])
+def test_embedding_and_head_parts(dtype, tied, bias, scale):
+    """The two ends of a model as parts: a scaled embedding, a head with and without bias,
+    tied to the embedding table or with a matrix of its own (hidden 192: the tensor-core
+    product on the bfloat16 path)."""
+    from cajeta_llm_b200.parts.plan import PartSpec
+    V, H = 333, 192
+    emb, w = make("embedding", PartSpec("token_embedding", {"scale": scale}), "", dtype, 3, vocab_size=V, hidden_size=H,
+                  weight_name="e.weight")
+    ids = torch.tensor([5, 332, 0, 5, 17], dtype=torch.int32, device=DEV)
+    hs = emb.forward(ids)
+    assert hs.dtype == torch.float32
+    assert torch.allclose(hs.double().cpu(), w["e.weight"][ids.long().cpu()] * (scale or 1.0), atol=1e-6, rtol=1e-6)
+    if bias and tied:
+        return
+    head, wh = make("head", PartSpec("linear_head", {"bias": bias}), "", dtype, 4, vocab_size=V, hidden_size=H,
+                    weight_name=None if tied else "h.weight", embedding=emb)
+    assert set(wh) == (set() if tied else {"h.weight"} | ({"h.bias"} if bias else set()))
+    x = (torch.randn(7, H, generator=torch.Generator().manual_seed(5)) * 0.5).to(head.runtime.act_dtype).to(DEV)
+    got = head.forward(x)
+    assert got.dtype == torch.float32 and tuple(got.shape) == (7, V)
+    want = P.linear(x.double().cpu(), w["e.weight"] if tied else wh["h.weight"], wh.get("h.bias"))
+    assert torch.allclose(got.double().cpu(), want, **tol(dtype))
+    with pytest.raises(ValueError, match="tied"):
+        make("head", PartSpec("linear_head", {"bias": True}), "", dtype, 4, vocab_size=V, hidden_size=H, weight_name=None,
+             embedding=emb)
+
+
 def step_context(requests, page, n_pages, device=DEV):
     """requests: [(prior_len, n_new)] -> a context like the step function builds, with a
     scrambled block table."""

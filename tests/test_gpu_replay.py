@@ -6,6 +6,7 @@ four live requests, portions of some beside single tokens of others, in a pool s
 that pages are used again.  Every wanted position of every mode is compared with the
 plain implementation, in float32 and in bfloat16.
 """
+import json
 import random
 
 import numpy as np
@@ -26,24 +27,27 @@ class TraceBuilder:
 
     def __init__(self):
         self.steps = []
-        self.rows = {}          # step -> [(rid, position)]
+        self.rows = {}          # step -> [(rid, position)] of the wanted rows
+        self.all_rows = {}      # step -> [(rid, position)] of every row the step runs
         self.progress = {}      # rid -> tokens fed so far
         self.peak = 0
 
     def step(self, parts, end=()):
         """parts: [(rid, tokens, want_indices)]"""
         n = len(self.steps)
-        entries, rows = [], []
+        entries, rows, every = [], [], []
         for rid, toks, want in parts:
             base = self.progress.get(rid, 0)
             entries.append({"id": rid, "tokens": list(toks), "want": list(want)})
             rows += [(rid, base + w) for w in want]
+            every += [(rid, base + i) for i in range(len(toks))]
             self.progress[rid] = base + len(toks)
         self.peak = max(self.peak, sum(round64(v) for v in self.progress.values()))
         for rid in end:
             del self.progress[rid]
         self.steps.append({"step": n, "entries": entries, "end": list(end)})
         self.rows[n] = rows
+        self.all_rows[n] = every
 
 
 def add_whole(tb, rid, toks):
@@ -144,20 +148,72 @@ def test_replay_every_way_of_cutting_matches_the_plain_implementation(name, dtyp
         tb, toks = build_trace(vocab, seed=5 + ord(name))
         assert tb.peak <= 4 * 64 + 64
     # the pool holds exactly the peak: the mixed part frees and reuses pages all the time
-    out = helpers.run_trace(model_dirs[name], dtype, tb.steps, str(tmp_path), max_tokens=tb.peak)
+    model_dir = model_dirs[name]
+    # (the 32-bit run also records its routing; the bfloat16 run does not, so that its steps are
+    # replayed from CUDA graphs wherever serving would replay them)
+    out = helpers.run_trace(model_dir, dtype, tb.steps, str(tmp_path), max_tokens=tb.peak,
+                            extra=["--dump-routing"] if dtype == "float32" else [])
     worst = 0.0
     for s in tb.steps:
         rows = tb.rows[s["step"]]
         if not rows:
             continue
         got = torch.from_numpy(out[s["step"]].copy())
-        want = torch.stack([helpers.plain_logits(model_dirs[name], toks[rid])[pos] for rid, pos in rows])
-        margins = torch.stack([helpers.plain_margins(model_dirs[name], toks[rid])[pos] for rid, pos in rows])
-        helpers.assert_close(got, want, dtype, f"{name} {dtype} step {s['step']} rows {rows[:4]}...", margins)
+        want = torch.stack([helpers.plain_logits(model_dir, toks[rid])[pos] for rid, pos in rows])
+        margins = torch.stack([helpers.plain_margins(model_dir, toks[rid])[pos] for rid, pos in rows])
+        # a bfloat16 row at a routing near-tie may fall the other way here; the pinned replay below holds it
+        helpers.assert_close(got, want, dtype, f"{name} {dtype} step {s['step']} rows {rows[:4]}...", margins, pinned_elsewhere=True)
         worst = max(worst, float((got - want).abs().max()))
     tied = helpers.near_tie_rows
     print(f"\n{name} {dtype}: {len(tb.steps)} steps, worst |diff| {worst:.3e}; rows excused as routing near-ties so far {tied['seen']} of {tied['rows']}")
     assert tied["seen"] <= 0.02 * max(1, tied["rows"])         # the allowance stays the exception
+
+    layers = sorted(helpers.plain_selections(model_dir, toks["w0"]))
+    if dtype == "float32":
+        # what the engine says it picked: the plain implementation's experts (a row within 1e-4 of a
+        # tie may fall the other way) and the plain implementation's margins
+        flips = 0
+        for s in tb.steps:
+            with open(tmp_path / f"{s['step']}.routing.json") as f:
+                dumped = json.load(f)["layers"]
+            assert sorted(dumped) == sorted(f"model.layers.{l}.mlp" for l in layers)
+            every = tb.all_rows[s["step"]]
+            smallest = torch.ones(len(every))
+            for l in layers:
+                rec = dumped[f"model.layers.{l}.mlp"]
+                smallest = torch.minimum(smallest, torch.tensor(rec["margin"]))
+                for i, (rid, pos) in enumerate(every):
+                    if rec["experts"][i] != helpers.plain_selections(model_dir, toks[rid])[l][pos]:
+                        assert float(helpers.plain_margins(model_dir, toks[rid])[pos]) < 1e-4, (s["step"], l, rid, pos)
+                        flips += 1
+            want_margin = torch.stack([helpers.plain_margins(model_dir, toks[rid])[pos] for rid, pos in every])
+            assert torch.allclose(smallest, want_margin.float(), atol=1e-4), s["step"]
+        print(f"{name} {dtype}: rows routed otherwise than in the plain implementation: {flips}")
+
+    if dtype == "bfloat16":
+        # the same trace with every row's experts given (the plain implementation's): nothing is
+        # discontinuous any more, and every logit of every wanted row must meet the bound
+        pins = tmp_path / "pins"
+        pins.mkdir()
+        for s in tb.steps:
+            every = tb.all_rows[s["step"]]
+            rec = {"layers": {f"model.layers.{l}.mlp": {"experts": [helpers.plain_selections(model_dir, toks[rid])[l][pos]
+                                                                     for rid, pos in every]} for l in layers}}
+            with open(pins / f"{s['step']}.routing.json", "w") as f:
+                json.dump(rec, f)
+        pinned_out = tmp_path / "pinned"
+        out = helpers.run_trace(model_dir, dtype, tb.steps, str(pinned_out), max_tokens=tb.peak,
+                                extra=["--pin-routing", str(pins), "--dump-routing"])
+        for s in tb.steps:
+            rows = tb.rows[s["step"]]
+            if not rows:
+                continue
+            got = torch.from_numpy(out[s["step"]].copy())
+            want = torch.stack([helpers.plain_logits(model_dir, toks[rid])[pos] for rid, pos in rows])
+            helpers.assert_close(got, want, dtype, f"{name} {dtype} pinned step {s['step']} rows {rows[:4]}...")
+        with open(pinned_out / f"{tb.steps[-1]['step']}.routing.json") as f, open(pins / f"{tb.steps[-1]['step']}.routing.json") as g:
+            ran, given = json.load(f)["layers"], json.load(g)["layers"]
+        assert all(ran[k]["experts"] == given[k]["experts"] and ran[k]["margin"] is None for k in given)
 
 
 def test_replay_writes_nothing_when_nothing_is_wanted_and_reuses_ids(model_dirs, tmp_path):

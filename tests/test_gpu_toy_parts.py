@@ -1,8 +1,9 @@
 """Generality of the parts, continued: a toy feed-forward with routing of its own, a toy
-position encoding (half of each head rotated, stretched frequencies) and a toy norm, all
-defined here, registered, and run inside the framework's own attention mixer, block, cache,
-step function and loader without a change to the package.  Layers differ: one has the toy
-feed-forward, the other the framework's dense one."""
+position encoding (half of each head rotated, stretched frequencies), a toy norm, a toy
+embedding (scaled) and a toy head (bias and a soft cap), all defined here, registered, and run
+inside the framework's own attention mixer, block, cache, step function and loader without a
+change to the package.  Layers differ: one has the toy feed-forward, the other the
+framework's dense one."""
 from dataclasses import dataclass
 
 import numpy as np
@@ -15,6 +16,7 @@ import plain_qwen2moe as P
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 HEADS, KV, HD, ROT, STRETCH, THETA = 3, 1, 32, 16, 4.0, 500.0
+EMBED_SCALE, LOGIT_CAP = 1.75, 0.5
 
 
 def define_toys():
@@ -84,6 +86,44 @@ def define_toys():
             y = (rows - rows.mean(dim=1, keepdim=True)) * self.weight
             return y.to(out_dtype or self.runtime.act_dtype), (y if want_f32 else None)
 
+    class ScaledEmbedding(Part):
+        """hs = table[token] * scale: only the interface of an embedding, nothing of the package's."""
+
+        def __init__(self, spec, prefix, runtime, vocab_size, hidden_size, weight_name):
+            super().__init__(spec, prefix, runtime)
+            self.shape, self.weight_name, self.scale = (vocab_size, hidden_size), weight_name, float(spec["scale"])
+            self.table = None
+
+        def params(self):
+            return {self.weight_name: ParamSpec(self.shape)}
+
+        def load(self, source):
+            self.table = self.fetch(source, self.weight_name)
+
+        def forward(self, token_ids):
+            return self.table[token_ids.long()].float() * self.scale
+
+    class CappedHead(Part):
+        """logits = cap * tanh((x W^T + b) / cap)."""
+
+        def __init__(self, spec, prefix, runtime, vocab_size, hidden_size, weight_name, embedding):
+            super().__init__(spec, prefix, runtime)
+            self.shape, self.weight_name, self.cap = (vocab_size, hidden_size), weight_name, float(spec["cap"])
+            self.weight = self.bias = None
+
+        def params(self):
+            return {self.weight_name: ParamSpec(self.shape),
+                    self.weight_name.replace("weight", "bias"): ParamSpec(self.shape[:1], role="vector")}
+
+        def load(self, source):
+            self.weight = self.fetch(source, self.weight_name)
+            self.bias = self.fetch(source, self.weight_name.replace("weight", "bias"))
+
+        def forward(self, x):
+            return self.cap * torch.tanh((x.float() @ self.weight.float().t() + self.bias) / self.cap)
+
+    register_part("embedding", "toy_scaled", ScaledEmbedding, replace=True)
+    register_part("head", "toy_capped", CappedHead, replace=True)
     register_part("position", "toy_stretched_half", StretchedHalfRotary, replace=True)
     register_part("feed_forward", "toy_pick_one", PickOneFeedForward, replace=True)
     register_part("norm", "toy_mean", MeanNorm, replace=True)
@@ -119,7 +159,8 @@ def define_toys():
         )
         return ModelPlan(architecture=cfg.architecture, hidden_size=h, vocab_size=cfg.vocab_size,
                          embedding_name="t.embed.weight", layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1)),
-                         final_norm=rms, final_norm_prefix="t.norm", lm_head_name="t.head.weight")
+                         final_norm=rms, final_norm_prefix="t.norm", lm_head_name="t.head.weight",
+                         embedding=PartSpec("toy_scaled", {"scale": EMBED_SCALE}), head=PartSpec("toy_capped", {"cap": LOGIT_CAP}))
 
     register_architecture("ToyPickOneForCausalLM", ToyConfig, build_plan, replace=True)
     return ToyConfig
@@ -129,7 +170,7 @@ def plain(weights, tokens, n_maps):
     """The toy model over one whole sequence in float64, from the formulas in the docstrings above."""
     W = {k: v.double() for k, v in weights.items()}
     T = len(tokens)
-    hs = W["t.embed.weight"][torch.tensor(tokens)]
+    hs = W["t.embed.weight"][torch.tensor(tokens)] * EMBED_SCALE
     inv = torch.tensor((np.power(np.float32(THETA), -2.0 * np.arange(ROT // 2, dtype=np.float32) / np.float32(ROT))
                         .astype(np.float32) / np.float32(STRETCH)).astype(np.float32)).double()
 
@@ -158,7 +199,8 @@ def plain(weights, tokens, n_maps):
         else:
             hs = hs + P.swiglu_mlp(P.rmsnorm(hs, W[f"{p}.n2.weight"], 1e-5), W[f"{p}.ff.gate_proj.weight"],
                                    W[f"{p}.ff.up_proj.weight"], W[f"{p}.ff.down_proj.weight"])
-    return P.linear(P.rmsnorm(hs, W["t.norm.weight"], 1e-5), W["t.head.weight"]).float()
+    y = P.linear(P.rmsnorm(hs, W["t.norm.weight"], 1e-5), W["t.head.weight"], W["t.head.bias"])
+    return (LOGIT_CAP * torch.tanh(y / LOGIT_CAP)).float()
 
 
 def test_toy_feed_forward_position_and_norm_run_in_the_framework(tmp_path):
@@ -171,6 +213,7 @@ def test_toy_feed_forward_position_and_norm_run_in_the_framework(tmp_path):
     cfg = ToyConfig(architecture="ToyPickOneForCausalLM", hidden_size=56, vocab_size=77, n_maps=3)
     schema = build_model(cfg, Runtime("float32", device="cpu")).params()
     assert "t.0.ff.maps.2.weight" in schema and "t.1.ff.gate_proj.weight" in schema and "t.0.n2.weight" in schema
+    assert tuple(schema["t.head.bias"].shape) == (77,) and tuple(schema["t.embed.weight"].shape) == (77, 56)
     write_model_folder(str(tmp_path), cfg, schema, seed=9, store_dtype=torch.float32)
     model, _ = load_model(str(tmp_path), Runtime("float32", device=DEV))
     runner = ModelRunner(model, page_tokens=4, max_seqs=2, max_tokens_per_seq=40, num_pages=16)

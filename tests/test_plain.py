@@ -134,3 +134,27 @@ def test_plain_sampler_arithmetic():
     for i in order:
         assert P.draw(d, cum + 1e-4) == i
         cum += float(d[i])
+
+
+@pytest.mark.parametrize("name", sorted(helpers.CONFIGS))
+def test_vectorised_restatement_equals_the_row_by_row_implementation(name, tmp_path):
+    """tests/plain_vectorised.py (whole tensors, used against the full-size models) against
+    tests/plain_qwen2moe.py (Python loops) on every small configuration: logits, the experts
+    each row picks in every sparse layer, and the routing margins."""
+    import plain_vectorised as PV
+    raw = helpers.CONFIGS[name]
+    d = str(tmp_path)
+    helpers.write_model(d, raw, seed=helpers.SEEDS[name])
+    config, weights = P.read_model(d)
+    n = 70 if name in helpers.LONG_REQUESTS else 45             # beyond the small windows; W's window is 40
+    tokens = helpers.random_tokens(raw["vocab_size"], n, seed=3)
+    m_rows, m_vec, picked = [1.0] * n, [1.0] * n, {}
+    want = P.forward(config, weights, tokens, margins=m_rows)
+    got = PV.forward(config, weights.__getitem__, tokens, margins=m_vec, selections=picked)
+    assert torch.allclose(got, want, atol=1e-11, rtol=1e-9), float((got - want).abs().max())
+    assert np.allclose(m_rows, m_vec, atol=1e-9)
+    sparse = [l for l in range(config["num_hidden_layers"]) if P.layer_is_sparse(config, l)]
+    assert sorted(picked) == sparse and all(tuple(s.shape) == (n, config["num_experts_per_tok"]) for s in picked.values())
+    # ties go to the lower index here as there
+    sel, w, margin = PV.route(torch.tensor([[1.0, 2.0, 2.0, 0.5, 2.0]], dtype=torch.float64), 2, False)
+    assert sel.tolist() == [[1, 2]] and abs(float(margin[0])) < 1e-12

@@ -14,6 +14,9 @@ class FakeCache:
     def pages_needed(self, slot, n):
         return self.books.pages_needed(slot, n)
 
+    def pages_to_hold(self, slot, n, step_tokens=0):
+        return self.books.pages_to_hold(slot, n, step_tokens)
+
     def free_pages(self):
         return self.books.free_pages()
 
@@ -25,8 +28,10 @@ class FakeRunner:
     """Keeps the books like the real runner and 'computes' a next token from the
     request's whole history, so that any loss of cached tokens would show."""
 
-    def __init__(self, pages, page_tokens=4, max_seqs=4, ctx=256):
-        self.books = CacheBooks([GroupSpec(1, 8, 0)], [pages], page_tokens, max_seqs, ctx)
+    def __init__(self, pages, page_tokens=4, max_seqs=4, ctx=256, groups=None):
+        groups = groups or [GroupSpec(1, 8, 0)]
+        counts = pages if isinstance(pages, (list, tuple)) else [pages] * len(groups)
+        self.books = CacheBooks(groups, list(counts), page_tokens, max_seqs, ctx)
         self.cache = FakeCache(self.books)
         self.history = {}
         self.log = []
@@ -173,3 +178,36 @@ def test_stop_tokens_budget_cancel_and_sink():
     assert s.request(c).finish_reason == FinishReason.CANCEL and s.request(c).generated == want[:1]
     assert [t for rid, t in seen if rid == a] == want[:4]
     assert r.books.free_pages() == [64 ]
+
+
+def test_a_windowed_group_is_sized_by_its_window_not_by_the_request():
+    """Two cache groups: one keeps every key, one a window of 10 tokens.  With steps of at most 6
+    tokens a request never holds more than ceil((10 + 6) / 4) + 1 = 5 pages of the windowed
+    group, so a pool of 2 x 5 + 1 pages serves two requests of 100 tokens, which would need 25
+    pages each in a group that kept everything; admission counts accordingly."""
+    groups = [GroupSpec(1, 8, 0), GroupSpec(1, 8, 10)]
+    r = FakeRunner(pages=[64, 11], page_tokens=4, max_seqs=2, ctx=128, groups=groups)
+    s = Scheduler(r, FakeSampler(), max_batch_tokens=6)
+    prompts = [list(range(5, 95)), list(range(200, 270))]
+    ids = [s.submit(p, SamplingParams(max_new_tokens=10)) for p in prompts]
+    most = 0
+    while s.has_work:
+        s.step_once()
+        for q in s.running:
+            g = r.books.groups[1]
+            most = max(most, int(g.next_page[q.slot]) - int(g.first_live[q.slot]))
+        assert len(s.running) == 2 or not s.waiting              # both run side by side from the start
+    assert 3 <= most <= 5 and s.counters.preempted == 0      # seen after each step, when the pages behind the window are back
+    want = []
+    for p in prompts:
+        solo_runner = FakeRunner(pages=64, groups=groups)
+        one = Scheduler(solo_runner, FakeSampler(), max_batch_tokens=512)
+        i = one.submit(p, SamplingParams(max_new_tokens=10))
+        one.run_all()
+        want.append(one.request(i).generated)
+    assert [s.request(i).generated for i in ids] == want
+    assert r.books.free_pages() == [64, 11]
+    r.books.check()
+    # in one step of a whole request the windowed group would need as much as the other one
+    slot = r.books.admit()
+    assert r.books.pages_to_hold(slot, 90) == [23, 23] and r.books.pages_to_hold(slot, 90, 6) == [23, 5]

@@ -143,3 +143,29 @@ def test_random_weights_depend_on_seed_and_name_only():
         if schema[n].init == "normal":
             assert not torch.equal(a.get(n, schema[n]), c.get(n, schema[n]))
     assert not torch.equal(a.get(names[3], schema[names[3]]).flatten()[:8], a.get(names[10], schema[names[10]]).flatten()[:8])
+
+
+def test_random_values_follow_the_plain_generator_element_by_element():
+    """The numpy generator against its restatement with Python integers: single elements far
+    apart (also beyond a chunk of the numpy loop and beyond 2^32), float32 and bfloat16."""
+    import plain_random as PR
+    from cajeta_llm_b200.parts.plan import ParamSpec
+    from cajeta_llm_b200.weights import random_fill as R
+    seed, name, std = 7, "model.layers.3.mlp.experts.5.up_proj.weight", 0.02
+    key = R.tensor_key(seed, name)
+    assert key == PR.key_of(seed, name)
+    n = R.CHUNK + 1000
+    x = R.fill(n, key, std)
+    for i in (0, 1, 2, 4097, R.CHUNK - 1, R.CHUNK, R.CHUNK + 999):
+        assert float(x[i]) == PR.value(seed, name, i, std), i
+    far = (1 << 33) + 12345
+    assert float(R.fill(3, key, std, start=far)[2]) == PR.value(seed, name, far + 2, std)
+    assert abs(float(x.mean())) < 3 * std / np.sqrt(n) and abs(float(x.std()) / std - 1.0) < 0.01
+    assert float(np.abs(x).max()) <= 4.9 * std
+    spec = ParamSpec((40, 50), std=std)
+    got = RandomWeights(seed, torch.bfloat16).get(name, spec)
+    assert got.dtype == torch.bfloat16 and tuple(got.shape) == (40, 50)
+    for i in (0, 7, 1999):
+        assert float(got.flatten()[i]) == PR.to_bfloat16(PR.value(seed, name, i, std)), i
+    got32 = RandomWeights(seed, torch.float32).get(name, spec)
+    assert float(got32.flatten()[1234]) == PR.value(seed, name, 1234, std)
