@@ -68,6 +68,26 @@ def _stream() -> ctypes.c_void_p:
 
 
 launches = 0      # kernels launched through this module since import (each wrapper launches one)
+# Measurement: parts name the class of work their next launches belong to (``tag``: "qkv", "expert
+# gate/up", ...; costs an assignment); while a trace is open every launch is followed by an event
+# on the stream, so that the time between two events is one launch's device time with the launches
+# serialised (an event between two kernels keeps them from overlapping).
+tag: Optional[str] = None
+_trace: Optional[list] = None
+
+
+def start_trace() -> None:
+    global _trace
+    _trace = []
+
+
+def stop_trace() -> list:
+    """[(class of work, event recorded after the launch)] since ``start_trace``."""
+    global _trace
+    out, _trace = _trace or [], None
+    return out
+
+
 _router_tickets: Dict[torch.device, torch.Tensor] = {}      # arrival tickets of the small-batch router (kept zero by the kernel)
 
 
@@ -75,6 +95,10 @@ def _check(status: int, what: str) -> None:
     global launches
     if status == 0:
         launches += 1
+        if _trace is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            _trace.append((tag or what, ev))
         return
     if status in _REFUSALS:
         raise KernelError(f"{what}: refused: {_REFUSALS[status]}")

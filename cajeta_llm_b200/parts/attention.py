@@ -104,12 +104,15 @@ class PagedAttention(Part):
         write = entry.writes_cache
         n_out = self.q_dim + (2 * self.kv_dim if write else 0)
         qkv = torch.empty((T, n_out), dtype=torch.float32, device=x.device)
+        K.tag = "qkv"
         project(rt, x, self.w_qkv[:n_out], qkv, bias=None if self.b_qkv is None else self.b_qkv[:n_out])
         q = torch.empty((T, self.heads, self.head_dim), dtype=rt.act_dtype, device=x.device)
+        K.tag = "rope + cache write"
         K.rope_kv_write(qkv, 0, self.q_dim, self.q_dim + self.kv_dim, q, entry.k_plane, entry.v_plane,
                         ctx.positions, ctx.row_req, entry.block_table, entry.page_tokens, self.heads, self.kv_heads,
                         self.head_dim, pos.rotary_dim, pos.inv_freq, write)
         out = torch.empty_like(q)
+        K.tag = "attention"
         if rt.fast_kernels and getattr(ctx, "all_single", False) and self.head_dim in (64, 128):
             # every request brings one token: the split-KV decode kernel
             K.decode_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
@@ -127,8 +130,9 @@ class PagedAttention(Part):
         else:
             K.paged_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
                               entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale)
+        K.tag = "o"
         parts = project_split(rt, out.view(T, self.q_dim), self.w_o, bias=self.b_o)
-        if parts is not None:
-            return parts                     # owed to the residual stream; the next norm adds them
-        project(rt, out.view(T, self.q_dim), self.w_o, residual, bias=self.b_o, accumulate=True)
-        return None
+        if parts is None:
+            project(rt, out.view(T, self.q_dim), self.w_o, residual, bias=self.b_o, accumulate=True)
+        K.tag = None
+        return parts                         # partial sums owed to the residual stream (the next norm adds them), or None

@@ -51,7 +51,9 @@ class TokenEmbedding(Part):
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         hs = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
+        K.tag = "embedding"
         K.embed_gather(hs, self.table, token_ids, self.scale)
+        K.tag = None
         return hs
 
 
@@ -92,5 +94,7 @@ class LinearHead(Part):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         out = torch.empty((x.shape[0], self.vocab), dtype=torch.float32, device=x.device)
+        K.tag = "head"
         project(self.runtime, x, self.weight, out, bias=self.bias)
+        K.tag = None
         return out

@@ -68,8 +68,11 @@ class DenseSwiGLU(Part):
     def forward(self, x: torch.Tensor, x_f32: Optional[torch.Tensor], residual: torch.Tensor, ctx) -> None:
         T = x.shape[0]
         act = torch.empty((T, self.inter), dtype=self.runtime.act_dtype, device=x.device)
+        K.tag = "dense gate/up"
         project(self.runtime, x, self.w_gate, act, w_up=self.w_up)
+        K.tag = "dense down"
         project(self.runtime, act, self.w_down, residual, accumulate=True)
+        K.tag = None
 
 
 @register_part("feed_forward", "sparse_moe")
@@ -222,6 +225,7 @@ class SparseMoE(Part):
         pins, dump = getattr(ctx, "routing_pin", None), getattr(ctx, "routing_dump", None)
         pin = pins.get(self.prefix) if pins else None
         gap = torch.empty((T,), dtype=torch.float32, device=dev) if dump is not None and pin is None else None
+        K.tag = "router"
         self._route(x_exact, sel, wts, shared_scale, pin, gap)
         if dump is not None:
             dump[self.prefix] = (sel, gap)
@@ -232,14 +236,17 @@ class SparseMoE(Part):
         offsets = torch.empty((E + C + 1,), dtype=torch.int32, device=dev)
         slot_token = torch.empty((n_slots,), dtype=torch.int32, device=dev)
         slot_of_pick = torch.empty((T * k,), dtype=torch.int32, device=dev)
+        K.tag = "grouping"
         K.moe_group(sel, k, E, offsets, slot_token, slot_of_pick, extra_groups=C)
         self.last_offsets = offsets          # kept for measurement: which experts the last step touched
 
         act = torch.empty((n_slots, self.inter), dtype=rt.act_dtype, device=dev)
         G = E + C
+        K.tag = "experts gate/up"
         project(rt, x, self.w_gate[:G], act, w_up=self.w_up[:G], group_offsets=offsets, a_row_index=slot_token,
                 max_group_rows=T)
         y = torch.empty((n_slots, self.hidden), dtype=torch.float32, device=dev)
+        K.tag = "experts down"
         project(rt, act, self.w_down[:G], y, group_offsets=offsets, max_group_rows=T, offsets_settled=True)
 
         shared = None
@@ -252,7 +259,11 @@ class SparseMoE(Part):
                 ws_up = self.w_up[E:].view(self.shared_inter, self.hidden)
             else:
                 ws_gate, ws_up = self.ws_gate, self.ws_up
+            K.tag = "shared gate/up"
             project(rt, x, ws_gate, sact, w_up=ws_up)
             shared = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
+            K.tag = "shared down"
             project(rt, sact, self.ws_down, shared)
+        K.tag = "combine"
         K.moe_combine(residual, y, slot_of_pick, wts, k, shared, shared_scale)
+        K.tag = None

@@ -91,20 +91,22 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
         K.gemm(x, w, out, bias=bias, accumulate=accumulate, w_up=w_up, group_offsets=group_offsets, a_row_index=a_row_index)
         return
     rows = out.shape[0]
-    if a_row_index is not None:
-        gathered = torch.empty((rows, x.shape[-1]), dtype=x.dtype, device=x.device)
-        K.gather_rows(x, a_row_index, gathered)
-        x = gathered
-        offsets_settled = True
     if w_up is not None:
         epi = K.EPI_SWIGLU_BF16
     elif out.dtype == torch.bfloat16:
         epi = K.EPI_STORE_BF16
     else:
         epi = K.EPI_ACC_F32 if accumulate else K.EPI_STORE_F32
+    bound = rows if max_group_rows is None else min(rows, max_group_rows)
+    if a_row_index is not None:
+        gathered = torch.empty((rows, x.shape[-1]), dtype=x.dtype, device=x.device)
+        tag, K.tag = K.tag, "row gather"
+        K.gather_rows(x, a_row_index, gathered)
+        K.tag = tag
+        x = gathered
+        offsets_settled = True
     # few rows: weights on the rows of the product; a group of a mixture rarely has more
     # rows than the step has tokens, which bounds the token tile
-    bound = rows if max_group_rows is None else min(rows, max_group_rows)
     tile = _token_tile(bound)
     if not tile and group_offsets is not None:
         # ragged groups: weights on the rows, tokens on the product's N (cut to the tokens a

@@ -276,3 +276,4 @@ def test_language_model_head_at_the_real_vocabulary(K, rows):
         assert bool((d <= 2e-3 + 2e-3 * want.abs()).all()), (lo, float(d.max()))
         worst = max(worst, float(d.max()))
     print(f"\nhead {rows} rows: worst |diff| {worst:.3e}")
+
