@@ -67,7 +67,7 @@ def _native() -> ctypes.CDLL:
             "cj_books_reserve_step": (c_int, [_P, _IP, _IP, c_int, _IP]), "cj_books_commit": (c_int, [_P, c_int, c_int]),
             "cj_books_reserve_one_each": (c_int, [_P, _IP, c_int, _P]), "cj_books_commit_one_each": (c_int, [_P, _IP, c_int]),
             "cj_books_table_width": (c_int, [_P, _IP, c_int]),
-            "cj_books_layout_step": (c_ll, [_P, c_int, _IP, _IP, _IP, _IP, _IP, c_int, _P, c_ll]),
+            "cj_books_layout_step": (c_ll, [_P, c_int, _IP, _IP, _IP, _IP, _IP, c_int, c_int, c_int, _P, c_ll]),
             "cj_books_check": (c_int, [_P]),
         }
         for name, (res, args) in sigs.items():
@@ -312,13 +312,15 @@ class CacheBooks:
         return self._lib.cj_books_table_width(self._h, _ip(s), s.size)
 
     def layout_step(self, slots: np.ndarray, n_tokens: np.ndarray, tokens: np.ndarray, n_want: np.ndarray,
-                    wants: np.ndarray, width: int, out: np.ndarray) -> int:
+                    wants: np.ndarray, width: int, out: np.ndarray, pad_requests: int = 0, pad_wanted: int = 0) -> int:
         """Lays a step's metadata into ``out`` (int32): tokens | positions | row -> request |
         request starts | prior lengths | slots | wanted rows | one slab ``[requests, width]`` of
-        block-table rows per group.  All arguments are contiguous int32 arrays; returns the
-        number of values written."""
+        block-table rows per group.  ``pad_requests`` / ``pad_wanted`` lay the per-request arrays
+        and the wanted rows out for at least that many (requests without rows, wanted row 0), so
+        that steps of one number of rows share one shape.  All arguments are contiguous int32
+        arrays; returns the number of values written."""
         n = self._lib.cj_books_layout_step(self._h, slots.size, _ip(slots), _ip(n_tokens), _ip(tokens), _ip(n_want),
-                                           _ip(wants), width, out.ctypes.data, out.size)
+                                           _ip(wants), width, pad_requests, pad_wanted, out.ctypes.data, out.size)
         if n < 0:
             self._fail()
         return int(n)

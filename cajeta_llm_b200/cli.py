@@ -14,7 +14,8 @@ spaces or commas, and the generated ids are printed, followed by
 ``[N tokens, budget | eos | stop | cancel]`` as the reference prints it
 (cli/Main.cajeta:83-122).  ``--prompt`` may be given several times; the prompts are then
 served together.  ``chat`` needs a chat template and a tokenizer and is not offered.
-Added flags: ``--dtype bfloat16|float32``, ``--max-batch-tokens N``, ``--num-blocks N``.
+Added flags: ``--dtype bfloat16|float32``, ``--max-batch-tokens N``, ``--num-blocks N``,
+``--no-warmup`` (skip the throw-away steps at load).
 
 A second verb writes a random-weights model folder from a configuration and a seed:
 
@@ -88,6 +89,8 @@ def parse_run(args: Sequence[str]):
             i = _need_val(args, i, a); o.max_batch_tokens = int(args[i])
         elif a == "--num-blocks":
             i = _need_val(args, i, a); o.num_blocks = int(args[i])
+        elif a == "--no-warmup":
+            o.warmup = False      # a bare toggle: the first request then pays for cold kernels and graph capture
         elif a == "--verbose":
             o.verbose = True      # a bare toggle: it takes no value
         else:

@@ -354,10 +354,16 @@ CJ_EXPORT int cj_books_table_width(void* h, const int* slots, int n) {
 //   one slab [requests, width] of block-table rows per group.
 // n_tokens[i] tokens of request i follow one another in `tokens`; wants holds, request after
 // request, n_want[i] indices into that request's tokens.  The caller has checked the tokens and
-// the wanted indices and has reserved the step's pages.  Returns the int32 values written, or
-// CJ_BOOKS_ERROR when `out` (capacity out_len) is too small or a slot holds nothing.
+// the wanted indices and has reserved the step's pages.
+// pad_requests > n lays the per-request arrays out for that many requests: the ones beyond n
+// bring no rows (they start where the rows end, hold nothing, slot -1, a table row of -1), so
+// that a step's buffer has the same shape whatever the number of its requests; pad_wanted > W
+// fills the wanted rows up with row 0 (their logits are computed and thrown away).  Returns the
+// int32 values written, or CJ_BOOKS_ERROR when `out` (capacity out_len) is too small or a slot
+// holds nothing.
 CJ_EXPORT long long cj_books_layout_step(void* h, int n, const int* slots, const int* n_tokens, const int* tokens,
-                                         const int* n_want, const int* wants, int width, int32_t* out, long long out_len) {
+                                         const int* n_want, const int* wants, int width, int pad_requests, int pad_wanted,
+                                         int32_t* out, long long out_len) {
     Books* b = B(h);
     long long T = 0, W = 0;
     for (int i = 0; i < n; ++i) {
@@ -366,17 +372,19 @@ CJ_EXPORT long long cj_books_layout_step(void* h, int n, const int* slots, const
         W += n_want[i];
     }
     if (width < 1 || width > b->width) { b->error = "block-table width " + std::to_string(width) + " is out of range"; return CJ_BOOKS_ERROR; }
+    const long long R = pad_requests > n ? pad_requests : n;
+    const long long Wp = pad_wanted > W ? pad_wanted : W;
     const long long G = (long long)b->groups.size();
-    const long long total = 3 * T + (n + 1) + 2LL * n + W + G * n * width;
+    const long long total = 3 * T + (R + 1) + 2LL * R + Wp + G * R * width;
     if (total > out_len) { b->error = "the step's metadata needs " + std::to_string(total) + " values"; return CJ_BOOKS_ERROR; }
     int32_t* tok = out;
     int32_t* pos = tok + T;
     int32_t* row_req = pos + T;
     int32_t* req_start = row_req + T;
-    int32_t* req_prior = req_start + n + 1;
-    int32_t* req_slot = req_prior + n;
-    int32_t* want_rows = req_slot + n;
-    int32_t* tables = want_rows + W;
+    int32_t* req_prior = req_start + R + 1;
+    int32_t* req_slot = req_prior + R;
+    int32_t* want_rows = req_slot + R;
+    int32_t* tables = want_rows + Wp;
     long long row = 0, wi = 0;
     for (int i = 0; i < n; ++i) {
         const int64_t prior = b->length[(size_t)slots[i]];
@@ -392,11 +400,20 @@ CJ_EXPORT long long cj_books_layout_step(void* h, int n, const int* slots, const
         wi += n_want[i];
         row += n_tokens[i];
     }
-    req_start[n] = (int32_t)row;
-    for (long long g = 0; g < G; ++g)
+    for (long long i = n; i < R; ++i) {
+        req_start[i] = (int32_t)row;
+        req_prior[i] = 0;
+        req_slot[i] = -1;
+    }
+    req_start[R] = (int32_t)row;
+    for (long long j = W; j < Wp; ++j) want_rows[j] = 0;
+    for (long long g = 0; g < G; ++g) {
         for (int i = 0; i < n; ++i)
-            memcpy(tables + (g * n + i) * width, b->groups[(size_t)g].table.data() + (size_t)slots[i] * b->width,
+            memcpy(tables + (g * R + i) * width, b->groups[(size_t)g].table.data() + (size_t)slots[i] * b->width,
                    (size_t)width * sizeof(int32_t));
+        for (long long i = n; i < R; ++i)
+            for (int j = 0; j < width; ++j) tables[(g * R + i) * width + j] = -1;
+    }
     return total;
 }
 

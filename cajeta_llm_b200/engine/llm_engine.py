@@ -42,6 +42,44 @@ class LlmEngine:
         self._scheduler = Scheduler(self.runner, self.sampler, max_batch_tokens=options.max_batch_tokens,
                                     chunk=options.chunk, eog_token_ids=self._eog, lookahead=options.lookahead)
         self._closed = False
+        if options.warmup:
+            self._warm_up()
+
+    def _warm_up(self) -> None:
+        """A throw-away prompt portion and decode steps right after load, as the reference does
+        (LlmEngine.cajeta:294-324): kernels are loaded and configured, and on the bfloat16 path
+        the decode graphs of the batch sizes 1, 2, 4, ... up to ``max_seqs`` are captured, before
+        the first request arrives.  Everything it held is given back."""
+        from .step import OutOfPages, StepEntry
+        r = self.runner
+        n = min(16, self.options.ctx - 8)
+        if n < 1:
+            return
+        sizes = sorted({b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= self.options.max_seqs} | {self.options.max_seqs})
+        if not r.cuda_graphs:
+            sizes = sizes[:1]
+        slots: List[int] = []
+        try:
+            for size in sizes:
+                fresh = []
+                while len(slots) + len(fresh) < size:
+                    s = r.admit()
+                    if s is None:
+                        break
+                    fresh.append(s)
+                if fresh:
+                    r.step([StepEntry(s, [0] * n, []) for s in fresh])
+                    slots += fresh
+                if any(r.cache.length(s) + 2 > self.options.ctx for s in slots):
+                    break
+                for _ in range(2):                     # the first captures this batch size's graph, the second replays it
+                    r.step([StepEntry(s, [0], [0]) for s in slots])
+        except OutOfPages:
+            pass                                       # a pool too small for all sizes: what fitted is warm
+        finally:
+            for s in slots:
+                r.release(s)
+            torch.cuda.synchronize()
 
     # -- loading ---------------------------------------------------------------------
     @classmethod

@@ -6,7 +6,9 @@ EngineOptions.cajeta:98-122: ``ctx`` 4096 (most tokens one request may hold),
 the largest portion), ``device``.  This engine adds ``dtype`` (``bfloat16`` serving
 path or the true ``float32`` path), ``max_batch_tokens`` (token budget of one mixed
 step), ``num_blocks`` (cache pages per layer group; 0 = enough for ``max_seqs``
-requests of ``ctx`` tokens) and the random-weights mode (``random_weights``, ``seed``).
+requests of ``ctx`` tokens), the random-weights mode (``random_weights``, ``seed``) and
+``warmup`` (the reference always warms at load with one throw-away prefill and decode step,
+LlmEngine.cajeta:294-324; here it can be switched off).
 The reference's tuning pins, KV store and per-backend switches have no counterpart.
 """
 from __future__ import annotations
@@ -32,6 +34,7 @@ class EngineOptions:
     verbose: bool = False
     cuda_graphs: bool = True           # replay pure decode steps of the bfloat16 path from CUDA graphs
     lookahead: bool = True             # while all requests decode, launch the next step before the host has seen this step's tokens
+    warmup: bool = True                # at load: a throw-away prompt portion and decode steps, so that the first request meets warm kernels and captured graphs
 
     def validate(self) -> None:
         if self.ctx < 1:

@@ -148,8 +148,8 @@ class ModelRunner:
             from ..csrc import build as _build
             _build.build_all(sorted(n for n in model.libraries() if n in _build.LIBRARIES))
         self._graphs: Dict[Tuple[int, int], _CapturedStep] = {}
-        self._mixed_graphs: Dict[Tuple[int, int, int], _CapturedStep] = {}   # by (rows, requests, wanted), oldest use first
-        self._mixed_seen: Dict[Tuple[int, int, int], int] = {}
+        self._mixed_graphs: Dict[Tuple[int, int], _CapturedStep] = {}   # by (rows, wanted rows filled up), oldest use first
+        self._mixed_seen: Dict[Tuple[int, int], int] = {}
         self._graph_pool = None
         self._decode_host: Dict[Tuple[int, int], tuple] = {}   # pinned metadata of decode steps by (rows, width), reused
         self._meta_copied = None                               # event: the last copy out of the buffer in use is over
@@ -198,9 +198,19 @@ class ModelRunner:
 
     def _step_mixed(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """A step with prompt portions on the bfloat16 path: uncaptured the first time its shape
-        (rows, requests, wanted rows) is met, captured the second time, replayed afterwards."""
+        is met, captured the second time, replayed afterwards.  The shape is the number of rows
+        and of wanted rows only: the per-request arrays are laid out for ``max_seqs`` requests
+        whatever the step has (the others bring no rows), and up to ``max_seqs`` wanted rows are
+        filled up to that number (the logits of the fillers are thrown away; a step that wants
+        nothing stays so), so that the steps
+        of a scheduler that fills a token budget - the same number of rows step after step, among
+        a changing number of requests of which a changing number ends - replay one graph."""
         from ..csrc import kernels as K
-        key = (sum(len(e.tokens) for e in entries), len(entries), sum(len(e.want) for e in entries))
+        rows = sum(len(e.tokens) for e in entries)
+        wanted = sum(len(e.want) for e in entries)
+        pad_requests = self.cache.max_seqs
+        pad_wanted = 0 if wanted == 0 else max(wanted, min(rows, pad_requests))
+        key = (rows, pad_wanted)
         cap = self._mixed_graphs.get(key)
         if cap is None:
             seen = self._mixed_seen[key] = self._mixed_seen.get(key, 0) + 1
@@ -209,7 +219,7 @@ class ModelRunner:
             if seen < MIXED_CAPTURE_AFTER:
                 return self._forward(self._prepare(entries))
         # block tables as wide as they can ever get: the captured kernels keep the row stride
-        host, layout = self._build_meta(entries, self.cache.books.max_pages_per_seq)
+        host, layout = self._build_meta(entries, self.cache.books.max_pages_per_seq, pad_requests, pad_wanted)
         if cap is None:
             meta = torch.empty(host.shape, dtype=torch.int32, device=self.runtime.device)
             meta.copy_(host, non_blocking=True)
@@ -225,13 +235,13 @@ class ModelRunner:
             while len(self._mixed_graphs) >= MIXED_GRAPHS_MAX:
                 self._mixed_graphs.pop(next(iter(self._mixed_graphs)))
             self._mixed_graphs[key] = _CapturedStep(graph, meta, static_logits, K.launches - before, None)
-            return logits
+            return logits[:wanted]
         self._mixed_graphs[key] = self._mixed_graphs.pop(key)      # most recently used last
         cap.meta.copy_(host, non_blocking=True)
         cap.graph.replay()
         K.launches += cap.launches
         self.graph_replays += 1
-        return cap.logits.clone()              # the static buffer is overwritten by the next replay
+        return cap.logits[:wanted].clone()     # the static buffer is overwritten by the next replay
 
     def check_waits(self) -> None:
         """Every wait inside the tensor-core kernels is bounded; one that ran out left a code
@@ -337,7 +347,7 @@ class ModelRunner:
             return dev[int(offs[i]): int(offs[i + 1])]
 
         return StepContext(
-            n_rows=req_start[-1], n_requests=R, token_ids=view(0), positions=view(1), row_req=view(2), req_start=view(3),
+            n_rows=req_start[len(entries)], n_requests=R, token_ids=view(0), positions=view(1), row_req=view(2), req_start=view(3),
             req_prior=view(4), req_slot=view(5), want_rows=view(6),
             tables=[view(7 + g).view(R, width) for g in range(G)],
             h_req_start=req_start, h_req_prior=req_prior, h_req_slot=slots,
@@ -387,11 +397,13 @@ class ModelRunner:
             h[offs[7 + g]:offs[8 + g]] = cache.table_rows(g, slots, width).reshape(-1)
         return host, (offs, R, width, G, rows, prior.tolist(), slots)
 
-    def _build_meta(self, entries: Sequence[StepEntry], width: Optional[int]):
+    def _build_meta(self, entries: Sequence[StepEntry], width: Optional[int], pad_requests: int = 0, pad_wanted: int = 0):
         """Checks the step, reserves its pages and lays its metadata into one pinned int32
         buffer: tokens | positions | row->request | request starts | prior lengths | slots |
         wanted rows | one block-table slab per cache group.  The reservation (all or nothing
-        over the whole step) and the layout are the native books' work."""
+        over the whole step) and the layout are the native books' work.  ``pad_requests`` /
+        ``pad_wanted``: the per-request arrays and the wanted rows are laid out for at least that
+        many (requests without rows; wanted row 0)."""
         cache = self.cache
         vocab = self.model.vocab
         slots = [e.slot for e in entries]
@@ -415,14 +427,15 @@ class ModelRunner:
             raise OutOfPages(f"step needs {short} new pages per group; free: {cache.free_pages()}")
         req_prior = [cache.length(s) for s in slots]
 
-        R = len(entries)
+        R = max(len(entries), pad_requests)
         T = int(counts.sum())
         if width is None:
             width = cache.table_width(slots)
         G = cache.num_groups
-        sizes = [T, T, T, R + 1, R, R, int(n_want.sum())] + [R * width] * G
+        sizes = [T, T, T, R + 1, R, R, max(int(n_want.sum()), pad_wanted)] + [R * width] * G
         offs = np.concatenate([[0], np.cumsum(sizes)])
         host = torch.empty((int(offs[-1]),), dtype=torch.int32, pin_memory=True)
-        cache.books.layout_step(slot_arr, counts, tokens.astype(np.int32), n_want, wants, width, host.numpy())
+        cache.books.layout_step(slot_arr, counts, tokens.astype(np.int32), n_want, wants, width, host.numpy(),
+                                pad_requests=pad_requests, pad_wanted=pad_wanted)
         req_start = np.concatenate([[0], np.cumsum(counts)]).tolist()
         return host, (offs, R, width, G, req_start, req_prior, slots)

@@ -285,6 +285,16 @@ def test_native_step_layout():
     want = ([10, 11, 12, 20] + [2, 3, 4, 7] + [0, 0, 0, 1] + [0, 3, 4] + [2, 7] + [s1, s0] + [0, 2, 3]
             + b.groups[0].table[[s1, s0], :2].reshape(-1).tolist() + b.groups[1].table[[s1, s0], :2].reshape(-1).tolist())
     assert out[:n].tolist() == want and (out[n:] == -7).all()
+    # the same step laid out for 4 requests and 5 wanted rows: requests without rows, wanted row 0
+    out2 = np.full(80, -7, dtype=np.int32)
+    n2 = b.layout_step(slots, counts, tokens, n_want, wants, width, out2, pad_requests=4, pad_wanted=5)
+    R, W = 4, 5
+    assert n2 == 3 * T + (R + 1) + 2 * R + W + G * R * width
+    none = [-1] * (2 * width)
+    want2 = ([10, 11, 12, 20] + [2, 3, 4, 7] + [0, 0, 0, 1] + [0, 3, 4, 4, 4] + [2, 7, 0, 0] + [s1, s0, -1, -1] + [0, 2, 3, 0, 0]
+             + b.groups[0].table[[s1, s0], :2].reshape(-1).tolist() + none
+             + b.groups[1].table[[s1, s0], :2].reshape(-1).tolist() + none)
+    assert out2[:n2].tolist() == want2 and (out2[n2:] == -7).all()
     with pytest.raises(CacheError, match="needs"):
         b.layout_step(slots, counts, tokens, n_want, wants, width, out[:10])
     with pytest.raises(CacheError, match="holds no request"):
