@@ -158,3 +158,63 @@ def test_vectorised_restatement_equals_the_row_by_row_implementation(name, tmp_p
     # ties go to the lower index here as there
     sel, w, margin = PV.route(torch.tensor([[1.0, 2.0, 2.0, 0.5, 2.0]], dtype=torch.float64), 2, False)
     assert sel.tolist() == [[1, 2]] and abs(float(margin[0])) < 1e-12
+
+
+def _filled2(rows, cols, seed):
+    i = np.arange(rows * cols, dtype=np.int64)
+    return torch.from_numpy((np.float32(0.0625) * (((i + seed) * 7 + 3) % 15).astype(np.float32) - np.float32(0.4375))
+                            .reshape(rows, cols)).double()
+
+
+def test_plain_parts_meet_the_cases_of_the_reference_tests():
+    """tests/golden/reference_cases.json holds the cases of the reference's own unit tests for
+    RMSNorm, the rotation, SwiGLU and attention (grouped heads, causal rows, a window whose
+    out-of-window values are 10^6) with the values those tests hold the reference to.  The plain
+    implementation's part functions meet them within the reference's tolerances."""
+    with open(os.path.join(os.path.dirname(GOLDEN), "reference_cases.json")) as f:
+        cases = json.load(f)
+
+    c = cases["rmsnorm"]
+    i = np.arange(c["rows"] * c["dim"])
+    x = torch.from_numpy((np.float32(0.25) * ((3 * i + 1) % 11).astype(np.float32) - np.float32(1.0)).reshape(c["rows"], c["dim"])).double()
+    w = torch.from_numpy(np.float32(0.125) * (np.arange(c["dim"]) + 1).astype(np.float32)).double()
+    assert np.allclose(P.rmsnorm(x, w, c["eps"]).numpy(), c["want"], atol=c["tolerance"], rtol=0)
+
+    c = cases["rope"]
+    hd = c["head_dim"]
+    xv = torch.from_numpy(np.float32(0.25) * (np.arange(hd) + 1).astype(np.float32) - np.float32(1.0)).double().reshape(1, 1, hd)
+    for theta, want in c["want"].items():
+        got = P.rope(xv, torch.tensor([c["position"]]), P.inv_freq(hd, float(theta), torch.float64))
+        assert np.allclose(got.reshape(-1).numpy(), want, atol=c["tolerance"], rtol=0), theta
+
+    c = cases["swiglu"]
+    g = torch.from_numpy(np.float32(0.75) * (np.arange(8) - 4).astype(np.float32)).double()
+    u = torch.from_numpy(np.float32(0.5) * (np.arange(8) + 1).astype(np.float32) - np.float32(2.0)).double()
+    assert np.allclose((P.silu(g) * u).numpy(), c["want"], atol=c["tolerance"], rtol=0)
+
+    c = cases["attention_gqa"]
+    nH, nKv, hd, T = c["heads"], c["kv_heads"], c["head_dim"], c["keys"]
+    q = torch.zeros(T, nH, hd, dtype=torch.float64)
+    q[T - 1] = _filled2(1, nH * hd, c["seeds"][0]).reshape(nH, hd)
+    k, v = (_filled2(T, nKv * hd, s).reshape(T, nKv, hd) for s in c["seeds"][1:])
+    assert np.allclose(P.attention(q, k, v, 0, c["scale"])[T - 1].numpy(), c["want"], atol=c["tolerance"], rtol=0)
+
+    c = cases["attention_causal"]
+    nH, nKv, hd, T = c["heads"], c["kv_heads"], c["head_dim"], c["rows_total"]
+    q = _filled2(T, nH * hd, c["seeds"][0]).reshape(T, nH, hd)
+    k, v = (_filled2(T, nKv * hd, s).reshape(T, nKv, hd) for s in c["seeds"][1:])
+    got = P.attention(q, k, v, 0, c["scale"])
+    assert np.allclose(got[c["rows"]].numpy(), c["want"], atol=c["tolerance"], rtol=0)
+
+    c = cases["attention_window"]
+    hd, T = c["head_dim"], c["keys"]
+    k = _filled2(T, hd, c["seeds"]["k"]).reshape(T, 1, hd)
+    v = torch.tensor([[1000000.0 if t < c["poison_before"] else float(np.float32(0.125) * np.float32(t % 5) - np.float32(0.25))] * hd
+                      for t in range(T)], dtype=torch.float64).reshape(T, 1, hd)
+    q = torch.zeros(T, 1, hd, dtype=torch.float64)
+    q[20, 0] = _filled2(1, hd, c["seeds"]["q20"])[0]
+    q[5, 0] = _filled2(1, hd, c["seeds"]["q5"])[0]
+    got = P.attention(q, k, v, c["window"], c["scale"])
+    assert float(got[20].abs().max()) < 1000.0                       # nothing of the values behind the window
+    assert np.allclose(got[20, 0].numpy(), c["row_20"], atol=c["tolerance"], rtol=0)
+    assert np.allclose(got[5, 0].numpy(), c["row_5"], atol=c["tolerance"], rtol=0)
