@@ -106,7 +106,7 @@ class ModelRunner:
     A step in which every request brings exactly one token (pure decode) is launch-bound:
     hundreds of small kernels.  On the bfloat16 path such a step is captured once per
     (batch size, context bucket) as a CUDA graph and replayed afterwards; the step's
-    metadata (tokens, positions, block tables) lives in a static device buffer that is
+    metadata (tokens, positions, block tables, slots) lives in a static device buffer that is
     refreshed before each replay.  The captured kernels are the same ones an uncaptured
     step launches, so both give the same logits.
 
@@ -141,7 +141,15 @@ class ModelRunner:
         self.page_tokens = page_tokens
         self.max_tokens_per_seq = max_tokens_per_seq
         self.steps_run = 0
-        self.cuda_graphs = cuda_graphs and self.runtime.fast_kernels and self.runtime.device.type == "cuda"
+        # Steps are captured as CUDA graphs on the bfloat16 path - unless a mixer keeps state and has
+        # not said that it is safe to capture.  A mixer with state says so with ``graph_safe = True``:
+        # it then finds its requests' slots, rows and positions in the step's DEVICE metadata only
+        # (``ctx.req_slot``, ``ctx.req_start``, ``ctx.row_req``, ``ctx.positions``: a captured step is
+        # replayed with other values in them), reads nothing back on the host, and leaves alone the
+        # requests a step's layout is filled up with (slot -1, no rows).
+        mixers = [model.blocks[e.layer].mixer for e in model.plan.schedule]
+        graph_safe = all(getattr(m, "graph_safe", m.state_need() is None) for m in mixers)
+        self.cuda_graphs = cuda_graphs and graph_safe and self.runtime.fast_kernels and self.runtime.device.type == "cuda"
         # what this model needs is compiled now, side by side (a library not named here is still
         # compiled when it is first wanted)
         if str(self.runtime.device).startswith("cuda"):
@@ -185,9 +193,9 @@ class ModelRunner:
             ctx = self._prepare(entries)
             ctx.routing_pin, ctx.routing_dump = routing_pin, routing_dump
             logits = self._forward(ctx)
-        elif self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and not self.cache.state:
+        elif self.cuda_graphs and all(len(e.tokens) == 1 for e in entries):
             return self._step_captured(entries)
-        elif self.cuda_graphs and not self.cache.state:
+        elif self.cuda_graphs:
             logits = self._step_mixed(entries)
         else:
             logits = self._forward(self._prepare(entries))
@@ -271,7 +279,7 @@ class ModelRunner:
         before): the host never sees them before the launch.  Returns the logits of every row,
         or None when this shape has no captured graph yet (the caller then takes the ordinary
         ``step`` once).  Raises :class:`OutOfPages` like ``step``."""
-        if not self.cuda_graphs or self.cache.state:
+        if not self.cuda_graphs:
             return None
         # chained steps are steps like any other: the kernels' wait flags are looked at as often
         self._calls = getattr(self, "_calls", 0) + 1

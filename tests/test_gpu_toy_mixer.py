@@ -50,22 +50,53 @@ def define_toy():
                     s.mul_(self.decay).add_(u[row])
                     residual[row] += s
 
+    class DecayMixerOnDevice(DecayMixer):
+        """The same mixer written so that a step which runs it can be captured as a CUDA graph and
+        replayed: it finds slots, rows and request boundaries in the step's device metadata only,
+        with shapes that depend on nothing but the step's numbers of rows and (laid-out) requests.
+        s after row j of a request = decay^(j+1) s_before + sum_{m <= j} decay^(j-m) u_m: one
+        masked triangular product instead of a loop over rows."""
+
+        graph_safe = True
+
+        def forward(self, x, residual, ctx, entry):
+            u = x.float() @ self.w.float().t()                                  # [rows, hidden]
+            rows = torch.arange(u.shape[0], device=u.device)
+            req = ctx.row_req.long()
+            start, slot = ctx.req_start.long(), ctx.req_slot.long()
+            j = rows - start[req]                                               # index of the row within its request's rows
+            same = req[:, None] == req[None, :]
+            ahead = rows[:, None] - rows[None, :]
+            m = torch.where(same & (ahead >= 0), torch.pow(self.decay, ahead.clamp(min=0).float()), 0.0)
+            before = entry.state[slot.clamp(min=0)[req]]                        # each row's request's state before the step
+            s = m @ u + torch.pow(self.decay, (j + 1).float())[:, None] * before
+            residual += s
+            # new state of every request that brought rows: s at its last row; the others (and the
+            # requests the layout was filled up with, slot -1) keep theirs
+            has = start[1:] > start[:-1]
+            last = (start[1:] - 1).clamp(min=0)
+            onehot = (torch.arange(entry.state.shape[0], device=u.device)[:, None] == slot[None, :]) & has[None, :]
+            onehot = onehot.float()                                             # [slots, requests]
+            entry.state.copy_(onehot @ s[last] + (1.0 - onehot.sum(dim=1, keepdim=True)) * entry.state)
+
     register_part("mixer", "toy_decay", DecayMixer, replace=True)
+    register_part("mixer", "toy_decay_device", DecayMixerOnDevice, replace=True)
 
     @dataclass(frozen=True)
     class ToyConfig(ModelConfig):
         hidden_size: int = 0
         vocab_size: int = 0
         decay: float = 0.5
+        mixer_kind: str = "toy_decay"
 
         @classmethod
         def from_reader(cls, r):
             return cls(architecture=r.raw["architectures"][0], hidden_size=r.integer("hidden_size"),
-                       vocab_size=r.integer("vocab_size"), decay=r.number("decay"))
+                       vocab_size=r.integer("vocab_size"), decay=r.number("decay"), mixer_kind=r.raw.get("mixer_kind", "toy_decay"))
 
         def to_json_dict(self):
             return {"architectures": [self.architecture], "hidden_size": self.hidden_size, "vocab_size": self.vocab_size,
-                    "decay": self.decay}
+                    "decay": self.decay, "mixer_kind": self.mixer_kind}
 
     def build_plan(cfg):
         h = cfg.hidden_size
@@ -76,7 +107,7 @@ def define_toy():
         att = PartSpec("attention", {"hidden_size": h, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16, "window": 0,
                                      "qkv_bias": False, "position": PartSpec("rope", {"head_dim": 16, "theta": 1e4})})
         layers = (
-            LayerSpec("toy.0", block, PartSpec("toy_decay", {"hidden_size": h, "decay": cfg.decay}), ff, norm, norm),
+            LayerSpec("toy.0", block, PartSpec(cfg.mixer_kind, {"hidden_size": h, "decay": cfg.decay}), ff, norm, norm),
             LayerSpec("toy.1", block, att, ff, norm, norm),
         )
         # run order: the state layer, the attention layer, the state layer AGAIN (its own
@@ -163,3 +194,54 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype, tmp_path):
     for n in seqs:
         helpers.assert_close(torch.cat(got[n]), want[n], dtype, f"toy request {n}")
     cache.books.check()
+
+
+def test_a_state_mixer_that_says_it_is_graph_safe_is_captured_and_replayed(tmp_path):
+    """The same toy model with the mixer that works from device metadata only (``graph_safe``):
+    on the bfloat16 path its steps are captured as CUDA graphs like any other model's - decode
+    steps and steps of one size with changing requests - give the bits of the same steps launched
+    kernel by kernel, and match the plain model.  (The mixer that walks host-side slot lists is
+    left uncaptured: the runner asks.)"""
+    ToyConfig = define_toy()
+    from cajeta_llm_b200.engine.model import build_model, load_model
+    from cajeta_llm_b200.engine.step import ModelRunner, StepEntry
+    from cajeta_llm_b200.parts.base import Runtime
+    from cajeta_llm_b200.weights.sources import write_model_folder
+
+    hidden = 136                                               # wide enough for the bfloat16 path's fast kernels
+    cfg = ToyConfig(architecture="ToyDecayForCausalLM", hidden_size=hidden, vocab_size=200, decay=0.6, mixer_kind="toy_decay_device")
+    schema = build_model(cfg, Runtime("float32", device="cpu")).params()
+    write_model_folder(str(tmp_path), cfg, schema, seed=4)
+    weights = P.read_safetensors(str(tmp_path / "model.safetensors"))
+    seqs = [helpers.random_tokens(200, n, seed=90 + n) for n in (40, 33, 27)]
+    want = [plain_toy(weights, t, hidden, 0.6) for t in seqs]
+    # 12 rows a step among one, two or three requests, then everybody decodes
+    plan = [{0: 12}, {0: 6, 1: 6}, {0: 2, 1: 2, 2: 8}, {1: 11, 2: 1}, {0: 1, 1: 1, 2: 10}]
+    outs = {}
+    for graphs in (False, True):
+        model, _ = load_model(str(tmp_path), Runtime("bfloat16", device=DEV))
+        runner = ModelRunner(model, page_tokens=4, max_seqs=3, max_tokens_per_seq=48, cuda_graphs=graphs)
+        assert runner.cuda_graphs == graphs
+        slots = [runner.admit() for _ in seqs]
+        at, got = [0, 0, 0], [[], [], []]
+        for counts in plan:
+            out = runner.step([StepEntry(slots[i], seqs[i][at[i]:at[i] + n], list(range(n))) for i, n in counts.items()])
+            lo = 0
+            for i, n in counts.items():
+                got[i].append(out[lo:lo + n].clone())
+                lo, at[i] = lo + n, at[i] + n
+        while min(len(seqs[i]) - at[i] for i in range(3)) > 0:
+            out = runner.step([StepEntry(slots[i], [seqs[i][at[i]]], [0]) for i in range(3)])
+            for i in range(3):
+                got[i].append(out[i:i + 1].clone())
+                at[i] += 1
+        outs[graphs] = [torch.cat(g).cpu() for g in got]
+        if graphs:
+            assert len(runner._mixed_graphs) == 1 and runner.graph_replays >= 3 + 5
+    for i in range(3):
+        assert torch.equal(outs[True][i], outs[False][i])
+        helpers.assert_close(outs[True][i], want[i][:at[i]], "bfloat16", f"graph-safe toy request {i}")
+    # the mixer that reads host-side lists is not captured
+    plain_cfg = ToyConfig(architecture="ToyDecayForCausalLM", hidden_size=hidden, vocab_size=200, decay=0.6)
+    model = build_model(plain_cfg, Runtime("bfloat16", device=DEV))
+    assert not getattr(model.blocks[0].mixer, "graph_safe", False)
