@@ -168,6 +168,7 @@ struct Args {
     int n_requests, table_stride, page_tokens, n_heads, n_kv, window;
     float scale_log2;
     int plane_rows;            // rows of the [pages * n_kv * page_tokens, 128] view of a cache plane
+    int block_rows;            // query rows a block takes: 256 (both tiles) or 128 (the second tile stays empty)
 };
 
 // What a query tile of the block covers: its rows, positions and the key tiles it needs.
@@ -185,7 +186,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // Blocks start in the order of blockIdx.y; the last rows of a request see the most keys, so
     // the last 256 rows of every request come first, then the 256 before them, and so on: the
     // longest blocks start first and the short ones fill the gaps at the end.
-    constexpr int BLOCK_ROWS = QT * BM;
+    // A block takes 256 rows (two tiles taking turns between the exponential unit and the tensor
+    // core: by far the better rate a key tile) or, when a launch is so small that most SMs would
+    // have no block, 128 (twice as many blocks, half as long).
+    const int BLOCK_ROWS = p.block_rows;
     int req = -1, row0 = 0, rows = 0;
     {
         int b = (int)blockIdx.y;
@@ -268,8 +272,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tma_prefetch_descriptor(&map_v);
             // Q: rows [row0, row0 + 256) of the [T, heads * 128] view, columns of this head; rows
             // past the step's end read as zero
-            mbar_expect_tx(q_full, QT * TILE_BYTES);
-            for (int g = 0; g < QT; ++g) {
+            const int q_tiles = qt[1].rows > 0 ? 2 : 1;
+            mbar_expect_tx(q_full, q_tiles * TILE_BYTES);
+            for (int g = 0; g < q_tiles; ++g) {
                 tma_load_2d(smem + SMEM_Q + g * TILE_BYTES, &map_q, q_full, h * HD, row0 + g * BM);
                 tma_load_2d(smem + SMEM_Q + g * TILE_BYTES + HALF_BYTES, &map_q, q_full, h * HD + 64, row0 + g * BM);
             }
@@ -517,11 +522,12 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols
 }  // namespace
 
 // q, out: [T, n_heads, 128] bf16; planes [pages, n_kv, 16, 128] bf16; req_start [n_requests + 1],
-// req_prior [n_requests].  Head size 128 and 16-token pages only; refuses anything else.
+// req_prior [n_requests].  Head size 128 and 16-token pages only; refuses anything else.  force_block_rows: 128 or 256
+// query rows a block, or 0 to let the launch's size decide.
 CJ_EXPORT int cj_prefill_attention_tc(const void* q, void* out, const void* kplane, const void* vplane, int n_pages,
                                       const int* req_start, const int* req_prior, int n_requests, int total_rows,
                                       const int* table, int table_stride, int page_tokens, int n_heads, int n_kv,
-                                      int hd, int window, float scale, cudaStream_t stream) {
+                                      int hd, int window, float scale, int force_block_rows, cudaStream_t stream) {
     if (total_rows <= 0 || n_requests <= 0) return 0;
     if (!q || !out || !kplane || !vplane || !req_start || !req_prior || !table) return CJ_ERR_ARG;
     if (hd != HD || page_tokens != 16) return CJ_ERR_SIZE;
@@ -539,11 +545,26 @@ CJ_EXPORT int cj_prefill_attention_tc(const void* q, void* out, const void* kpla
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
+    // 256 rows a block (two tiles taking turns: measured 1.9 times the rate of one tile a block)
+    // unless that leaves more than half of the SMs without a block: then 128 (measured: one prompt
+    // of 1,024 tokens 22.2 -> 19.5 us, of 512 tokens 14.9 -> 12.5 us; of 2,048 tokens 38.1 -> 40.1 us,
+    // so that one stays at 256)
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            sm_count = 1;
+    }
+    int block_rows = force_block_rows;
+    if (block_rows != 128 && block_rows != 256) {
+        const long long blocks_256 = ((total_rows + 255) / 256 + n_requests - 1) * n_heads;      // at most
+        block_rows = 2 * blocks_256 <= sm_count ? 128 : 256;
+    }
     Args a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, req_start, req_prior, table, n_requests, table_stride, page_tokens,
-           n_heads, n_kv, window, scale * 1.4426950408889634f, (int)plane_rows};
+           n_heads, n_kv, window, scale * 1.4426950408889634f, (int)plane_rows, block_rows};
     // heads run fastest, so that blocks start in the order of their length (the last rows of a
     // request see the most keys) and the heads of one group read the same keys one after another
-    const long long row_blocks = (total_rows + QT * BM - 1) / (QT * BM) + n_requests;
+    const long long row_blocks = (total_rows + block_rows - 1) / block_rows + n_requests;
     if (row_blocks > 65535) return CJ_ERR_SIZE;
     dim3 grid(n_heads, (unsigned)row_blocks);
     cj::launch(prefill_attention_tc_kernel, dim3(grid), dim3(THREADS), SMEM_TOTAL, stream, mq, mk, mv, a);
