@@ -43,7 +43,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_prefill_tc": "attention_prefill_tc.cu",
     "random_fill": "random_fill.cu",
 }
-HEADERS = ["common.cuh", "tc_common.cuh", "rope_epilogue.cuh", "sampling_static.h"]
+HEADERS = ["common.cuh", "tc_common.cuh", "sampling_static.h"]
 
 # host-only libraries (no CUDA): compiled with the host C++ compiler, so that the books of the
 # cache manager also load on a machine without nvcc or a GPU

@@ -29,7 +29,6 @@
 // maps, io/WmmaKernel.cajeta (q4kWmmaIdMwKernel), and the dense projection GEMMs of
 // model/Linear.cajeta; both wmma-class there.
 #include "common.cuh"
-#include "rope_epilogue.cuh"
 #include "tc_common.cuh"
 
 using namespace tc;
@@ -40,7 +39,7 @@ constexpr int BK = 64;             // K elements per stage: one 128-byte swizzle
 constexpr int UMMA_K = 16;         // K of one tcgen05.mma of kind::f16
 constexpr int THREADS = 192;
 
-enum Epilogue { EPI_STORE_F32 = 0, EPI_ACC_F32 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_BF16 = 3, EPI_ROPE_CACHE = 4 };
+enum Epilogue { EPI_STORE_F32 = 0, EPI_ACC_F32 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_BF16 = 3 };
 
 struct Args {
     int tokens;                 // rows of X
@@ -54,7 +53,6 @@ struct Args {
     int k_splits;               // > 1: each split stores its partial at out + split * split_stride
     long long split_stride;
     int offsets_settled;        // the groups' offsets were complete before the kernel before this one began
-    cj::RopeArgs rope;          // EPI_ROPE_CACHE: where the rotated q, k and the raw v go
 };
 
 template <int N_MMA, bool SWAP, bool DUAL, int STAGES>
@@ -325,76 +323,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     // the result is rounded to bfloat16 (8 bits): the fast exponential and division (2 ulp of float32) do not show
                     if (EPI == EPI_SWIGLU_BF16) v[j] = __fdividef(v[j], 1.0f + __expf(-v[j])) * __uint_as_float(v1[j]);
                 }
-                if (EPI == EPI_ROPE_CACHE && !SWAP) {
-                    // this thread owns one token row and 16 consecutive features of it: eight rotation
-                    // pairs side by side (see rope_epilogue.cuh)
-                    const int token = c.tok0 + r, feat = c.feat0 + c0;
-                    if (token >= c.tok_end || feat >= p.features) continue;
-                    if (add_bias) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) if (feat + j < p.features) v[j] += p.bias[feat + j];
-                    }
-                    const cj::RopeFeature first = cj::rope_feature(p.rope, feat, p.features);
-                    const bool one_head = (feat % p.rope.hd) + 16 <= p.rope.hd && feat + 16 <= p.features;
-                    if (one_head && (first.pair >= 0 ? (p.rope.rot == p.rope.hd && (p.rope.hd & 15) == 0) : (p.rope.hd & 7) == 0)) {
-                        // 16 features of one head: 8 low dims and 8 high dims (or 16 dims that are not
-                        // rotated), each run 16-byte aligned: whole 16-byte stores
-                        __nv_bfloat16* dst;
-                        if (first.region == 0) dst = p.rope.q_out + (size_t)token * p.rope.q_dim + first.head * p.rope.hd;
-                        else {
-                            const long long base = p.rope.kv_base[token];
-                            if (base < 0) continue;
-                            dst = (first.region == 1 ? p.rope.kplane : p.rope.vplane) + base + (long long)first.head * p.rope.head_stride;
-                        }
-                        uint4 lo, hi;
-                        __nv_bfloat162* l2 = (__nv_bfloat162*)&lo;
-                        __nv_bfloat162* h2 = (__nv_bfloat162*)&hi;
-                        if (first.pair >= 0) {
-                            const float2* cs = p.rope.cos_sin + (size_t)token * (p.rope.rot >> 1) + first.pair;
-                            float a[8], b[8];
-#pragma unroll
-                            for (int q = 0; q < 8; ++q) {
-                                const float2 t = cs[q];
-                                a[q] = fmaf(-v[2 * q + 1], t.y, v[2 * q] * t.x);
-                                b[q] = fmaf(v[2 * q], t.y, v[2 * q + 1] * t.x);
-                            }
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                l2[q] = __floats2bfloat162_rn(a[2 * q], a[2 * q + 1]);
-                                h2[q] = __floats2bfloat162_rn(b[2 * q], b[2 * q + 1]);
-                            }
-                            *(uint4*)(dst + first.dim) = lo;
-                            *(uint4*)(dst + first.dim + (p.rope.rot >> 1)) = hi;
-                        } else {
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                l2[q] = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
-                                h2[q] = __floats2bfloat162_rn(v[8 + 2 * q], v[8 + 2 * q + 1]);
-                            }
-                            *(uint4*)(dst + first.dim) = lo;
-                            *(uint4*)(dst + first.dim + 8) = hi;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const cj::RopeFeature ft = cj::rope_feature(p.rope, feat + j, p.features);
-                            if (ft.region >= 0) cj::rope_store(p.rope, ft, token, v[j], v[j ^ 1]);
-                        }
-                    }
-                } else if (EPI == EPI_ROPE_CACHE) {
-                    // this thread owns one feature; its rotation partner is the neighbouring lane.  Every
-                    // lane takes part in the exchange, also one past the last feature.
-                    const int feat = c.feat0 + r;
-                    const cj::RopeFeature ft = cj::rope_feature(p.rope, feat, p.features);
-                    const float b = (add_bias && ft.region >= 0) ? p.bias[feat] : 0.0f;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float own = v[j] + b;
-                        const float partner = __shfl_xor_sync(0xffffffffu, own, 1);
-                        const int token = c.tok0 + c0 + j;
-                        if (ft.region >= 0 && token < c.tok_end) cj::rope_store(p.rope, ft, token, own, partner);
-                    }
-                } else if (!SWAP) {
+                if (!SWAP) {
                     // this thread owns one token row and 16 consecutive features of it
                     const int token = c.tok0 + r, feat = c.feat0 + c0;
                     if (token >= c.tok_end || feat >= p.features) continue;
@@ -578,46 +507,6 @@ CJ_EXPORT int cj_gemm_tc(const void* x, long long ldx, const void* w, const void
     }
 #undef CASE
     return CJ_ERR_ARG;
-}
-
-// The q/k/v projection with the rotation and the cache write in its epilogue (rope_epilogue.cuh):
-// w is the stacked [q_dim + 2 kv_dim (or q_dim alone when write_kv is 0), K] matrix with the rows of
-// every q and k head laid out pair by pair, bias likewise.  cos_sin: float2 [tokens, rot / 2];
-// kv_base: [tokens] element offsets into the planes, -1 where a token has no page; q_out: bf16
-// [tokens, q_dim]; planes: bf16 [pages, n_kv, page_tokens, hd].  swap / n_mma as in cj_gemm_tc.
-CJ_EXPORT int cj_gemm_tc_rope(const void* x, long long ldx, const void* w, const float* bias, int tokens, int K, int swap,
-                              int n_mma, void* q_out, void* kplane, void* vplane, const void* cos_sin,
-                              const long long* kv_base, int q_dim, int kv_dim, int hd, int rot, int page_tokens,
-                              int write_kv, cudaStream_t stream) {
-    if (tokens <= 0) return 0;
-    if (!x || !w || !q_out || !cos_sin || K <= 0) return CJ_ERR_ARG;
-    if (write_kv && (!kplane || !vplane || !kv_base)) return CJ_ERR_ARG;
-    if (K % 8 != 0 || ldx % 8 != 0) return CJ_ERR_ALIGN;
-    if (((uintptr_t)x | (uintptr_t)w) & 15) return CJ_ERR_ALIGN;
-    if (hd <= 0 || rot < 0 || rot > hd || (rot & 1) || q_dim % hd != 0 || kv_dim % hd != 0 || page_tokens <= 0) return CJ_ERR_SIZE;
-    if (((uintptr_t)q_out | (uintptr_t)kplane | (uintptr_t)vplane) & 15) return CJ_ERR_ALIGN;
-    const int features = q_dim + (write_kv ? 2 * kv_dim : 0);
-    int x_box = swap ? n_mma : 128, w_box = swap ? 128 : n_mma;
-    CUtensorMap mx, mw;
-    if (!make_map_bf16(&mx, x, tokens, K, ldx, x_box)) return CJ_ERR_ARG;
-    if (!make_map_bf16(&mw, w, features, K, K, w_box)) return CJ_ERR_ARG;
-    Args a{tokens, features, K, q_out, 0, bias, nullptr, 0, 1, 0, 0,
-           cj::RopeArgs{(__nv_bfloat16*)q_out, (__nv_bfloat16*)kplane, (__nv_bfloat16*)vplane, (const float2*)cos_sin, kv_base,
-                        q_dim, kv_dim, hd, rot, page_tokens * hd, write_kv}};
-    if (swap) {
-        switch (n_mma) {
-            case 16: return launch_auto<16, true, false, EPI_ROPE_CACHE>(mx, mw, mw, a, stream);
-            case 32: return launch_auto<32, true, false, EPI_ROPE_CACHE>(mx, mw, mw, a, stream);
-            case 64: return launch_auto<64, true, false, EPI_ROPE_CACHE>(mx, mw, mw, a, stream);
-            case 128: return launch_auto<128, true, false, EPI_ROPE_CACHE>(mx, mw, mw, a, stream);
-        }
-    } else {
-        switch (n_mma) {
-            case 128: return launch_auto<128, false, false, EPI_ROPE_CACHE>(mx, mw, mw, a, stream);
-            case 256: return launch_auto<256, false, false, EPI_ROPE_CACHE>(mx, mw, mw, a, stream);
-        }
-    }
-    return CJ_ERR_SIZE;
 }
 
 // 0, or the code of the first bounded wait that ran out (1 producer, 2 product issue,

@@ -32,7 +32,6 @@
 // reference counterpart: the same per-expert and dense projection GEMMs as the one-SM kernel
 // (io/WmmaKernel.cajeta, model/Linear.cajeta).
 #include "common.cuh"
-#include "rope_epilogue.cuh"
 #include "tc_common.cuh"
 
 using namespace tc;
@@ -46,7 +45,7 @@ constexpr int FEAT_TILE = 256;      // feature rows a pair of blocks covers
 constexpr int MAX_GROUPS = 1024;
 constexpr int MAX_ACC_STAGES = 2;
 
-enum Epilogue { EPI_STORE_F32 = 0, EPI_ACC_F32 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_BF16 = 3, EPI_ROPE_CACHE = 4 };
+enum Epilogue { EPI_STORE_F32 = 0, EPI_ACC_F32 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_BF16 = 3 };
 
 struct Args {
     int tokens, features, K;
@@ -55,7 +54,6 @@ struct Args {
     const float* bias;
     const int* group_offsets;
     int groups;
-    cj::RopeArgs rope;          // EPI_ROPE_CACHE: where the rotated q, k and the raw v go
 };
 
 template <int N_TOK, int STAGES>
@@ -242,8 +240,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 const int feat = c.feat0 + (int)rank * 128 + r;
                 const bool live = feat < p.features;
                 const float b = (p.bias != nullptr && live) ? p.bias[feat] : 0.0f;
-                cj::RopeFeature ft;
-                if (EPI == EPI_ROPE_CACHE) ft = cj::rope_feature(p.rope, feat, p.features);
 #pragma unroll 1
                 for (int c0 = 0; c0 < N_TOK; c0 += 32) {
                     if (c0 >= n_cols) break;
@@ -251,17 +247,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     tmem_ld16(lane_base + c0, *(uint32_t(*)[16])&v[0]);
                     tmem_ld16(lane_base + c0 + 16, *(uint32_t(*)[16])&v[16]);
                     tmem_ld_wait();
-                    if (EPI == EPI_ROPE_CACHE) {
-                        // this thread owns one feature; its rotation partner is the neighbouring lane (the
-                        // weight rows are laid out pair by pair).  Every lane takes part in the exchange.
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const float own = __uint_as_float(v[j]) + b;
-                            const float partner = __shfl_xor_sync(0xffffffffu, own, 1);
-                            if (ft.region >= 0 && c0 + j < n_cols) cj::rope_store(p.rope, ft, c.tok0 + c0 + j, own, partner);
-                        }
-                        continue;
-                    }
                     if (!live) continue;
                     // column j is token tok0 + c0 + j: a warp writes 32 consecutive features of a token
                     const long long o0 = (long long)(c.tok0 + c0) * p.ldo + feat;
@@ -592,29 +577,6 @@ CJ_EXPORT int cj_gemm_tc2(const void* x, long long ldx, const void* w, const voi
     }
 #undef CASE
     return CJ_ERR_ARG;
-}
-
-// The q/k/v projection with the rotation and the cache write in its epilogue, on pairs of SMs
-// (arguments as cj_gemm_tc_rope; n_tok 128 or 256).
-CJ_EXPORT int cj_gemm_tc2_rope(const void* x, long long ldx, const void* w, const float* bias, int tokens, int K, int n_tok,
-                               void* q_out, void* kplane, void* vplane, const void* cos_sin, const long long* kv_base,
-                               int q_dim, int kv_dim, int hd, int rot, int page_tokens, int write_kv, cudaStream_t stream) {
-    if (tokens <= 0) return 0;
-    if (!x || !w || !q_out || !cos_sin || K <= 0) return CJ_ERR_ARG;
-    if (write_kv && (!kplane || !vplane || !kv_base)) return CJ_ERR_ARG;
-    if (K % 8 != 0 || ldx % 8 != 0) return CJ_ERR_ALIGN;
-    if (((uintptr_t)x | (uintptr_t)w) & 15) return CJ_ERR_ALIGN;
-    if (hd <= 0 || rot < 0 || rot > hd || (rot & 1) || q_dim % hd != 0 || kv_dim % hd != 0 || page_tokens <= 0) return CJ_ERR_SIZE;
-    if (n_tok != 128 && n_tok != 256) return CJ_ERR_SIZE;
-    const int features = q_dim + (write_kv ? 2 * kv_dim : 0);
-    CUtensorMap mx, mw;
-    if (!make_map_bf16(&mw, w, features, K, K, 128)) return CJ_ERR_ARG;
-    if (!make_map_bf16(&mx, x, tokens, K, ldx, n_tok / 2)) return CJ_ERR_ARG;
-    Args a{tokens, features, K, q_out, 0, bias, nullptr, 0,
-           cj::RopeArgs{(__nv_bfloat16*)q_out, (__nv_bfloat16*)kplane, (__nv_bfloat16*)vplane, (const float2*)cos_sin, kv_base,
-                        q_dim, kv_dim, hd, rot, page_tokens * hd, write_kv}};
-    if (n_tok == 256) return launch<256, EPI_ROPE_CACHE>(mx, mw, a, stream);
-    return launch<128, EPI_ROPE_CACHE>(mx, mw, a, stream);
 }
 
 CJ_EXPORT int cj_gemm_tc2_error() {

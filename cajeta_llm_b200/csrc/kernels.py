@@ -436,62 +436,6 @@ def gemm_tc2(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int,
     _check(st, "gemm_tc2")
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = (cos, sin)(float32(positions[t]) * inv_freq[i]); out float32 [T, half, 2]."""
-    _need(positions, "positions", torch.int32), _need(inv_freq, "inv_freq", torch.float32), _need(out, "out", torch.float32)
-    T, half = positions.numel(), inv_freq.numel()
-    if tuple(out.shape) != (T, half, 2):
-        raise KernelError(f"rope_table: out {tuple(out.shape)} is not [{T}, {half}, 2]")
-    st = library("rowwise").cj_rope_table(_ptr(positions), _ptr(inv_freq), _i(T), _i(half), _ptr(out), _stream())
-    _check(st, "rope_table")
-
-
-def kv_rows(positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int, n_kv: int,
-            head_dim: int, out: torch.Tensor) -> None:
-    """out[t] = element offset, in a cache plane [pages, n_kv, page_tokens, head_dim], of (the page of row t's
-    position, kv head 0, the position's slot, dim 0); -1 where the row's request has no page there.  int64 [T]."""
-    _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
-    _need(out, "out", torch.int64)
-    T = positions.numel()
-    st = library("rowwise").cj_kv_rows(_ptr(positions), _ptr(row_req), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(n_kv),
-                                       _i(head_dim), _i(T), _ptr(out), _stream())
-    _check(st, "kv_rows")
-
-
-def gemm_rope_cache(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
-                    k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], cos_sin: torch.Tensor,
-                    kv_base: Optional[torch.Tensor], q_dim: int, kv_dim: int, head_dim: int, rotary_dim: int, page_tokens: int,
-                    swap: bool, tile: int, pair: bool = False) -> None:
-    """The stacked q | k | v projection (``w`` [q_dim + 2 kv_dim, K], or [q_dim, K] when no planes are given;
-    the rows of every q and k head laid out rotation pair by rotation pair) with the rotation and the cache
-    write in the product's epilogue: q goes to ``q_out`` (bfloat16 [T, q_dim]), the rotated k and the raw v
-    into the planes at ``kv_base`` (see ``kv_rows``).  ``swap`` / ``tile`` as ``gemm_tc``'s ``swap`` / ``n_mma``;
-    ``pair``: on pairs of SMs (``tile`` 128 or 256 tokens)."""
-    _need(x, "x", torch.bfloat16), _need(w, "w", torch.bfloat16), _need(q_out, "q_out", torch.bfloat16)
-    _need(cos_sin, "cos_sin", torch.float32)
-    T, K = x.shape
-    write = k_plane is not None
-    if write:
-        _need(k_plane, "k_plane", torch.bfloat16), _need(v_plane, "v_plane", torch.bfloat16), _need(kv_base, "kv_base", torch.int64)
-    if w.shape[0] != q_dim + (2 * kv_dim if write else 0) or w.shape[1] != K:
-        raise KernelError(f"gemm_rope_cache: w {tuple(w.shape)} does not fit q {q_dim}, kv {kv_dim}, K {K}")
-    if bias is not None:
-        _need(bias, "bias", torch.float32)
-    if cos_sin.numel() != T * rotary_dim:
-        raise KernelError(f"gemm_rope_cache: cos_sin {tuple(cos_sin.shape)} is not [{T}, {rotary_dim // 2}, 2]")
-    if pair:
-        st = library("gemm_tc2").cj_gemm_tc2_rope(
-            _ptr(x), _ll(x.stride(0)), _ptr(w), _ptr(bias), _i(T), _i(K), _i(tile), _ptr(q_out), _ptr(k_plane), _ptr(v_plane),
-            _ptr(cos_sin), _ptr(kv_base), _i(q_dim), _i(kv_dim), _i(head_dim), _i(rotary_dim), _i(page_tokens),
-            _i(1 if write else 0), _stream())
-    else:
-        st = library("gemm_tc").cj_gemm_tc_rope(
-            _ptr(x), _ll(x.stride(0)), _ptr(w), _ptr(bias), _i(T), _i(K), _i(1 if swap else 0), _i(tile), _ptr(q_out),
-            _ptr(k_plane), _ptr(v_plane), _ptr(cos_sin), _ptr(kv_base), _i(q_dim), _i(kv_dim), _i(head_dim), _i(rotary_dim),
-            _i(page_tokens), _i(1 if write else 0), _stream())
-    _check(st, "gemm_rope_cache")
-
-
 def gemm_tc_error() -> int:
     """0, or the code of a bounded wait inside a tensor-core kernel that ran out of time."""
     return int(library("gemm_tc").cj_gemm_tc_error())

@@ -275,59 +275,6 @@ CJ_EXPORT int cj_rmsnorm(float* x, const float* w, float eps, int rows, int H, v
 }
 
 // ---------------------------------------------------------------------------------
-// What the q/k/v projection needs to rotate and store in its own epilogue (rope_epilogue.cuh),
-// worked out once per step instead of once per layer: cos and sin of every row's angles,
-// out[t][i] = (cos, sin)(float(p_t) * inv[i]) - the same float32 angle and functions as the
-// fused kernel below - and, per cache group, where each row's position lies in the planes:
-// the element offset of (page, kv head 0, slot, dim 0), or -1 without a page.
-// Both read only the step's positions and tables (written before the step's first kernel).
-// ---------------------------------------------------------------------------------
-__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int T, int half,
-                                  float2* __restrict__ out) {
-    cj::release_successor();
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const bool in = i < (long long)T * half;
-    float2 v = make_float2(1.0f, 0.0f);
-    if (in) {
-        const float ang = (float)__ldcg(positions + i / half) * inv_freq[i % half];
-        v = make_float2(cosf(ang), sinf(ang));
-    }
-    cj::after_predecessor();           // an earlier kernel may still be reading the table of the step before
-    if (in) out[i] = v;
-}
-
-__global__ void kv_rows_kernel(const int* __restrict__ positions, const int* __restrict__ row_req, const int* __restrict__ table,
-                               int table_stride, int page_tokens, int n_kv, int hd, int T, long long* __restrict__ out) {
-    cj::release_successor();
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
-    long long base = -1;
-    if (t < T) {
-        const int pos = __ldcg(positions + t);
-        const int page = __ldcg(table + (size_t)__ldcg(row_req + t) * table_stride + pos / page_tokens);
-        if (page >= 0) base = (((long long)page * n_kv) * page_tokens + pos % page_tokens) * hd;
-    }
-    cj::after_predecessor();
-    if (t < T) out[t] = base;
-}
-
-CJ_EXPORT int cj_rope_table(const int* positions, const float* inv_freq, int T, int half, void* out, cudaStream_t stream) {
-    if (T <= 0 || half <= 0) return 0;
-    if (!positions || !inv_freq || !out) return CJ_ERR_ARG;
-    const long long n = (long long)T * half;
-    cj::launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, positions, inv_freq, T, half, (float2*)out);
-    return launch_status();
-}
-
-CJ_EXPORT int cj_kv_rows(const int* positions, const int* row_req, const int* table, int table_stride, int page_tokens,
-                         int n_kv, int hd, int T, long long* out, cudaStream_t stream) {
-    if (T <= 0) return 0;
-    if (!positions || !row_req || !table || !out || page_tokens <= 0) return CJ_ERR_ARG;
-    cj::launch(kv_rows_kernel, dim3((unsigned)((T + 127) / 128)), dim3(128), 0, stream, positions, row_req, table, table_stride,
-               page_tokens, n_kv, hd, T, out);
-    return launch_status();
-}
-
-// ---------------------------------------------------------------------------------
 // Rotary encoding of q and k at each row's absolute position, fused with the write of
 // the rotated k and the raw v into the cache pages of the row's request.
 // Half-split pairs (d, d + rot/2): ang = float(p) * inv[d]; a' = a cos - b sin;

@@ -81,7 +81,6 @@ class StepContext:
     decode_scratch: Optional[object] = None    # scratch of the split-KV decode attention for this step (None: the runtime's)
     routing_pin: Optional[Dict[str, torch.Tensor]] = None     # a routed feed-forward's prefix -> int32 [rows, k]: experts given, not chosen
     routing_dump: Optional[Dict[str, tuple]] = None           # filled by routed feed-forwards: prefix -> (experts [rows, k], margins [rows])
-    scratch: Dict = field(default_factory=dict)                # what parts work out once a step and share (by their own keys)
 
 
 @dataclass
@@ -239,7 +238,6 @@ class ModelRunner:
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
-            ctx.scratch = {}                                 # what the parts worked out for the run above is not the graph's
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 static_logits = self._forward(ctx)
             while len(self._mixed_graphs) >= MIXED_GRAPHS_MAX:
@@ -324,9 +322,6 @@ class ModelRunner:
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
-            # what the parts worked out once for the run above (tables of the step) lives outside the
-            # graph's pool and was computed outside the graph: the captured run works it out again
-            ctx.scratch = {}
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 static_logits = self._forward(ctx)
             self._graphs[key] = _CapturedStep(graph, meta, static_logits, K.launches - before, ctx.decode_scratch)

@@ -127,45 +127,6 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
                   offsets_settled=offsets_settled)
 
 
-def rope_pairs_order(heads: int, kv_heads: int, head_dim: int, rotary_dim: int) -> torch.Tensor:
-    """Row order of the stacked q | k | v projection for :func:`project_rope_cache`: within every q
-    and k head the two halves of each rotation pair side by side (0, rot/2, 1, rot/2 + 1, ...), the
-    dims past the rotary part after them, v rows as they are.  ``order[new_row] = old_row``."""
-    half = rotary_dim // 2
-    in_head = [d + h * half for d in range(half) for h in (0, 1)] + list(range(rotary_dim, head_dim))
-    rows = [hd * head_dim + d for hd in range(heads + kv_heads) for d in in_head]
-    rows += list(range((heads + kv_heads) * head_dim, (heads + 2 * kv_heads) * head_dim))
-    return torch.tensor(rows, dtype=torch.long)
-
-
-def rope_cache_ok(runtime, hidden: int, features: int) -> bool:
-    """Whether a q/k/v projection of these sizes runs on the tensor cores for EVERY number of rows (the
-    choice is made once, at load, because the weight rows are laid out for it)."""
-    return bool(runtime.fast_kernels and hidden >= MIN_K and hidden % 8 == 0 and features >= MIN_FEATURES)
-
-
-def project_rope_cache(runtime, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
-                       k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], cos_sin: torch.Tensor,
-                       kv_base: Optional[torch.Tensor], q_dim: int, kv_dim: int, head_dim: int, rotary_dim: int,
-                       page_tokens: int) -> None:
-    """The q/k/v projection whose epilogue rotates q and k and writes k and v into the cache pages
-    (``csrc/rope_epilogue.cuh``): the same choice of product as :func:`project` makes for a dense
-    weight - weights on the rows for few tokens, pairs of SMs for many."""
-    rows = x.shape[0]
-    tile = _token_tile(rows)
-    if tile:
-        K.gemm_rope_cache(x, w, bias, q_out, k_plane, v_plane, cos_sin, kv_base, q_dim, kv_dim, head_dim, rotary_dim,
-                          page_tokens, True, tile)
-        return
-    pair_tile = _pair_tile(runtime, rows, w, False, False)
-    if pair_tile:
-        K.gemm_rope_cache(x, w, bias, q_out, k_plane, v_plane, cos_sin, kv_base, q_dim, kv_dim, head_dim, rotary_dim,
-                          page_tokens, False, pair_tile, pair=True)
-        return
-    K.gemm_rope_cache(x, w, bias, q_out, k_plane, v_plane, cos_sin, kv_base, q_dim, kv_dim, head_dim, rotary_dim,
-                      page_tokens, False, 256 if w.shape[0] >= 512 else 128)
-
-
 def project_split(runtime, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """For a few rows and a weight with few output features: the product cut along K into
     enough pieces to occupy the machine.  Returns the partial sums [S, tokens, features]

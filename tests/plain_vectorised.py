@@ -169,17 +169,9 @@ def engine_views(model) -> Callable[[str], torch.Tensor]:
             views[norm.name("weight")] = (lambda n=norm: n.weight)
         a = block.mixer
         bounds = {"q": (0, a.q_dim), "k": (a.q_dim, a.q_dim + a.kv_dim), "v": (a.q_dim + a.kv_dim, a.q_dim + 2 * a.kv_dim)}
-        # the engine may keep the rows of q and k heads in another order (rotation pairs side by side):
-        # ``qkv_row_order[new] = old``; the checkpoint's order is restored here (a copy then, not a view)
-        order = getattr(a, "qkv_row_order", None)
-        back = None if order is None else torch.argsort(order)
-
-        def rows(t, lo, hi, back=back):
-            return t[lo:hi] if back is None else t[back.to(t.device)[lo:hi]]
-
         for n, (lo, hi) in bounds.items():
-            views[a.name(f"{n}_proj.weight")] = (lambda a=a, lo=lo, hi=hi: rows(a.w_qkv, lo, hi))
-            views[a.name(f"{n}_proj.bias")] = (lambda a=a, lo=lo, hi=hi: rows(a.b_qkv, lo, hi))
+            views[a.name(f"{n}_proj.weight")] = (lambda a=a, lo=lo, hi=hi: a.w_qkv[lo:hi])
+            views[a.name(f"{n}_proj.bias")] = (lambda a=a, lo=lo, hi=hi: a.b_qkv[lo:hi])
         views[a.name("o_proj.weight")] = (lambda a=a: a.w_o)
         f = block.feed_forward
         if hasattr(f, "num_experts"):

@@ -281,59 +281,3 @@ def test_language_model_head_at_the_real_vocabulary(K, rows):
     print(f"\nhead {rows} rows: worst |diff| {worst:.3e}")
 
 
-
-@pytest.mark.parametrize("heads,n_kv,hd,rot", [(4, 2, 128, 128), (6, 3, 64, 64), (4, 1, 64, 32), (5, 2, 80, 80), (3, 3, 48, 24)])
-@pytest.mark.parametrize("T", [1, 8, 40, 100, 200, 300, 600, 1100])
-def test_projection_that_rotates_and_writes_the_cache(K, heads, n_kv, hd, rot, T):
-    """The q/k/v product whose epilogue rotates q and k and puts k and v into the cache pages, in
-    all three products it can run on (weights on the rows for few tokens, tokens on the rows, pairs
-    of SMs for many), against the plain rotation of a float64 product: head sizes 128 and 64, a
-    rotary part smaller than the head, head sizes that are no multiple of 16; rows of several
-    requests at scattered positions and pages; nothing else in the planes is touched."""
-    from cajeta_llm_b200.parts.base import Runtime
-    from cajeta_llm_b200.parts.linear import project_rope_cache, rope_pairs_order
-    Kd, page = 256, 16
-    q_dim, kv_dim = heads * hd, n_kv * hd
-    g = torch.Generator().manual_seed(700 + T + hd)
-    x = rnd(T, Kd, seed=701 + T)
-    w = rnd(q_dim + 2 * kv_dim, Kd, seed=702, scale=0.1)
-    bias = torch.randn(q_dim + 2 * kv_dim, generator=g).to(DEV)
-    # three requests share the rows; each row at its own position, pages scrambled
-    n_req, width = 3, 80
-    req = torch.randint(0, n_req, (T,), generator=g)
-    pos = torch.randperm(width * page, generator=g)[:T].to(torch.int32)          # distinct positions: no two rows share a slot
-    table = torch.randperm(n_req * width, generator=g).to(torch.int32).view(n_req, width)
-    inv = P.inv_freq(rot, 10000.0, torch.float32)
-    positions, row_req, table_d = pos.to(DEV), req.to(torch.int32).to(DEV), table.to(DEV)
-    cos_sin = torch.empty(T, rot // 2, 2, device=DEV)
-    K.rope_table(positions, inv.to(DEV), cos_sin)
-    ang = pos.float()[:, None] * inv[None, :]
-    assert torch.allclose(cos_sin.cpu(), torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1), atol=1e-6, rtol=0)
-    kv_base = torch.empty(T, dtype=torch.int64, device=DEV)
-    K.kv_rows(positions, row_req, table_d, page, n_kv, hd, kv_base)
-    want_base = (table[req, (pos // page).long()].long() * n_kv * page + (pos % page).long()) * hd
-    assert torch.equal(kv_base.cpu(), want_base)
-    order = rope_pairs_order(heads, n_kv, hd, rot).to(DEV)
-    kp = torch.zeros(n_req * width, n_kv, page, hd, dtype=torch.bfloat16, device=DEV)
-    vp = torch.zeros_like(kp)
-    q_out = torch.full((T, q_dim), 7.0, dtype=torch.bfloat16, device=DEV)
-    project_rope_cache(Runtime("bfloat16", device=DEV), x, w[order].contiguous(), bias[order].contiguous(), q_out, kp, vp, cos_sin,
-                       kv_base, q_dim, kv_dim, hd, rot, page)
-    qkv = x.double().cpu() @ w.double().cpu().t() + bias.double().cpu()
-
-    def rotated(t, n):
-        t = t.reshape(T, n, hd)
-        return torch.cat([P.rope(t[..., :rot], pos.long(), inv.double()), t[..., rot:]], dim=-1)
-
-    want_q, want_k = rotated(qkv[:, :q_dim], heads), rotated(qkv[:, q_dim:q_dim + kv_dim], n_kv)
-    want_v = qkv[:, q_dim + kv_dim:].reshape(T, n_kv, hd)
-    close(q_out.view(T, heads, hd).cpu(), want_q, atol=3e-2, rtol=2e-2)
-    pages, slots = table[req, (pos // page).long()].long(), (pos % page).long()
-    close(kp[pages.to(DEV), :, slots.to(DEV)].cpu(), want_k, atol=3e-2, rtol=2e-2)
-    close(vp[pages.to(DEV), :, slots.to(DEV)].cpu(), want_v, atol=3e-2, rtol=2e-2)
-    assert int((kp != 0).any(dim=-1).sum()) <= T * n_kv and int((vp != 0).any(dim=-1).sum()) <= T * n_kv
-    # a projection that owns no cache (it reads another entry's): q alone
-    q_only = torch.empty_like(q_out)
-    project_rope_cache(Runtime("bfloat16", device=DEV), x, w[order][:q_dim].contiguous(), bias[order][:q_dim].contiguous(), q_only,
-                       None, None, cos_sin, None, q_dim, kv_dim, hd, rot, page)
-    assert torch.equal(q_only, q_out)
