@@ -172,6 +172,59 @@ def model_numbers(cfg, n_layers):
                 attention_flops=lambda T: 4 * heads * hd * T * (T + 1) // 2)
 
 
+def timeline(runner, batch, prompts, rng, vocab, n_layers) -> int:
+    """One replayed decode step of ``batch`` requests under the profiler: launches overlap (a kernel's
+    blocks are set up while the one before drains), so a kernel's duration contains its wait; what
+    adds up to the step is how much later each kernel ENDS than every kernel before it."""
+    import collections
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from cajeta_llm_b200.engine.step import StepEntry
+    slots = [runner.admit() for _ in range(batch)]
+    for i in range(0, batch, 8):
+        runner.step([StepEntry(s, p, []) for s, p in zip(slots[i:i + 8], prompts(len(slots[i:i + 8]), PROMPT))])
+
+    def one():
+        return runner.step([StepEntry(s, [int(rng.integers(0, vocab))], [0]) for s in slots])
+
+    for _ in range(6):
+        one()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            one()
+        torch.cuda.synchronize()
+    events = sorted((e for e in prof.events() if e.device_type is not None and "Memcpy" not in e.name and "Memset" not in e.name
+                     and e.device_time_total > 0 and e.time_range is not None), key=lambda e: e.time_range.start)
+    first = [i for i, e in enumerate(events) if "embed_gather" in e.name]
+    if not first:
+        print("no kernel of a step was recorded")
+        return 1
+    step = events[first[-1]:]
+    t0 = step[0].time_range.start
+
+    def short(name):
+        for junk in ("void ", "(anonymous namespace)::", "cj::"):
+            name = name.replace(junk, "")
+        return name.split("(")[0][:56]
+
+    spent, prev_end = collections.OrderedDict(), t0
+    for e in step:
+        end = e.time_range.end
+        a = spent.setdefault(short(e.name), [0, 0.0])
+        a[0] += 1
+        a[1] += max(0.0, end - prev_end)
+        prev_end = max(prev_end, end)
+    print(f"decode step, batch {batch}, {n_layers} layers, {PROMPT}-token contexts: {len(step)} kernels, {prev_end - t0:.1f} us")
+    for name, (n, us) in spent.items():
+        print(f"  {name:58s} x{n:4d}  ends {us:8.1f} us later than what ran before it ({us / max(1, n):6.2f} a launch)")
+    for s in slots:
+        runner.release(s)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -184,6 +237,10 @@ def main() -> int:
     ap.add_argument("--model", default="a2.7b", choices=sorted(MODELS), help="layer sizes (default: the headline configuration)")
     ap.add_argument("--min-seconds", type=float, default=2.0,
                     help="device time over which the K-step region is repeated at the headline point (half of it at the other points)")
+    ap.add_argument("--batch", type=int, default=BATCH, help="requests of the headline decode run (default 8: the headline)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="instead of the bench line: where one replayed decode step of --batch requests spends its time, kernel by "
+                         "kernel, from the device's own timestamps (how much later each kernel ends than the one before it)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -215,7 +272,7 @@ def main() -> int:
     n_layers = cfg["num_hidden_layers"]
     pk = peaks()
     nums = model_numbers(cfg, n_layers)
-    max_b = 64 if not args.quick else BATCH
+    max_b = 64 if not args.quick else max(BATCH, args.batch)
     longest_prefill = 8192 if not args.quick else PREFILL_TOKENS
     ctx = max(CTX, longest_prefill + 64)
     # pool: 64 requests of 512 + generated tokens, 8 at the full context, or the longest prompt, whichever is largest
@@ -355,11 +412,14 @@ def main() -> int:
         out["_sum_us_per_step"] = round(sum(spent.values()), 1)
         return out
 
+    if args.timeline:
+        return timeline(runner, args.batch, prompts, rng, vocab, n_layers)
+
     # ---- headline: batch 8 -------------------------------------------------------------
     clocks = ClockSampler()
     clocks.start()                      # from before the warm-up on, so that a short region has samples too
     time.sleep(0.3)                     # nvidia-smi needs a moment to come up
-    main_run = decode_run(BATCH, warmup, steps, args.min_seconds)
+    main_run = decode_run(args.batch, warmup, steps, args.min_seconds)
     clock_info = clocks.stop()
     if clock_info.get("sm_mhz"):
         clock_info["ms_per_step_x_sm_mhz"] = main_run["ms_per_step"] * clock_info["sm_mhz"]
@@ -434,12 +494,12 @@ def main() -> int:
                "value_waiting_for_each_step": waited}
 
     line = {
-        "metric": f"decode tokens/s at batch 8 ({model_name}, bf16, random weights)",
+        "metric": f"decode tokens/s at batch {args.batch} ({model_name}, bf16, random weights)",
         "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights (bell-shaped, std 0.02), uniform random token ids",
         "config": {
-            "model": model_name, "global_batch": BATCH, "seq_len": CTX, "prompt_len": PROMPT,
+            "model": model_name, "global_batch": args.batch, "seq_len": CTX, "prompt_len": PROMPT,
             "parallelism": "single GPU", "layers": n_layers, "layers_in_config": full_layers, "hidden": cfg["hidden_size"],
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "experts": cfg["num_experts"], "top_k": cfg["num_experts_per_tok"], "moe_inter": cfg["moe_intermediate_size"],
