@@ -138,7 +138,7 @@ __device__ __forceinline__ void select_row(const float* row, int t, int E, int k
         }
         return;
     }
-    float wsum = 0.0f, last = 0.0f;
+    float wsum = 0.0f, last = 0.0f, mine = 0.0f;
     for (int j = 0; j < k; ++j) {
         float bp = -1.0f;
         int best = -1;
@@ -157,7 +157,13 @@ __device__ __forceinline__ void select_row(const float* row, int t, int E, int k
         // pick falls to expert j with a NaN weight so that the fault shows in the logits
         if (best < 0) { best = j < E ? j : 0; bp = __int_as_float(0x7fc00000); }
         else if (lane == 0) probs[best] = -1.0f;
-        if (lane == 0) { sel[t * k + j] = best; w[t * k + j] = bp; }
+        // a pick's weight stays with lane j until the sum is known (picks past 31 go through memory)
+        const bool held = norm_topk && j < 32;
+        if (held && lane == j) mine = bp;
+        if (lane == 0) {
+            sel[t * k + j] = best;
+            if (!held) w[t * k + j] = bp;
+        }
         wsum += bp;
         last = bp;
         __syncwarp();
@@ -168,9 +174,11 @@ __device__ __forceinline__ void select_row(const float* row, int t, int E, int k
         next = warp_max(next);
         if (lane == 0) gap[t] = (k < E && last > 0.0f) ? (last - next) / last : 1.0f;
     }
-    if (norm_topk && lane == 0) {
+    if (norm_topk) {
         if (wsum < 0.00006103515625f) wsum = 0.00006103515625f;
-        for (int j = 0; j < k; ++j) w[t * k + j] = w[t * k + j] / wsum;
+        if (lane < k) w[t * k + lane] = mine / wsum;
+        if (lane == 0)
+            for (int j = 32; j < k; ++j) w[t * k + j] = w[t * k + j] / wsum;
     }
 }
 

@@ -475,7 +475,10 @@ CJ_EXPORT int cj_rope_kv_write(const float* qkv, int ld, int q_off, int k_off, i
 // reference: model/MoeFfn.cajeta:1849-1916 (row form), combine kernel
 // io/QuantKernel.cajeta:40747; shared expert model/Prim.cajeta:1652-1664.
 // ---------------------------------------------------------------------------------
-template <int VEC>
+// KT > 0: k is KT and the picks' loads are written out, so that a thread has all its indices
+// under way at once and then all its rows (a loop over a run-time k waits for each in turn:
+// ten round trips to memory instead of three).  The sums keep their order either way.
+template <int VEC, int KT>
 __global__ void moe_combine_kernel(float* __restrict__ hs, const float* __restrict__ y, const int* __restrict__ slot_of_pick,
                                    const float* __restrict__ w, int k, const float* __restrict__ shared, int chunks,
                                    long long chunk_stride, const float* __restrict__ shared_scale, int H) {
@@ -484,46 +487,77 @@ __global__ void moe_combine_kernel(float* __restrict__ hs, const float* __restri
     int t = blockIdx.x;
     int i = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
     if (i >= H) return;
-    float acc[VEC];
+    constexpr int CH = 4;                       // chunks of the shared expert whose loads are written out
+    float acc[VEC], sh[VEC], res[VEC];
 #pragma unroll
-    for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
-    for (int j = 0; j < k; ++j) {
-        int s = slot_of_pick[t * k + j];
-        float wj = w[t * k + j];
-        const float* src = y + (size_t)s * H + i;
-        if (VEC == 4) {
-            float4 v4 = *(const float4*)src;
-            acc[0] += wj * v4.x; acc[1] += wj * v4.y; acc[2] += wj * v4.z; acc[3] += wj * v4.w;
-        } else {
-            acc[0] += wj * src[0];
+    for (int v = 0; v < VEC; ++v) acc[v] = sh[v] = 0.0f;
+    float* dst = hs + (size_t)t * H + i;
+    if (KT > 0) {
+        int slot[KT > 0 ? KT : 1];
+        float wj[KT > 0 ? KT : 1], row[KT > 0 ? KT : 1][VEC], part[CH][VEC];
+#pragma unroll
+        for (int j = 0; j < KT; ++j) {
+            slot[j] = slot_of_pick[t * KT + j];
+            wj[j] = w[t * KT + j];
         }
-    }
-    if (shared) {
-        float sh[VEC];
+        const float g = (shared && shared_scale) ? shared_scale[t] : 1.0f;
+        if (VEC == 4) *(float4*)res = *(const float4*)dst; else res[0] = dst[0];
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) sh[v] = 0.0f;
-        for (int c = 0; c < chunks; ++c) {
-            const float* src = shared + c * chunk_stride + (size_t)t * H + i;
-            if (VEC == 4) {
-                float4 v4 = *(const float4*)src;
-                sh[0] += v4.x; sh[1] += v4.y; sh[2] += v4.z; sh[3] += v4.w;
-            } else {
-                sh[0] += src[0];
+        for (int c = 0; c < CH; ++c) {
+            if (shared && c < chunks) {
+                const float* src = shared + c * chunk_stride + (size_t)t * H + i;
+                if (VEC == 4) *(float4*)part[c] = *(const float4*)src; else part[c][0] = src[0];
             }
         }
-        float g = shared_scale ? shared_scale[t] : 1.0f;
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) acc[v] += g * sh[v];
-    }
-    float* dst = hs + (size_t)t * H + i;
-    if (VEC == 4) {
-        float4 o = *(float4*)dst;
-        o.x += acc[0]; o.y += acc[1]; o.z += acc[2]; o.w += acc[3];
-        *(float4*)dst = o;
+        for (int j = 0; j < KT; ++j) {
+            const float* src = y + (size_t)slot[j] * H + i;
+            if (VEC == 4) *(float4*)row[j] = *(const float4*)src; else row[j][0] = src[0];
+        }
+#pragma unroll
+        for (int j = 0; j < KT; ++j)
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v] += wj[j] * row[j][v];
+        if (shared) {
+#pragma unroll
+            for (int c = 0; c < CH; ++c)
+                if (c < chunks)
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) sh[v] += part[c][v];
+            for (int c = CH; c < chunks; ++c) {
+                const float* src = shared + c * chunk_stride + (size_t)t * H + i;
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) sh[v] += src[v];
+            }
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v] += g * sh[v];
+        }
     } else {
-        dst[0] += acc[0];
+        for (int j = 0; j < k; ++j) {
+            int s = slot_of_pick[t * k + j];
+            float wj = w[t * k + j];
+            const float* src = y + (size_t)s * H + i;
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v] += wj * src[v];
+        }
+        if (shared) {
+            for (int c = 0; c < chunks; ++c) {
+                const float* src = shared + c * chunk_stride + (size_t)t * H + i;
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) sh[v] += src[v];
+            }
+            float g = shared_scale ? shared_scale[t] : 1.0f;
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v] += g * sh[v];
+        }
+        if (VEC == 4) *(float4*)res = *(const float4*)dst; else res[0] = dst[0];
     }
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) res[v] += acc[v];
+    if (VEC == 4) *(float4*)dst = *(float4*)res; else dst[0] = res[0];
 }
+
+constexpr int COMBINE_UNROLLED_MAX_ROWS = 256;
 
 CJ_EXPORT int cj_moe_combine(float* hs, const float* y, const int* slot_of_pick, const float* w, int k,
                              const float* shared, int chunks, long long chunk_stride, const float* shared_scale, int T,
@@ -536,8 +570,21 @@ CJ_EXPORT int cj_moe_combine(float* hs, const float* y, const int* slot_of_pick,
     int threads = H / per >= 256 ? 256 : 128;
     dim3 grid(T, (H / per + threads - 1) / threads + (H % per ? 1 : 0));
     if (grid.y > 65535) return CJ_ERR_SIZE;
-    if (vec) cj::launch(moe_combine_kernel<4>, dim3(grid), dim3(threads), 0, stream, hs, y, slot_of_pick, w, k, shared, chunks, chunk_stride, shared_scale, H);
-    else cj::launch(moe_combine_kernel<1>, dim3(grid), dim3(threads), 0, stream, hs, y, slot_of_pick, w, k, shared, chunks, chunk_stride, shared_scale, H);
+#define LAUNCH(V, KT) cj::launch(moe_combine_kernel<V, KT>, dim3(grid), dim3(threads), 0, stream, hs, y, slot_of_pick, w, k, shared, chunks, chunk_stride, shared_scale, H)
+    // few rows wait on latency and take the written-out form; many rows are bound by bytes, and there the
+    // loop's smaller register file (more blocks an SM) measured faster
+    if (vec) {
+        switch (T <= COMBINE_UNROLLED_MAX_ROWS ? k : 0) {
+            case 2: LAUNCH(4, 2); break;
+            case 4: LAUNCH(4, 4); break;
+            case 6: LAUNCH(4, 6); break;
+            case 8: LAUNCH(4, 8); break;
+            default: LAUNCH(4, 0);
+        }
+    } else {
+        LAUNCH(1, 0);
+    }
+#undef LAUNCH
     return launch_status();
 }
 

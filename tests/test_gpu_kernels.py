@@ -207,6 +207,36 @@ def test_gemm_swiglu_and_grouped(K, dtype):
     assert torch.allclose(hs2.double(), want2, atol=1e-5, rtol=1e-5)
 
 
+@pytest.mark.parametrize("k", [1, 2, 3, 4, 6, 8])
+@pytest.mark.parametrize("H,C", [(136, 0), (136, 1), (200, 5), (75, 3)])
+def test_combine_of_few_rows_and_of_many_gives_the_same_bits(K, k, H, C):
+    """Few rows take a form whose loads are written out per pick, many rows a loop: both hold to the
+    weighted sum in selection order plus the gated chunks of a shared expert in chunk order, and a row
+    has the same bits in either (the first rows of the large call are the small call's rows)."""
+    few, many = 7, 300
+    slots = many * k
+    g = torch.Generator().manual_seed(100 * k + H)
+    y = rnd(slots, H, seed=31)
+    slot_of_pick = torch.randperm(slots, generator=g).to(torch.int32).to(DEV)
+    w = rnd(many, k, seed=32).abs()
+    shared = rnd(C, many, H, seed=33) if C else None
+    gate = rnd(many, seed=34).abs() if C else None
+    hs0 = rnd(many, H, seed=35)
+    want = hs0.double().clone()
+    picks = slot_of_pick.view(many, k).long()
+    for j in range(k):
+        want += w[:, j].double()[:, None] * y[picks[:, j]].double()
+    if C:
+        want += gate.double()[:, None] * shared.double().sum(0)
+    big = hs0.clone()
+    K.moe_combine(big, y, slot_of_pick, w, k, shared, gate)
+    assert torch.allclose(big.double(), want, atol=1e-5, rtol=1e-5)
+    small = hs0[:few].clone()
+    K.moe_combine(small, y, slot_of_pick[:few * k].contiguous(), w[:few].contiguous(), k,
+                  shared[:, :few].contiguous() if C else None, gate[:few].contiguous() if C else None)
+    assert torch.equal(small, big[:few])
+
+
 @pytest.mark.parametrize("T,k,E,extra", [(9, 2, 5, 0), (511, 4, 60, 0), (513, 4, 60, 2), (3000, 3, 7, 1)])
 def test_grouping_is_a_stable_sort_by_expert(K, T, k, E, extra):
     """Few picks (8 warps a block) and thousands (32 warps): offsets count each expert's picks, the
