@@ -329,6 +329,7 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
     // kernel before this one: the chain position -> table -> addresses runs while that kernel
     // drains.  (Read past L1: the buffers are the same from step to step.)
     const int p = __ldcg(positions + t);
+    const int req = __ldcg(row_req + t);          // sent for beside the position, not after the test on it
     const int from = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
     const int n_keys = p - from + 1;
     const int n_splits = (n_keys + TC_CHUNK - 1) / TC_CHUNK;
@@ -336,7 +337,7 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int key0 = from + split * TC_CHUNK;
     const int count = min(TC_CHUNK, p - key0 + 1);
-    const int* tab = table + (size_t)__ldcg(row_req + t) * table_stride;
+    const int* tab = table + (size_t)req * table_stride;
 
     if (tid < TC_CHUNK) {
         long long b = 0;
