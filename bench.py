@@ -301,16 +301,6 @@ def main() -> int:
         torch.cuda.synchronize()
         return a.elapsed_time(b)
 
-    def experts_touched():
-        """Distinct routed experts the last step used, summed over the layers."""
-        distinct = 0
-        for blk in runner.model.blocks:
-            off = getattr(blk.feed_forward, "last_offsets", None)
-            if off is not None:
-                o = off.cpu().numpy()[: cfg["num_experts"] + 1]       # the routed groups (shared chunks follow them)
-                distinct += int((o[1:] > o[:-1]).sum())
-        return distinct
-
     def decode_run(batch, n_warm, n_steps, min_seconds, prompt_len=PROMPT):
         """Prefill ``batch`` prompts and time ``n_steps`` decode steps on the device after
         ``n_warm`` untimed ones; again from fresh prompts until ``min_seconds`` were timed."""
@@ -335,8 +325,12 @@ def main() -> int:
             times.append(event_ms(lambda: one(next(it)), reps=n_steps))
             launches = K.launches - launches0
             if not step_bytes:
-                # bytes the last step had to read
-                distinct = experts_touched()
+                # bytes a step like the timed ones has to read: one more step, launched kernel by kernel
+                # so that it can say which experts its rows picked (a replayed graph keeps that to itself)
+                dump = {}
+                extra = rng.integers(0, vocab, size=batch)
+                runner.step([StepEntry(s, [int(extra[j])], [0]) for j, s in enumerate(slots)], routing_dump=dump)
+                distinct = sum(int(torch.unique(sel).numel()) for sel, _ in dump.values())
                 ctx_len = prompt_len + n_warm + n_steps
                 step_bytes = (n_layers * nums["per_layer_fixed"] + distinct * nums["per_expert"] + nums["head"]
                               + batch * ctx_len * nums["kv_per_token"] + batch * nums["H"] * 2)
@@ -382,10 +376,11 @@ def main() -> int:
         first = torch.cuda.Event(enable_timing=True)
         first.record()
         K.start_trace()
-        runner.step(entries, routing_dump={})
+        dump = {}
+        runner.step(entries, routing_dump=dump)
         trace = K.stop_trace()
         torch.cuda.synchronize()
-        touched = experts_touched() / max(1, n_layers)
+        touched = sum(int(torch.unique(sel).numel()) for sel, _ in dump.values()) / max(1, n_layers)
         for s in slots:
             runner.release(s)
         spent, prev = {}, first

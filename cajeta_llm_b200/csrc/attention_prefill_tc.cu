@@ -181,6 +181,23 @@ struct QueryTile {
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, Args p) {
+    // A step's arrays are laid out for more requests than it may have (the shape of a captured step
+    // covers the most it can hold), and the grid for the most row blocks those could make: most
+    // blocks of such a launch have nothing to do.  Each finds that out from the sum of the
+    // requests' row blocks - a few loads a lane, before anything else (the step's layout was
+    // written before the step's first kernel) - and leaves at once; an idle block that walked the
+    // whole list first kept an SM for as long as a short row block takes.
+    {
+        int tiles = 0;
+        for (int r = threadIdx.x & 31; r < p.n_requests; r += 32)
+            tiles += (__ldcg(p.req_start + r + 1) - __ldcg(p.req_start + r) + p.block_rows - 1) / p.block_rows;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) tiles += __shfl_xor_sync(0xffffffffu, tiles, o);
+        if ((int)blockIdx.y >= tiles) {
+            cj::after_predecessor();
+            return;
+        }
+    }
     cj::after_predecessor();
     // ---- which request and which 256 rows of it -----------------------------------------------
     // Blocks start in the order of blockIdx.y; the last rows of a request see the most keys, so

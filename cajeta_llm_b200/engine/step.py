@@ -156,7 +156,7 @@ class ModelRunner:
             from ..csrc import build as _build
             _build.build_all(sorted(n for n in model.libraries() if n in _build.LIBRARIES))
         self._graphs: Dict[Tuple[int, int], _CapturedStep] = {}
-        self._mixed_graphs: Dict[Tuple[int, int], _CapturedStep] = {}   # by (rows, wanted rows filled up), oldest use first
+        self._mixed_graphs: Dict[Tuple[int, int, int], _CapturedStep] = {}   # by (rows, wanted rows filled up, requests rounded up), oldest use first
         self._mixed_seen: Dict[Tuple[int, int], int] = {}
         self._graph_pool = None
         self._decode_host: Dict[Tuple[int, int], tuple] = {}   # pinned metadata of decode steps by (rows, width), reused
@@ -206,19 +206,22 @@ class ModelRunner:
 
     def _step_mixed(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """A step with prompt portions on the bfloat16 path: uncaptured the first time its shape
-        is met, captured the second time, replayed afterwards.  The shape is the number of rows
-        and of wanted rows only: the per-request arrays are laid out for ``max_seqs`` requests
-        whatever the step has (the others bring no rows), and up to ``max_seqs`` wanted rows are
-        filled up to that number (the logits of the fillers are thrown away; a step that wants
-        nothing stays so), so that the steps
-        of a scheduler that fills a token budget - the same number of rows step after step, among
-        a changing number of requests of which a changing number ends - replay one graph."""
+        is met, captured the second time, replayed afterwards.  The shape is the number of rows,
+        the number of requests rounded up to a power of two (at most ``max_seqs``: the per-request
+        arrays are laid out for that many, the others bring no rows) and the number of wanted
+        rows, which up to the padded number of requests is filled up to it (the logits of the
+        fillers are thrown away; a step that wants nothing stays so) - so that the steps of a
+        scheduler that fills a token budget, the same number of rows step after step among a
+        changing number of requests of which a changing number ends, replay a few graphs.  (Laid
+        out for ``max_seqs`` requests whatever the step has, a lone prompt portion paid for the
+        row blocks that sixty-three absent requests could have had: the attention's grid covers
+        the most the layout can hold.)"""
         from ..csrc import kernels as K
         rows = sum(len(e.tokens) for e in entries)
         wanted = sum(len(e.want) for e in entries)
-        pad_requests = self.cache.max_seqs
+        pad_requests = min(self.cache.max_seqs, 1 << max(0, len(entries) - 1).bit_length())
         pad_wanted = 0 if wanted == 0 else max(wanted, min(rows, pad_requests))
-        key = (rows, pad_wanted)
+        key = (rows, pad_wanted, pad_requests)
         cap = self._mixed_graphs.get(key)
         if cap is None:
             seen = self._mixed_seen[key] = self._mixed_seen.get(key, 0) + 1

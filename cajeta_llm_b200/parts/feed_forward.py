@@ -97,7 +97,6 @@ class SparseMoE(Part):
         self.ws_gate = self.ws_up = self.ws_down = None
         self.shared_gate_w = None
         self.router_split = None        # [cols, 3 hidden] bfloat16: router rows (and the gate's) three times over
-        self.last_offsets = None
         # chunks of the shared expert that run as extra groups of the grouped products
         self.shared_chunks = 0
         if self.shared_inter > 0 and self.shared_inter % self.inter == 0 and self.shared_inter // self.inter <= 64:
@@ -238,7 +237,6 @@ class SparseMoE(Part):
         slot_of_pick = torch.empty((T * k,), dtype=torch.int32, device=dev)
         K.tag = "grouping"
         K.moe_group(sel, k, E, offsets, slot_token, slot_of_pick, extra_groups=C)
-        self.last_offsets = offsets          # kept for measurement: which experts the last step touched
 
         act = torch.empty((n_slots, self.inter), dtype=rt.act_dtype, device=dev)
         G = E + C

@@ -94,6 +94,35 @@ def test_rmsnorm_partial_sums_and_three_term_form(K, H):
     assert float((three - exact.double().cpu()).abs().max()) <= 2.0 ** -22 * float(exact.abs().max())
 
 
+@pytest.mark.parametrize("H", [2048, 1540, 3584, 384])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_of_a_row_does_not_depend_on_the_rows_beside_it(K, H, out_dtype):
+    """Hundreds of rows in one call against the plain norm, and bit for bit against the same rows
+    normed a few at a time - with pending partial sums, the float32 copy and the three-term form."""
+    rows, few = 333, 9
+    x0 = rnd(rows, H, seed=41, scale=3.0)
+    w = rnd(H, seed=42)
+    parts = rnd(3, rows, H, seed=43)
+    want = P.rmsnorm((x0.double() + parts.double().sum(0)).cpu(), w.double().cpu(), 1e-6)
+    x = x0.clone()
+    out, out32 = torch.empty(rows, H, device=DEV, dtype=out_dtype), torch.empty(rows, H, device=DEV)
+    split = torch.empty(rows, 3 * H, device=DEV, dtype=torch.bfloat16)
+    K.rmsnorm(x, w, 1e-6, out, out32, None, parts, split)
+    assert torch.allclose(out32.double().cpu(), want, atol=1e-5, rtol=1e-5)
+    for lo in (0, 100, rows - few):
+        xs = x0[lo:lo + few].clone()
+        o, o32 = torch.empty(few, H, device=DEV, dtype=out_dtype), torch.empty(few, H, device=DEV)
+        sp = torch.empty(few, 3 * H, device=DEV, dtype=torch.bfloat16)
+        K.rmsnorm(xs, w, 1e-6, o, o32, None, parts[:, lo:lo + few].contiguous(), sp)
+        assert torch.equal(xs, x[lo:lo + few]) and torch.equal(o, out[lo:lo + few])
+        assert torch.equal(o32, out32[lo:lo + few]) and torch.equal(sp, split[lo:lo + few])
+    plain = torch.empty(rows, H, device=DEV, dtype=out_dtype)             # and without any of the extras
+    K.rmsnorm(x0, w, 1e-6, plain)
+    one = torch.empty(1, H, device=DEV, dtype=out_dtype)
+    K.rmsnorm(x0[200:201].contiguous(), w, 1e-6, one)
+    assert torch.equal(one[0], plain[200])
+
+
 @pytest.mark.parametrize("dtype,H", [(torch.bfloat16, 2048), (torch.bfloat16, 72), (torch.float32, 100), (torch.bfloat16, 67)])
 @pytest.mark.parametrize("rows", [5, 300, 700])
 def test_gather_rows(K, dtype, H, rows):
