@@ -37,7 +37,8 @@ namespace {
 
 constexpr int BK = 64;             // K elements per stage: one 128-byte swizzle row
 constexpr int UMMA_K = 16;         // K of one tcgen05.mma of kind::f16
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;          // warps 0 and 6: loads; warp 1: products; warps 2-5: epilogue
+constexpr int LOADERS = 2;
 
 enum Epilogue { EPI_STORE_F32 = 0, EPI_ACC_F32 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_BF16 = 3 };
 
@@ -198,18 +199,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // a grouped launch knows its number of tiles only now (it depends on the routing)
     if (p.group_offsets) total_tiles = tiles_before[p.groups] * feat_tiles * p.k_splits;
 
-    if (warp == 0) {
-        // ---- TMA producer: streams stage after stage, straight across tile boundaries ----------
+    if (warp == 0 || warp == 6) {
+        // ---- TMA producers: stream stage after stage, straight across tile boundaries ----------
+        // Two warps, one taking the even iterations and one the odd: what ONE thread can have
+        // under way in bulk loads is bounded (measured: a thread streams 36 GB/s of cold 16 KB
+        // tiles however deep its ring, two threads twice that), and with every SM streaming, one
+        // issuing thread an SM stops at 5.4 TB/s.  A loader is never a whole round of the ring
+        // ahead of the products (LOADERS < STAGES), which is what a wait by phase parity needs.
+        static_assert(LOADERS < STAGES, "a loader must stay within one round of the ring");
+        const int mine = warp == 0 ? 0 : 1;
         if (elect_one()) {
-            tma_prefetch_descriptor(&map_x);
-            tma_prefetch_descriptor(&map_w);
-            if (DUAL) tma_prefetch_descriptor(&map_w2);
+            if (mine == 0) {
+                tma_prefetch_descriptor(&map_x);
+                tma_prefetch_descriptor(&map_w);
+                if (DUAL) tma_prefetch_descriptor(&map_w2);
+            }
             uint32_t early = 0;               // stages whose weight tiles left before the wait
             if (early_ok) {
                 for (int tile = blockIdx.x; tile < total_tiles && early < STAGES; tile += gridDim.x) {
                     TileCoord c = decode_tile<TOK_TILE, FEAT_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before);
                     if (!c.valid) continue;
                     for (int i = 0; i < c.n_kb && early < STAGES; ++i, ++early) {
+                        if ((int)(early % LOADERS) != mine) continue;
                         uint8_t* st = tiles + (size_t)early * S::STAGE_BYTES;
                         mbar_expect_tx(&full_bar[early], S::STAGE_BYTES);
                         int k0 = (c.kb_begin + i) * BK;
@@ -225,6 +236,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 TileCoord c = decode_tile<TOK_TILE, FEAT_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before);
                 if (!c.valid) continue;
                 for (int i = 0; i < c.n_kb; ++i, ++it) {
+                    if ((int)(it % LOADERS) != mine) continue;
                     int s = it % STAGES;
                     uint8_t* st = tiles + (size_t)s * S::STAGE_BYTES;
                     int k0 = (c.kb_begin + i) * BK;
@@ -287,7 +299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 ++acc_it;
             }
         }
-    } else {
+    } else if (warp < 6) {
         // ---- epilogue: warps 2..5, each its own quarter of the 128 lanes --------------------
         if (early_ok) cj::after_predecessor();
         const int quarter = warp & 3;

@@ -40,7 +40,8 @@ namespace {
 
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;          // warps 0 and 6: loads; warp 1: products; warps 2-5: epilogue
+constexpr int LOADERS = 2;          // one thread keeps only so many bulk loads under way: the ring's stages are dealt to two
 constexpr int FEAT_TILE = 256;      // feature rows a pair of blocks covers
 constexpr int MAX_GROUPS = 1024;
 constexpr int MAX_ACC_STAGES = 2;
@@ -163,8 +164,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const uint32_t tmem_base = *tmem_slot;
     if (p.group_offsets) total_tiles = tiles_before[p.groups] * feat_tiles;
 
-    if (warp == 0) {
-        // ---- TMA producer (in both blocks) ---------------------------------------------------
+    if (warp == 0 || warp == 6) {
+        // ---- TMA producers (in both blocks): one warp the even iterations, one the odd -------
+        static_assert(LOADERS < STAGES, "a loader must stay within one round of the ring");
+        const int mine = warp == 0 ? 0 : 1;
         if (elect_one()) {
             tma_prefetch_descriptor(&map_x);
             tma_prefetch_descriptor(&map_w);
@@ -176,6 +179,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 const int k_blocks = (p.K + BK - 1) / BK;
                 const int w_row = c.w_row0 + rank * 128;
                 for (int i = 0; i < k_blocks; ++i, ++it) {
+                    if ((int)(it % LOADERS) != mine) continue;
                     int s = it % STAGES;
                     ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, 1);
                     if (!ok) break;
@@ -222,7 +226,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 ++acc_it;
             }
         }
-    } else {
+    } else if (warp < 6) {
         // ---- epilogue: warps 2..5 of both blocks, each its quarter of the block's 128 lanes -----
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
@@ -357,7 +361,9 @@ swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     if (p.group_offsets) total_tiles = tiles_before[p.groups] * feat_tiles;
     const int k_blocks = (p.K + BK - 1) / BK;
 
-    if (warp == 0) {
+    if (warp == 0 || warp == 6) {
+        static_assert(LOADERS < STAGES, "a loader must stay within one round of the ring");
+        const int mine = warp == 0 ? 0 : 1;
         if (elect_one()) {
             tma_prefetch_descriptor(&map_x);
             tma_prefetch_descriptor(rank == 0 ? &map_wg : &map_wu);
@@ -366,6 +372,7 @@ swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             for (int tile = cluster; tile < total_tiles && ok; tile += clusters) {
                 TileCoord c = decode_tile<SW_TOK, SW_FEAT>(p, tile, feat_tiles, tok_tiles, tiles_before);
                 for (int i = 0; i < k_blocks; ++i, ++it) {
+                    if ((int)(it % LOADERS) != mine) continue;
                     int s = it % STAGES;
                     ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, 1);
                     if (!ok) break;
@@ -408,7 +415,7 @@ swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 ++acc_it;
             }
         }
-    } else {
+    } else if (warp < 6) {
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
         uint32_t acc_it = 0;
