@@ -264,7 +264,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
 // and weighted values are 256 tensor instructions and a few dozen fragment loads instead of
 // thousands of multiply-adds, and ALL query heads of a kv head's group (up to 8 at a time) share
 // them - the product's 16 rows are those heads (the rest zero), its columns the chunk's 128
-// keys.  Warp w takes keys [16 w, 16 w + 16) for both products; the warps exchange row maxima
+// keys.  Warp w takes keys [32 w, 32 w + 32) for both products; the warps exchange row maxima
 // through shared memory and add their partial outputs there in warp order.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool valid) {
@@ -298,11 +298,23 @@ __device__ __forceinline__ const __nv_bfloat16* tile_at(const __nv_bfloat16* bas
 }
 
 constexpr int TC_CHUNK = 128;
-constexpr int TC_THREADS = 256;      // 8 warps, 16 keys each
 constexpr int TC_HEADS = 8;          // query heads of a kv head a block takes at a time
 
+// One tile of shared memory holds the chunk's keys and then its values: the keys are fetched and
+// scored, the values fetched over them while the exponentials run.  A chunk is a chain of round
+// trips (position -> page table -> keys -> values -> partial result) whose length the bytes hardly
+// change; what an SM streams is the chunks it has side by side times their bytes over that
+// length.  With keys and values in tiles of their own (64 KB) and 256 threads, three blocks fit
+// an SM and the kernel streamed 3.9-4.0 TB/s; with one tile (32 KB) and 128 threads - four warps
+// of 32 keys - five do, for a chain one round trip longer: 5.4 TB/s at 32 rows x 4,096 keys (a
+// step 9 % shorter), batch 64 x 576 keys 3.6 % shorter, batch 1 0.6 % longer.  Six blocks an SM
+// (80 registers, a few spilled) measured 1-2 % slower than five.
+constexpr int TC_THREADS = 128;
+constexpr int TC_WARPS = TC_THREADS / 32;
+constexpr int TC_BLOCKS = 5;         // blocks an SM
+
 template <int HD>
-__global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
+__global__ void __launch_bounds__(TC_THREADS, TC_BLOCKS) decode_attention_tc_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ kplane,
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ positions, const int* __restrict__ row_req,
     const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int head_batches,
@@ -310,14 +322,12 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
     int max_splits, int merge_later) {
     cj::release_successor();
     constexpr int COLS = HD / 8;
-    constexpr int WARPS = TC_THREADS / 32;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;             // [128][HD] swizzled; later the warps' partial outputs
-    __nv_bfloat16* vs = ks + TC_CHUNK * HD;                   // [128][HD] swizzled
-    __nv_bfloat16* qs = vs + TC_CHUNK * HD;                   // [16][HD] swizzled: the group's heads, zero rows below
-    __shared__ long long bases[TC_CHUNK];
-    __shared__ float smax[WARPS][16];
-    __shared__ float ssum[WARPS][16];
+    __nv_bfloat16* kv = (__nv_bfloat16*)smem_raw;             // [128][HD] swizzled: the keys, then the values, then the warps' partial outputs
+    __nv_bfloat16* qs = kv + TC_CHUNK * HD;                   // [16][HD] swizzled: the group's heads, zero rows below
+    __shared__ int bases[TC_CHUNK];                           // the key's row in the plane (pages x kv heads x page tokens)
+    __shared__ float smax[TC_WARPS][16];
+    __shared__ float ssum[TC_WARPS][16];
     __shared__ int is_last;
 
     const int t = blockIdx.x, split = blockIdx.z;
@@ -325,11 +335,8 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
     const int group = n_heads / n_kv;
     const int h0 = kvh * group + hb * TC_HEADS;
     const int n_h = min(TC_HEADS, group - hb * TC_HEADS);
-    // The step's positions and page tables were written before the step's first kernel, not by the
-    // kernel before this one: the chain position -> table -> addresses runs while that kernel
-    // drains.  (Read past L1: the buffers are the same from step to step.)
     const int p = __ldcg(positions + t);
-    const int req = __ldcg(row_req + t);          // sent for beside the position, not after the test on it
+    const int req = __ldcg(row_req + t);
     const int from = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
     const int n_keys = p - from + 1;
     const int n_splits = (n_keys + TC_CHUNK - 1) / TC_CHUNK;
@@ -338,95 +345,101 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
     const int key0 = from + split * TC_CHUNK;
     const int count = min(TC_CHUNK, p - key0 + 1);
     const int* tab = table + (size_t)req * table_stride;
-
-    if (tid < TC_CHUNK) {
-        long long b = 0;
+    {
+        int b = 0;
         if (tid < count) {
             int key = key0 + tid;
             int page = __ldcg(tab + key / page_tokens);
-            b = (((long long)page * n_kv + kvh) * page_tokens + key % page_tokens) * HD;
+            b = (page * n_kv + kvh) * page_tokens + key % page_tokens;
         }
         bases[tid] = b;
     }
-    // Only the row's own position was written by the kernel before this one (the rotation and
-    // cache write of this step); it lies in the row's last chunk.  The other chunks hold keys and
-    // values of earlier steps: their fetch starts while that kernel drains.
+    // only the row's own position was written by the kernel before this one; it lies in the row's last chunk
     const bool older_keys_only = split < n_splits - 1;
     if (!older_keys_only) cj::after_predecessor();
     __syncthreads();
     constexpr int ROWS_STEP = TC_THREADS / COLS;
     const int c = tid % COLS, r0 = tid / COLS;
-    const int in_row = (c ^ (r0 & 7)) * 8;
-    {
-        // all keys, then all values; rows past the chunk's end are filled with zeros (a stale
-        // value row times a zero weight could still be NaN)
 #pragma unroll
-        for (int j = 0; j < TC_CHUNK / ROWS_STEP; ++j) {
-            int r = r0 + j * ROWS_STEP;
-            cp_async16_zfill(ks + r * HD + in_row, kplane + bases[r] + c * 8, r < count);
-        }
-        cp_async_commit();
-#pragma unroll
-        for (int j = 0; j < TC_CHUNK / ROWS_STEP; ++j) {
-            int r = r0 + j * ROWS_STEP;
-            cp_async16_zfill(vs + r * HD + in_row, vplane + bases[r] + c * 8, r < count);
-        }
-        cp_async_commit();
+    for (int j = 0; j < TC_CHUNK / ROWS_STEP; ++j) {
+        const int r = r0 + j * ROWS_STEP;
+        cp_async16_zfill(kv + r * HD + ((c ^ (r & 7)) * 8), kplane + (size_t)bases[r] * HD + c * 8, r < count);
     }
+    cp_async_commit();
     if (older_keys_only) cj::after_predecessor();
-    if (r0 < 16) {
+#pragma unroll
+    for (int r = r0; r < 16; r += ROWS_STEP) {
         // the queries (the kernel before wrote them): q rows, zero below the heads taken
         uint4 qv = make_uint4(0u, 0u, 0u, 0u);
-        if (r0 < n_h) qv = __ldcg((const uint4*)(q + ((size_t)t * n_heads + h0 + r0) * HD + c * 8));
-        *(uint4*)(qs + r0 * HD + in_row) = qv;
+        if (r < n_h) qv = __ldcg((const uint4*)(q + ((size_t)t * n_heads + h0 + r) * HD + c * 8));
+        *(uint4*)(qs + r * HD + ((c ^ (r & 7)) * 8)) = qv;
     }
-    cp_async_wait<1>();
+    cp_async_wait<0>();
     __syncthreads();
 
-    // ---- scores of this warp's 16 keys for the 16 rows -------------------------------------------
+    // ---- scores of this warp's 32 keys (two blocks of 16) for the 16 rows -------------------------
     const int g = lane >> 2, t4 = lane & 3, mi = lane >> 3;
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    float s[2][2][4];
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) s[kb][j][0] = s[kb][j][1] = s[kb][j][2] = s[kb][j][3] = 0.0f;
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk) {
-        unsigned qf[4], b[4];
+        unsigned qf[4];
         ldmatrix_x4(qf, tile_at<HD>(qs, lane & 15, kk * 16 + (lane >> 4) * 8));
-        ldmatrix_x4(b, tile_at<HD>(ks, warp * 16 + (mi >> 1) * 8 + (lane & 7), kk * 16 + (mi & 1) * 8));
-        mma_bf16(s[0], qf, b[0], b[1]);
-        mma_bf16(s[1], qf, b[2], b[3]);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+            unsigned b[4];
+            ldmatrix_x4(b, tile_at<HD>(kv, warp * 32 + kb * 16 + (mi >> 1) * 8 + (lane & 7), kk * 16 + (mi & 1) * 8));
+            mma_bf16(s[kb][0], qf, b[0], b[1]);
+            mma_bf16(s[kb][1], qf, b[2], b[3]);
+        }
     }
-    // s[j][e]: row g (e < 2) or g + 8, key warp * 16 + j * 8 + 2 t4 + (e & 1)
+    // s[kb][j][e]: row g (e < 2) or g + 8, key warp * 32 + kb * 16 + j * 8 + 2 t4 + (e & 1)
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const bool in = warp * 16 + j * 8 + 2 * t4 + e < count;
-            s[j][e] = in ? s[j][e] * scale : -INFINITY;
-            s[j][2 + e] = in ? s[j][2 + e] * scale : -INFINITY;
-            mx0 = fmaxf(mx0, s[j][e]);
-            mx1 = fmaxf(mx1, s[j][2 + e]);
-        }
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const bool in = warp * 32 + kb * 16 + j * 8 + 2 * t4 + e < count;
+                s[kb][j][e] = in ? s[kb][j][e] * scale : -INFINITY;
+                s[kb][j][2 + e] = in ? s[kb][j][2 + e] * scale : -INFINITY;
+                mx0 = fmaxf(mx0, s[kb][j][e]);
+                mx1 = fmaxf(mx1, s[kb][j][2 + e]);
+            }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     if (t4 == 0) { smax[warp][g] = mx0; smax[warp][g + 8] = mx1; }
-    __syncthreads();                                            // every warp is done with the keys, too
+    __syncthreads();                                            // every warp is done with the keys
+    // the values over the keys; their fetch runs during the exponentials.  Rows past the chunk's end
+    // are filled with zeros (a stale value row times a zero weight could still be NaN)
+#pragma unroll
+    for (int j = 0; j < TC_CHUNK / ROWS_STEP; ++j) {
+        const int r = r0 + j * ROWS_STEP;
+        cp_async16_zfill(kv + r * HD + ((c ^ (r & 7)) * 8), vplane + (size_t)bases[r] * HD + c * 8, r < count);
+    }
+    cp_async_commit();
     float m0 = smax[0][g], m1 = smax[0][g + 8];
 #pragma unroll
-    for (int w = 1; w < WARPS; ++w) { m0 = fmaxf(m0, smax[w][g]); m1 = fmaxf(m1, smax[w][g + 8]); }
+    for (int w = 1; w < TC_WARPS; ++w) { m0 = fmaxf(m0, smax[w][g]); m1 = fmaxf(m1, smax[w][g + 8]); }
     // the chunk has at least one key, so the maxima are finite
-    unsigned pf[4];
-    float sum0, sum1;
-    {
-        float e00 = expf(s[0][0] - m0), e01 = expf(s[0][1] - m0), e02 = expf(s[0][2] - m1), e03 = expf(s[0][3] - m1);
-        float e10 = expf(s[1][0] - m0), e11 = expf(s[1][1] - m0), e12 = expf(s[1][2] - m1), e13 = expf(s[1][3] - m1);
-        sum0 = (e00 + e01) + (e10 + e11);
-        sum1 = (e02 + e03) + (e12 + e13);
-        pf[0] = pack_bf16(e00, e01);
-        pf[1] = pack_bf16(e02, e03);
-        pf[2] = pack_bf16(e10, e11);
-        pf[3] = pack_bf16(e12, e13);
+    unsigned pf[2][4];
+    float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+        float e00 = expf(s[kb][0][0] - m0), e01 = expf(s[kb][0][1] - m0), e02 = expf(s[kb][0][2] - m1), e03 = expf(s[kb][0][3] - m1);
+        float e10 = expf(s[kb][1][0] - m0), e11 = expf(s[kb][1][1] - m0), e12 = expf(s[kb][1][2] - m1), e13 = expf(s[kb][1][3] - m1);
+        sum0 += (e00 + e01) + (e10 + e11);
+        sum1 += (e02 + e03) + (e12 + e13);
+        pf[kb][0] = pack_bf16(e00, e01);
+        pf[kb][1] = pack_bf16(e02, e03);
+        pf[kb][2] = pack_bf16(e10, e11);
+        pf[kb][3] = pack_bf16(e12, e13);
     }
     sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
     sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
@@ -441,15 +454,16 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
 #pragma unroll
-    for (int dp = 0; dp < HD / 16; ++dp) {
-        unsigned b[4];
-        ldmatrix_x4_trans(b, tile_at<HD>(vs, warp * 16 + (mi & 1) * 8 + (lane & 7), dp * 16 + (mi >> 1) * 8));
-        mma_bf16(o[2 * dp], pf, b[0], b[1]);
-        mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
-    }
-    // rows below the heads taken are zero work; the first n_h rows go to shared memory (the keys'
-    // tile is free: every warp passed the barrier after its scores): [warp][row][HD] float32
-    float* osum = (float*)ks;
+    for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; ++dp) {
+            unsigned b[4];
+            ldmatrix_x4_trans(b, tile_at<HD>(kv, warp * 32 + kb * 16 + (mi & 1) * 8 + (lane & 7), dp * 16 + (mi >> 1) * 8));
+            mma_bf16(o[2 * dp], pf[kb], b[0], b[1]);
+            mma_bf16(o[2 * dp + 1], pf[kb], b[2], b[3]);
+        }
+    __syncthreads();                                            // every warp is done with the values: the tile is free
+    float* osum = (float*)kv;                                   // [warp][row][HD] float32
     if (g < n_h) {
 #pragma unroll
         for (int i = 0; i < HD / 8; ++i)
@@ -462,7 +476,7 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
         float2 a = make_float2(0.0f, 0.0f);
         float l = 0.0f;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) {
+        for (int w = 0; w < TC_WARPS; ++w) {
             float2 v = *(const float2*)(osum + ((size_t)w * TC_HEADS + row) * HD + 2 * d2);
             a.x += v.x;
             a.y += v.y;
@@ -478,17 +492,13 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attention_tc_kernel(
             if (d2 == 0) {
                 float m = smax[0][row];
 #pragma unroll
-                for (int w = 1; w < WARPS; ++w) m = fmaxf(m, smax[w][row]);
+                for (int w = 1; w < TC_WARPS; ++w) m = fmaxf(m, smax[w][row]);
                 part_ml[slot * 2] = m;
                 part_ml[slot * 2 + 1] = l;
             }
         }
     }
-    if (n_splits == 1) return;
-    // with many chunks in the step the merge is a kernel of its own (decode_merge_kernel): a block
-    // then ends with its partial stores, without the fence and the ticket's round trip to memory,
-    // and the SM's shared memory is free for the next chunk that much sooner
-    if (merge_later) return;
+    if (n_splits == 1 || merge_later) return;
 
     // the last chunk of this (row, kv head, head batch) to finish merges all chunks, in chunk order
     __syncthreads();
@@ -626,8 +636,8 @@ CJ_EXPORT int cj_decode_attention_tc(const void* q, void* out, const void* kplan
     dim3 grid(T, n_kv * head_batches, splits);
 #define LAUNCH(HD)                                                                                                     \
     {                                                                                                                  \
-        constexpr int smem = (2 * TC_CHUNK + 16) * HD * (int)sizeof(__nv_bfloat16);                                    \
-        static_assert(8 * TC_HEADS * HD * 4 <= TC_CHUNK * HD * 2, "the warps' partial outputs must fit the keys' tile"); \
+        constexpr int smem = (TC_CHUNK + 16) * HD * (int)sizeof(__nv_bfloat16);                                        \
+        static_assert(TC_WARPS * TC_HEADS * HD * 4 <= TC_CHUNK * HD * 2, "the warps' partial outputs must fit the tile"); \
         static bool configured = false;                                                                                \
         if (!configured) {                                                                                             \
             cudaError_t e = cudaFuncSetAttribute(decode_attention_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
