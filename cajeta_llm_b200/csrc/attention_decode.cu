@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
 // The same chunk on the tensor cores (mma.sync m16n8k16, bf16 in, f32 out): a chunk's scores
 // and weighted values are 256 tensor instructions and a few dozen fragment loads instead of
 // thousands of multiply-adds, and ALL query heads of a kv head's group (up to 8 at a time) share
-// them - the product's 16 rows are those heads (the rest zero), its columns the chunk's 128
+// them - the product's 16 rows are those heads (the rest fed zeros), its columns the chunk's 128
 // keys.  Warp w takes keys [32 w, 32 w + 32) for both products; the warps exchange row maxima
 // through shared memory and add their partial outputs there in warp order.
 // ---------------------------------------------------------------------------------------------
@@ -286,6 +286,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// the same product with rows 8..15 of A zero: c0, c1 are rows 0..7; rows 8..15 land in d0, d1
+__device__ __forceinline__ void mma_bf16_top(float& c0, float& c1, float& d0, float& d1, unsigned a0, unsigned a2, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c0), "+f"(c1), "+f"(d0), "+f"(d1)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x2(unsigned (&r)[2], const void* smem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(s));
 }
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -324,10 +334,10 @@ __global__ void __launch_bounds__(TC_THREADS, TC_BLOCKS) decode_attention_tc_ker
     constexpr int COLS = HD / 8;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* kv = (__nv_bfloat16*)smem_raw;             // [128][HD] swizzled: the keys, then the values, then the warps' partial outputs
-    __nv_bfloat16* qs = kv + TC_CHUNK * HD;                   // [16][HD] swizzled: the group's heads, zero rows below
+    __nv_bfloat16* qs = kv + TC_CHUNK * HD;                   // [8][HD] swizzled: the group's heads, zero rows below them
     __shared__ int bases[TC_CHUNK];                           // the key's row in the plane (pages x kv heads x page tokens)
-    __shared__ float smax[TC_WARPS][16];
-    __shared__ float ssum[TC_WARPS][16];
+    __shared__ float smax[TC_WARPS][TC_HEADS];
+    __shared__ float ssum[TC_WARPS][TC_HEADS];
     __shared__ int is_last;
 
     const int t = blockIdx.x, split = blockIdx.z;
@@ -367,37 +377,40 @@ __global__ void __launch_bounds__(TC_THREADS, TC_BLOCKS) decode_attention_tc_ker
     }
     cp_async_commit();
     if (older_keys_only) cj::after_predecessor();
-#pragma unroll
-    for (int r = r0; r < 16; r += ROWS_STEP) {
+    static_assert(ROWS_STEP >= TC_HEADS, "one pass of the block's threads covers the query tile");
+    if (r0 < TC_HEADS) {
         // the queries (the kernel before wrote them): q rows, zero below the heads taken
         uint4 qv = make_uint4(0u, 0u, 0u, 0u);
-        if (r < n_h) qv = __ldcg((const uint4*)(q + ((size_t)t * n_heads + h0 + r) * HD + c * 8));
-        *(uint4*)(qs + r * HD + ((c ^ (r & 7)) * 8)) = qv;
+        if (r0 < n_h) qv = __ldcg((const uint4*)(q + ((size_t)t * n_heads + h0 + r0) * HD + c * 8));
+        *(uint4*)(qs + r0 * HD + ((c ^ (r0 & 7)) * 8)) = qv;
     }
     cp_async_wait<0>();
     __syncthreads();
 
-    // ---- scores of this warp's 32 keys (two blocks of 16) for the 16 rows -------------------------
+    // ---- scores of this warp's 32 keys (two blocks of 16) ---------------------------------------------
+    // The product has 16 rows and the block at most 8 heads: rows 8..15 of both products are fed
+    // zeros and their sums land in two registers that nothing reads.
     const int g = lane >> 2, t4 = lane & 3, mi = lane >> 3;
-    float s[2][2][4];
+    float idle0 = 0.0f, idle1 = 0.0f;
+    float s[2][2][2];
 #pragma unroll
     for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
-        for (int j = 0; j < 2; ++j) s[kb][j][0] = s[kb][j][1] = s[kb][j][2] = s[kb][j][3] = 0.0f;
+        for (int j = 0; j < 2; ++j) s[kb][j][0] = s[kb][j][1] = 0.0f;
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk) {
-        unsigned qf[4];
-        ldmatrix_x4(qf, tile_at<HD>(qs, lane & 15, kk * 16 + (lane >> 4) * 8));
+        unsigned qf[2];
+        ldmatrix_x2(qf, tile_at<HD>(qs, lane & 7, kk * 16 + ((lane >> 3) & 1) * 8));
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
             unsigned b[4];
             ldmatrix_x4(b, tile_at<HD>(kv, warp * 32 + kb * 16 + (mi >> 1) * 8 + (lane & 7), kk * 16 + (mi & 1) * 8));
-            mma_bf16(s[kb][0], qf, b[0], b[1]);
-            mma_bf16(s[kb][1], qf, b[2], b[3]);
+            mma_bf16_top(s[kb][0][0], s[kb][0][1], idle0, idle1, qf[0], qf[1], b[0], b[1]);
+            mma_bf16_top(s[kb][1][0], s[kb][1][1], idle0, idle1, qf[0], qf[1], b[2], b[3]);
         }
     }
-    // s[kb][j][e]: row g (e < 2) or g + 8, key warp * 32 + kb * 16 + j * 8 + 2 t4 + (e & 1)
-    float mx0 = -INFINITY, mx1 = -INFINITY;
+    // s[kb][j][e]: row g, key warp * 32 + kb * 16 + j * 8 + 2 t4 + e
+    float mx0 = -INFINITY;
 #pragma unroll
     for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
@@ -406,15 +419,11 @@ __global__ void __launch_bounds__(TC_THREADS, TC_BLOCKS) decode_attention_tc_ker
             for (int e = 0; e < 2; ++e) {
                 const bool in = warp * 32 + kb * 16 + j * 8 + 2 * t4 + e < count;
                 s[kb][j][e] = in ? s[kb][j][e] * scale : -INFINITY;
-                s[kb][j][2 + e] = in ? s[kb][j][2 + e] * scale : -INFINITY;
                 mx0 = fmaxf(mx0, s[kb][j][e]);
-                mx1 = fmaxf(mx1, s[kb][j][2 + e]);
             }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    if (t4 == 0) { smax[warp][g] = mx0; smax[warp][g + 8] = mx1; }
+    if (t4 == 0) smax[warp][g] = mx0;
     __syncthreads();                                            // every warp is done with the keys
     // the values over the keys; their fetch runs during the exponentials.  Rows past the chunk's end
     // are filled with zeros (a stale value row times a zero weight could still be NaN)
@@ -424,43 +433,38 @@ __global__ void __launch_bounds__(TC_THREADS, TC_BLOCKS) decode_attention_tc_ker
         cp_async16_zfill(kv + r * HD + ((c ^ (r & 7)) * 8), vplane + (size_t)bases[r] * HD + c * 8, r < count);
     }
     cp_async_commit();
-    float m0 = smax[0][g], m1 = smax[0][g + 8];
+    float m0 = smax[0][g];
 #pragma unroll
-    for (int w = 1; w < TC_WARPS; ++w) { m0 = fmaxf(m0, smax[w][g]); m1 = fmaxf(m1, smax[w][g + 8]); }
-    // the chunk has at least one key, so the maxima are finite
-    unsigned pf[2][4];
-    float sum0 = 0.0f, sum1 = 0.0f;
+    for (int w = 1; w < TC_WARPS; ++w) m0 = fmaxf(m0, smax[w][g]);
+    // the chunk has at least one key, so the maximum is finite
+    unsigned pf[2][2];
+    float sum0 = 0.0f;
 #pragma unroll
     for (int kb = 0; kb < 2; ++kb) {
-        float e00 = expf(s[kb][0][0] - m0), e01 = expf(s[kb][0][1] - m0), e02 = expf(s[kb][0][2] - m1), e03 = expf(s[kb][0][3] - m1);
-        float e10 = expf(s[kb][1][0] - m0), e11 = expf(s[kb][1][1] - m0), e12 = expf(s[kb][1][2] - m1), e13 = expf(s[kb][1][3] - m1);
+        float e00 = expf(s[kb][0][0] - m0), e01 = expf(s[kb][0][1] - m0);
+        float e10 = expf(s[kb][1][0] - m0), e11 = expf(s[kb][1][1] - m0);
         sum0 += (e00 + e01) + (e10 + e11);
-        sum1 += (e02 + e03) + (e12 + e13);
         pf[kb][0] = pack_bf16(e00, e01);
-        pf[kb][1] = pack_bf16(e02, e03);
-        pf[kb][2] = pack_bf16(e10, e11);
-        pf[kb][3] = pack_bf16(e12, e13);
+        pf[kb][1] = pack_bf16(e10, e11);
     }
     sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
     sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
-    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
-    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
-    if (t4 == 0) { ssum[warp][g] = sum0; ssum[warp][g + 8] = sum1; }
+    if (t4 == 0) ssum[warp][g] = sum0;
     cp_async_wait<0>();
     __syncthreads();                                            // everyone's value pieces have landed
 
     // ---- this warp's keys' share of the weighted values -----------------------------------------------
-    float o[HD / 8][4];
+    float o[HD / 8][2];
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = 0.0f;
 #pragma unroll
     for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
         for (int dp = 0; dp < HD / 16; ++dp) {
             unsigned b[4];
             ldmatrix_x4_trans(b, tile_at<HD>(kv, warp * 32 + kb * 16 + (mi & 1) * 8 + (lane & 7), dp * 16 + (mi >> 1) * 8));
-            mma_bf16(o[2 * dp], pf[kb], b[0], b[1]);
-            mma_bf16(o[2 * dp + 1], pf[kb], b[2], b[3]);
+            mma_bf16_top(o[2 * dp][0], o[2 * dp][1], idle0, idle1, pf[kb][0], pf[kb][1], b[0], b[1]);
+            mma_bf16_top(o[2 * dp + 1][0], o[2 * dp + 1][1], idle0, idle1, pf[kb][0], pf[kb][1], b[2], b[3]);
         }
     __syncthreads();                                            // every warp is done with the values: the tile is free
     float* osum = (float*)kv;                                   // [warp][row][HD] float32
@@ -636,7 +640,7 @@ CJ_EXPORT int cj_decode_attention_tc(const void* q, void* out, const void* kplan
     dim3 grid(T, n_kv * head_batches, splits);
 #define LAUNCH(HD)                                                                                                     \
     {                                                                                                                  \
-        constexpr int smem = (TC_CHUNK + 16) * HD * (int)sizeof(__nv_bfloat16);                                        \
+        constexpr int smem = (TC_CHUNK + TC_HEADS) * HD * (int)sizeof(__nv_bfloat16);                                  \
         static_assert(TC_WARPS * TC_HEADS * HD * 4 <= TC_CHUNK * HD * 2, "the warps' partial outputs must fit the tile"); \
         static bool configured = false;                                                                                \
         if (!configured) {                                                                                             \
