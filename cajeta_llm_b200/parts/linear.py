@@ -112,7 +112,8 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
         # ragged groups: weights on the rows, tokens on the product's N (cut to the tokens a
         # tile really has), the tile wide enough that most groups stream their weights once
         # (the SwiGLU form keeps two accumulators per stage: beyond 128 tokens tensor memory
-        # holds one stage only and the epilogue no longer overlaps the next tile)
+        # holds one stage only and the epilogue no longer overlaps the next tile: tiles of 160 or 256 tokens
+        # measured 131 -> 146 us a layer at 2,048 prompt rows, 198 -> 231 us at 4,096)
         tile = min(128, _group_tile(rows, w.shape[0])) if w_up is not None else _group_tile(rows, w.shape[0])
     pair_tile = 0 if tile and group_offsets is None else _pair_tile(runtime, rows, w, w_up is not None, group_offsets is not None)
     if pair_tile:
