@@ -380,6 +380,44 @@ def test_steps_of_one_size_replay_one_graph_whatever_their_requests(model_dirs):
     helpers.assert_close(outs[True][-1:], want, "bfloat16", "steps of one size", margins)
 
 
+@pytest.mark.parametrize("trial", range(6))
+def test_random_workloads_with_and_without_graphs_and_alone(model_dirs, trial):
+    """Random requests (prompts of 1 to 250 tokens, 1 to 30 new tokens) through the scheduler with random
+    limits (live requests, token budget, pages down to one more than the longest request needs, so that
+    some runs preempt): with CUDA graphs the schedule and the kernels are those of the run without, so every
+    request generates the same tokens; and in float32, whose kernels do not depend on the batch, the same
+    tokens as the request alone."""
+    import random
+    from cajeta_llm_b200.sampling.params import SamplingParams
+    rnd = random.Random(100 + trial)
+    name = rnd.choice(["M", "W", "X"])
+    vocab = helpers.CONFIGS[name]["vocab_size"]
+    reqs = [([rnd.randrange(vocab) for _ in range(rnd.choice([1, 2, 3, 17, 40, 64, 65, 130, 250]))], rnd.randint(1, 30))
+            for _ in range(rnd.randint(6, 14))]
+    max_seqs = rnd.choice([2, 3, 4, 6, 8])
+    budget = rnd.choice([32, 48, 96, 200])
+    need = max((len(p) + n + 15) // 16 + 1 for p, n in reqs)
+    blocks = rnd.choice([need + 1, need + 2, need + need // 2, need * 2, need * max_seqs])
+
+    def run(dtype, graphs, requests, seqs, pages):
+        eng = engine_for(model_dirs[name], dtype, ctx=512, max_seqs=seqs, block_tokens=16, num_blocks=pages,
+                         max_batch_tokens=budget, cuda_graphs=graphs, warmup=False)
+        ids = [eng.submit_tokens(p, n, SamplingParams(max_new_tokens=n, stop_token_ids=())) for p, n in requests]
+        eng.run_all()
+        out = [list(eng.request(i).generated) for i in ids]
+        replays = eng.runner.graph_replays
+        eng.close()
+        return out, replays
+
+    with_graphs, replays = run("bfloat16", True, reqs, max_seqs, blocks)
+    without, _ = run("bfloat16", False, reqs, max_seqs, blocks)
+    assert replays > 0 and with_graphs == without
+    if trial % 2 == 0:
+        batched, _ = run("float32", False, reqs, max_seqs, blocks)
+        alone = [run("float32", False, [r], 1, need + 2)[0][0] for r in reqs]
+        assert batched == alone
+
+
 def routing_pins(model_dir, rows):
     """The plain implementation's experts for the rows [(tokens, position)] of one step, as the
     step function's ``routing_pin``: a routed feed-forward's prefix -> int32 [rows, k]."""
