@@ -97,8 +97,9 @@ def test_rmsnorm_partial_sums_and_three_term_form(K, H):
 @pytest.mark.parametrize("H", [2048, 1540, 3584, 384])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_rmsnorm_of_a_row_does_not_depend_on_the_rows_beside_it(K, H, out_dtype):
-    """Hundreds of rows in one call against the plain norm, and bit for bit against the same rows
-    normed a few at a time - with pending partial sums, the float32 copy and the three-term form."""
+    """Hundreds of rows in one call (wide rows then take the kernel with a quarter of the threads) against
+    the plain norm, and bit for bit against the same rows normed a few at a time - with pending partial
+    sums, the float32 copy and the three-term form."""
     rows, few = 333, 9
     x0 = rnd(rows, H, seed=41, scale=3.0)
     w = rnd(H, seed=42)
