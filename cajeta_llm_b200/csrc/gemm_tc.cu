@@ -54,6 +54,19 @@ struct Args {
     int k_splits;               // > 1: each split stores its partial at out + split * split_stride
     long long split_stride;
     int offsets_settled;        // the groups' offsets were complete before the kernel before this one began
+    int choose_height;          // grouped, weights on the rows: the tile's height is chosen in the kernel (see LowTiles)
+};
+
+// Grouped products of a decode step: how many groups hold rows is known only on the device, and with it
+// the number of tiles.  352 tiles of 128 weight rows on 148 SMs are two full rounds and a third in which
+// 56 SMs stream alone; tiles of 112 or 96 rows can make the rounds come out even.  So such a launch
+// carries tensor maps for boxes of 112 and 96 rows too, and every block - from the same sum of the
+// groups' token tiles - picks the height whose last round wastes least.  A product still spans 128
+// rows: the rows past the tile's height are whatever the stage held before, and nobody reads their sums.
+constexpr int LOW_HEIGHTS = 2;
+__host__ __device__ constexpr int low_height(int i) { return i == 0 ? 112 : 96; }
+struct LowTiles {
+    CUtensorMap w[LOW_HEIGHTS], w2[LOW_HEIGHTS];
 };
 
 template <int N_MMA, bool SWAP, bool DUAL, int STAGES>
@@ -78,8 +91,9 @@ struct TileCoord {
     bool valid;
 };
 
-template <int TOK_TILE, int FEAT_TILE>
-__device__ __forceinline__ TileCoord decode_tile(const Args& p, int tile, int feat_tiles, int tok_tiles, const int* tiles_before) {
+template <int TOK_TILE>
+__device__ __forceinline__ TileCoord decode_tile(const Args& p, int tile, int feat_tiles, int tok_tiles, const int* tiles_before,
+                                                 const int FEAT_TILE) {
     TileCoord c;
     c.valid = true;
     int group = 0, f, tt;
@@ -125,10 +139,12 @@ __device__ __forceinline__ TileCoord decode_tile(const Args& p, int tile, int fe
 template <int N_MMA, bool SWAP, bool DUAL, int EPI, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-               const __grid_constant__ CUtensorMap map_w2, Args p, int feat_tiles, int tok_tiles, int total_tiles) {
+               const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ LowTiles low, Args p, int feat_tiles,
+               int tok_tiles, int total_tiles) {
     using S = Smem<N_MMA, SWAP, DUAL, STAGES>;
     constexpr int TOK_TILE = S::X_ROWS;          // token rows a tile covers
-    constexpr int FEAT_TILE = S::W_ROWS;         // weight rows a tile covers
+    int feat_tile = S::W_ROWS;                   // weight rows a tile covers (a grouped decode launch may choose fewer)
+    int height = -1;                             // which of the lower heights, or -1
     constexpr uint32_t ACC_COLS = N_MMA;         // tensor-memory columns of one accumulator
     constexpr uint32_t STAGE_COLS = ACC_COLS * (DUAL ? 2 : 1);
     // two accumulator stages when they fit the 512 columns of tensor memory, else one (the
@@ -197,7 +213,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     cj::release_successor();
     const uint32_t tmem_base = *tmem_slot;
     // a grouped launch knows its number of tiles only now (it depends on the routing)
-    if (p.group_offsets) total_tiles = tiles_before[p.groups] * feat_tiles * p.k_splits;
+    if (p.group_offsets) {
+        if (SWAP && p.choose_height) {
+            // rounds of the persistent blocks times the bytes of a tile, for each height
+            const long long tt = (long long)tiles_before[p.groups] * p.k_splits, blocks = gridDim.x;
+            long long best = (tt * feat_tiles + blocks - 1) / blocks * S::W_ROWS;
+            // (a launch of one round is as long as one tile's chain of products, whatever the tile's height)
+#pragma unroll
+            for (int i = 0; i < LOW_HEIGHTS && tt * feat_tiles > blocks; ++i) {
+                const int h = low_height(i), ft = (p.features + h - 1) / h;
+                const long long cost = (tt * ft + blocks - 1) / blocks * h;
+                if (cost < best) { best = cost; height = i; feat_tile = h; feat_tiles = ft; }
+            }
+        }
+        total_tiles = tiles_before[p.groups] * feat_tiles * p.k_splits;
+    }
+    const CUtensorMap* mw = height < 0 ? &map_w : &low.w[height];
+    const CUtensorMap* mw2 = height < 0 ? &map_w2 : &low.w2[height];
+    const uint32_t stage_tx = S::X_BYTES + (DUAL ? 2 : 1) * (uint32_t)feat_tile * BK * 2;      // bytes a stage's loads bring
 
     if (warp == 0 || warp == 6) {
         // ---- TMA producers: stream stage after stage, straight across tile boundaries ----------
@@ -211,21 +244,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (elect_one()) {
             if (mine == 0) {
                 tma_prefetch_descriptor(&map_x);
-                tma_prefetch_descriptor(&map_w);
-                if (DUAL) tma_prefetch_descriptor(&map_w2);
+                tma_prefetch_descriptor(mw);
+                if (DUAL) tma_prefetch_descriptor(mw2);
             }
             uint32_t early = 0;               // stages whose weight tiles left before the wait
             if (early_ok) {
                 for (int tile = blockIdx.x; tile < total_tiles && early < STAGES; tile += gridDim.x) {
-                    TileCoord c = decode_tile<TOK_TILE, FEAT_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before);
+                    TileCoord c = decode_tile<TOK_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before, feat_tile);
                     if (!c.valid) continue;
                     for (int i = 0; i < c.n_kb && early < STAGES; ++i, ++early) {
                         if ((int)(early % LOADERS) != mine) continue;
                         uint8_t* st = tiles + (size_t)early * S::STAGE_BYTES;
-                        mbar_expect_tx(&full_bar[early], S::STAGE_BYTES);
+                        mbar_expect_tx(&full_bar[early], stage_tx);
                         int k0 = (c.kb_begin + i) * BK;
-                        tma_load_2d(st + S::X_BYTES, &map_w, &full_bar[early], k0, c.w_row0);
-                        if (DUAL) tma_load_2d(st + S::X_BYTES + S::W_BYTES, &map_w2, &full_bar[early], k0, c.w_row0);
+                        tma_load_2d(st + S::X_BYTES, mw, &full_bar[early], k0, c.w_row0);
+                        if (DUAL) tma_load_2d(st + S::X_BYTES + S::W_BYTES, mw2, &full_bar[early], k0, c.w_row0);
                     }
                 }
                 cj::after_predecessor();
@@ -233,7 +266,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                TileCoord c = decode_tile<TOK_TILE, FEAT_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before);
+                TileCoord c = decode_tile<TOK_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before, feat_tile);
                 if (!c.valid) continue;
                 for (int i = 0; i < c.n_kb; ++i, ++it) {
                     if ((int)(it % LOADERS) != mine) continue;
@@ -247,10 +280,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     }
                     ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, 1);
                     if (!ok) break;
-                    mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+                    mbar_expect_tx(&full_bar[s], stage_tx);
                     tma_load_2d(st, &map_x, &full_bar[s], k0, c.tok0);
-                    tma_load_2d(st + S::X_BYTES, &map_w, &full_bar[s], k0, c.w_row0);
-                    if (DUAL) tma_load_2d(st + S::X_BYTES + S::W_BYTES, &map_w2, &full_bar[s], k0, c.w_row0);
+                    tma_load_2d(st + S::X_BYTES, mw, &full_bar[s], k0, c.w_row0);
+                    if (DUAL) tma_load_2d(st + S::X_BYTES + S::W_BYTES, mw2, &full_bar[s], k0, c.w_row0);
                 }
             }
         }
@@ -261,7 +294,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             uint32_t it = 0, acc_it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                TileCoord c = decode_tile<TOK_TILE, FEAT_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before);
+                TileCoord c = decode_tile<TOK_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before, feat_tile);
                 if (!c.valid) continue;
                 const int as = acc_it % ACC_STAGES;
                 ok = mbar_wait(&acc_empty[as], ((acc_it / ACC_STAGES) & 1) ^ 1, 4);      // the epilogue has drained it
@@ -307,7 +340,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         uint32_t acc_it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            TileCoord c = decode_tile<TOK_TILE, FEAT_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before);
+            TileCoord c = decode_tile<TOK_TILE>(p, tile, feat_tiles, tok_tiles, tiles_before, feat_tile);
             if (!c.valid) continue;
             const int as = acc_it % ACC_STAGES;
             ok = mbar_wait(&acc_full[as], (acc_it / ACC_STAGES) & 1, 3);
@@ -383,7 +416,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     // this thread owns one feature; column j is token tok0 + c0 + j, so a warp
                     // writes 32 consecutive features of a token at a time
                     const int feat = c.feat0 + r;
-                    if (feat >= p.features) continue;
+                    if (r >= feat_tile || feat >= p.features) continue;
                     const float b = add_bias ? p.bias[feat] : 0.0f;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -422,8 +455,18 @@ inline int sm_count() {
     return n;
 }
 
+// CAJETA_B200_TILE_HEIGHTS=0 keeps tiles of 128 weight rows in every launch
+inline bool tile_heights() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("CAJETA_B200_TILE_HEIGHTS");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
 template <int N_MMA, bool SWAP, bool DUAL, int EPI, int STAGES>
-int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2, const Args& a, cudaStream_t stream) {
+int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2, const LowTiles& low, const Args& a, cudaStream_t stream) {
     using S = Smem<N_MMA, SWAP, DUAL, STAGES>;
     auto kern = gemm_tc_kernel<N_MMA, SWAP, DUAL, EPI, STAGES>;
     static bool configured = false;
@@ -435,10 +478,12 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2,
     if (a.group_offsets && a.groups > MAX_GROUPS) return CJ_ERR_SIZE;
     int feat_tiles = (a.features + S::W_ROWS - 1) / S::W_ROWS;
     int tok_tiles = (a.tokens + S::X_ROWS - 1) / S::X_ROWS + (a.group_offsets ? a.groups : 0);
-    long long total = (long long)feat_tiles * tok_tiles * a.k_splits;
+    // (with lower tiles there are more of them: the bound covers the lowest)
+    const int most_feat_tiles = a.choose_height ? (a.features + low_height(LOW_HEIGHTS - 1) - 1) / low_height(LOW_HEIGHTS - 1) : feat_tiles;
+    long long total = (long long)most_feat_tiles * tok_tiles * a.k_splits;
     if (total > 0x7fffffffLL) return CJ_ERR_SIZE;
     int grid = (int)(total < sm_count() ? total : sm_count());
-    cj::launch(kern, dim3(grid), dim3(THREADS), S::TOTAL, stream, mx, mw, mw2, a, feat_tiles, tok_tiles, (int)total);
+    cj::launch(kern, dim3(grid), dim3(THREADS), S::TOTAL, stream, mx, mw, mw2, low, a, feat_tiles, tok_tiles, (int)((long long)feat_tiles * tok_tiles * a.k_splits));
     return cj::launch_status();
 }
 
@@ -448,31 +493,31 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2,
 // decode tokens a second at batch 8; three stages, so that two kernels' blocks fit an SM
 // side by side: -7 %)
 template <int N_MMA, bool SWAP, bool DUAL, int EPI>
-int launch_auto(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2, const Args& a, cudaStream_t stream) {
+int launch_auto(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2, const LowTiles& low, const Args& a, cudaStream_t stream) {
     constexpr int stage = Smem<N_MMA, SWAP, DUAL, 1>::STAGE_BYTES;
     constexpr int budget = (SWAP && N_MMA <= 32 ? 222 : 200) * 1024;
     constexpr int cap = SWAP && N_MMA <= 32 ? 12 : 8;
     constexpr int STAGES = (budget / stage) > cap ? cap : (budget / stage);
-    return launch<N_MMA, SWAP, DUAL, EPI, STAGES>(mx, mw, mw2, a, stream);
+    return launch<N_MMA, SWAP, DUAL, EPI, STAGES>(mx, mw, mw2, low, a, stream);
 }
 
 template <bool SWAP, bool DUAL, int EPI>
-int dispatch_n(int n_mma, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2, const Args& a, cudaStream_t s) {
+int dispatch_n(int n_mma, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2, const LowTiles& low, const Args& a, cudaStream_t s) {
     if constexpr (SWAP) {
         switch (n_mma) {
-            case 16: return launch_auto<16, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
-            case 32: return launch_auto<32, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
-            case 64: return launch_auto<64, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
-            case 96: return launch_auto<96, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
-            case 128: return launch_auto<128, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
-            case 160: return launch_auto<160, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
-            case 192: return launch_auto<192, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
-            case 256: return launch_auto<256, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
+            case 16: return launch_auto<16, SWAP, DUAL, EPI>(mx, mw, mw2, low, a, s);
+            case 32: return launch_auto<32, SWAP, DUAL, EPI>(mx, mw, mw2, low, a, s);
+            case 64: return launch_auto<64, SWAP, DUAL, EPI>(mx, mw, mw2, low, a, s);
+            case 96: return launch_auto<96, SWAP, DUAL, EPI>(mx, mw, mw2, low, a, s);
+            case 128: return launch_auto<128, SWAP, DUAL, EPI>(mx, mw, mw2, low, a, s);
+            case 160: return launch_auto<160, SWAP, DUAL, EPI>(mx, mw, mw2, low, a, s);
+            case 192: return launch_auto<192, SWAP, DUAL, EPI>(mx, mw, mw2, low, a, s);
+            case 256: return launch_auto<256, SWAP, DUAL, EPI>(mx, mw, mw2, low, a, s);
         }
     } else {
         switch (n_mma) {
-            case 128: return launch_auto<128, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
-            case 256: if constexpr (!DUAL) return launch_auto<256, SWAP, DUAL, EPI>(mx, mw, mw2, a, s);
+            case 128: return launch_auto<128, SWAP, DUAL, EPI>(mx, mw, mw2, low, a, s);
+            case 256: if constexpr (!DUAL) return launch_auto<256, SWAP, DUAL, EPI>(mx, mw, mw2, low, a, s);
         }
     }
     return CJ_ERR_SIZE;
@@ -507,10 +552,21 @@ CJ_EXPORT int cj_gemm_tc(const void* x, long long ldx, const void* w, const void
     if (!make_map_bf16(&mw, w, total_w_rows, K, K, w_box)) return CJ_ERR_ARG;
     if (w2) { if (!make_map_bf16(&mw2, w2, total_w_rows, K, K, w_box)) return CJ_ERR_ARG; }
     else mw2 = mw;
-    Args a{tokens, features, K, out, ldo, bias, group_offsets, groups, k_splits, split_stride, offsets_settled};
+    // a decode step's grouped products (weights on the rows, a handful of tokens): the kernel chooses the tile's height
+    const int choose_height = (swap && group_offsets && n_mma <= 32 && features > 128 && tile_heights()) ? 1 : 0;
+    LowTiles low;
+    for (int i = 0; i < LOW_HEIGHTS; ++i) {
+        low.w[i] = mw;
+        low.w2[i] = mw2;
+        if (choose_height) {
+            if (!make_map_bf16(&low.w[i], w, total_w_rows, K, K, low_height(i))) return CJ_ERR_ARG;
+            if (w2 && !make_map_bf16(&low.w2[i], w2, total_w_rows, K, K, low_height(i))) return CJ_ERR_ARG;
+        }
+    }
+    Args a{tokens, features, K, out, ldo, bias, group_offsets, groups, k_splits, split_stride, offsets_settled, choose_height};
 #define CASE(EPI, DUAL)                                                                              \
-    if (swap) return dispatch_n<true, DUAL, EPI>(n_mma, mx, mw, mw2, a, stream);                      \
-    else return dispatch_n<false, DUAL, EPI>(n_mma, mx, mw, mw2, a, stream);
+    if (swap) return dispatch_n<true, DUAL, EPI>(n_mma, mx, mw, mw2, low, a, stream);                 \
+    else return dispatch_n<false, DUAL, EPI>(n_mma, mx, mw, mw2, low, a, stream);
     switch (epilogue) {
         case EPI_STORE_F32: CASE(EPI_STORE_F32, false)
         case EPI_ACC_F32: CASE(EPI_ACC_F32, false)

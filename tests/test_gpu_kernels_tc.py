@@ -79,6 +79,34 @@ def test_grouped(K, swap, n_mma):
         lo += c
 
 
+@pytest.mark.parametrize("live", [20, 27, 40])
+def test_grouped_products_of_many_live_groups_choose_their_tile_height(K, live):
+    """A decode step's grouped product with more tiles than the machine has SMs picks, inside the kernel,
+    tiles of 112 or 96 weight rows when that evens out the rounds (20 live groups of 1,408 features: 112;
+    27: 96; 40: 128 stays); 1,408 is a multiple of neither, so the last tile of a group is a partial one
+    beside another group's rows.  Against the float64 products, plain and SwiGLU."""
+    E, N, Kd = 40, 1408, 256
+    g = torch.Generator().manual_seed(live)
+    chosen = sorted(torch.randperm(E, generator=g)[:live].tolist())
+    counts = [0] * E
+    for i, e in enumerate(chosen):
+        counts[e] = 1 + i % 3
+    T = sum(counts)
+    offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    x = rnd(T, Kd, seed=27)
+    wg, wu = rnd(E, N, Kd, seed=28, scale=0.1), rnd(E, N, Kd, seed=29, scale=0.1)
+    out = torch.full((T, N), -3.0, device=DEV)
+    K.gemm_tc(x, wg, out, K.EPI_STORE_F32, True, 16, group_offsets=offsets)
+    act = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tc(x, wg, act, K.EPI_SWIGLU_BF16, True, 16, w_up=wu, group_offsets=offsets, offsets_settled=True)
+    lo = 0
+    for e, c in enumerate(counts):
+        xe = x[lo:lo + c].double()
+        close(out[lo:lo + c], xe @ wg[e].double().t())
+        close(act[lo:lo + c], P.silu(xe @ wg[e].double().t()) * (xe @ wu[e].double().t()), atol=2e-2, rtol=1e-2)
+        lo += c
+
+
 @pytest.mark.parametrize("splits", [2, 4, 7])
 def test_split_k_partials_sum_to_the_product(K, splits):
     T, N, Kd = 8, 384, 1408
